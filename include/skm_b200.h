@@ -1,0 +1,182 @@
+/*
+ * C ABI of the B200 k-means engine (libskm_b200.so).
+ *
+ * Plain pointers and sizes only; every entry point returns a status code and never throws.  The
+ * drop-in C++ classes in include/superkmeans/ and the Python package are thin layers over exactly
+ * these functions.  Each declaration names the reference interface it stands in for, by path
+ * inside the SuperKMeans repository.
+ *
+ * Unless a parameter says otherwise, matrices are row-major float32 and live in HOST memory; the
+ * `*_on_device` flags switch an argument to device memory of the handle's GPU.
+ */
+#ifndef SKM_B200_H
+#define SKM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct skm_handle skm_handle;
+
+typedef enum skm_status {
+    SKM_OK = 0,
+    SKM_INVALID_ARGUMENT = 1, /* maps to std::invalid_argument / ValueError */
+    SKM_RUNTIME_ERROR = 2,    /* maps to std::runtime_error / RuntimeError */
+    SKM_CUDA_ERROR = 3,
+    SKM_COMM_ERROR = 4
+} skm_status;
+
+/* Field-for-field mirror of SuperKMeansConfig (include/superkmeans/superkmeans.h:23-55) followed by
+ * the three fields HierarchicalSuperKMeansConfig adds (include/superkmeans/hierarchical_superkmeans.h:11-17).
+ * n_threads is accepted and ignored (there are no CPU worker threads). */
+typedef struct skm_config {
+    uint32_t iters;
+    float sampling_fraction;
+    uint32_t max_points_per_cluster;
+    uint32_t n_threads;
+    uint32_t seed;
+    int32_t use_blas_only;
+    float tol;
+    float recall_tol;
+    int32_t early_termination;
+    int32_t sample_queries;
+    uint64_t objective_k;
+    float ann_explore_fraction;
+    float min_not_pruned_pct;
+    float max_not_pruned_pct;
+    float adjustment_factor_for_partial_d;
+    int32_t unrotate_centroids;
+    int32_t verbose;
+    int32_t angular;
+    int32_t suppress_warnings;
+    int32_t data_already_rotated;
+    uint32_t iters_mesoclustering;
+    uint32_t iters_fineclustering;
+    uint32_t iters_refinement;
+} skm_config;
+
+/* Mirror of SuperKMeansIterationStats (superkmeans.h:60-72). */
+typedef struct skm_iter_stats {
+    uint64_t iteration;
+    float objective;
+    float shift;
+    uint64_t split;
+    float recall;
+    float not_pruned_pct;
+    uint32_t partial_d;
+    int32_t is_gemm_only;
+} skm_iter_stats;
+
+/* Which list of statistics: SuperKMeans::iteration_stats (superkmeans.h:1492) or one of the three
+ * lists of HierarchicalSuperKMeansIterationStats (hierarchical_superkmeans.h:22-26). */
+typedef enum skm_stats_phase { SKM_STATS_FLAT = 0, SKM_STATS_MESO = 1, SKM_STATS_FINE = 2, SKM_STATS_REFINE = 3 } skm_stats_phase;
+
+/* Sum-all-reduce of `count` elements at device pointer `buf` across the ranks of a sharded run.
+ * dtype: 0 = float32, 1 = float64, 2 = int32.  Must return 0 on success, after the reduced values
+ * are visible to work submitted later on any stream of the device. */
+typedef int (*skm_allreduce_fn)(void* user, void* buf, uint64_t count, int dtype);
+
+/* Defaults of SuperKMeansConfig{} / HierarchicalSuperKMeansConfig{}. */
+void skm_default_config(skm_config* cfg, int hierarchical);
+
+/* Message of the last failure on `h`; with h == NULL, of the last failed skm_create on this thread. */
+const char* skm_last_error(const skm_handle* h);
+
+/* SuperKMeans::SuperKMeans / HierarchicalSuperKMeans::HierarchicalSuperKMeans
+ * (superkmeans.h:123-140, hierarchical_superkmeans.h:43-66): same validation, same exception
+ * classes through the status code.  `device` is the CUDA device ordinal (-1 = current device). */
+skm_status skm_create(const skm_config* cfg, uint64_t n_clusters, uint64_t dimensionality, int hierarchical, int device, skm_handle** out);
+void skm_destroy(skm_handle* h);
+
+/* The d x d rotation matrix M of ADSamplingPruner (include/superkmeans/pdx/adsampling.h:76-85);
+ * Rotate computes X * M^T (:191-215).  Setting it replaces the matrix generated from the seed. */
+skm_status skm_set_rotation(skm_handle* h, const float* m);
+skm_status skm_get_rotation(skm_handle* h, float* m_out);
+
+/* SuperKMeans::Train / HierarchicalSuperKMeans::Train (superkmeans.h:162-332,
+ * hierarchical_superkmeans.h:84-541).  centroids_out: n_clusters x d, host. */
+skm_status skm_train(skm_handle* h, const float* data, uint64_t n, int data_on_device, const float* queries, uint64_t n_queries, float* centroids_out);
+
+/* SuperKMeans::Assign (superkmeans.h:346-382).  out: n entries, host (device if *_on_device). */
+skm_status skm_assign(skm_handle* h, const float* vectors, const float* centroids, uint64_t n, uint64_t n_centroids, int on_device, uint32_t* out);
+
+/* SuperKMeans::AssignTrainingPoints (superkmeans.h:397-564). */
+skm_status skm_assign_training_points(skm_handle* h, const float* vectors, const float* centroids, uint64_t n, uint64_t n_centroids, int on_device, uint32_t* out);
+
+/* GetNClusters, IsTrained, GetSamplingFraction (superkmeans.h:567-573); n_mesoclusters
+ * (hierarchical_superkmeans.h:817). */
+uint64_t skm_n_clusters(const skm_handle* h);
+int skm_is_trained(const skm_handle* h);
+float skm_sampling_fraction(const skm_handle* h);
+uint64_t skm_n_mesoclusters(const skm_handle* h);
+
+/* iteration_stats / hierarchical_iteration_stats.  Writes at most `cap` entries; *count receives
+ * the number available. */
+skm_status skm_get_iteration_stats(const skm_handle* h, int phase, skm_iter_stats* out, uint64_t cap, uint64_t* count);
+
+/* Public member `assignments` (superkmeans.h:1491) and GetDistancesPointer (:576): state left by
+ * the last training pass, n entries each, copied to host. */
+skm_status skm_get_assignments(skm_handle* h, uint32_t* out, uint64_t n);
+skm_status skm_get_distances(skm_handle* h, float* out, uint64_t n);
+/* horizontal_centroids after training: rotated-space centroids, n_clusters x d. */
+skm_status skm_get_rotated_centroids(skm_handle* h, float* out);
+/* Objective of the last iteration accumulated in float64 (the reference sums float32). */
+double skm_last_objective_f64(const skm_handle* h);
+
+/* Sharded training: this handle holds rows [row_offset, row_offset + n_local) of a global data set
+ * of n_global rows; per-iteration sums, counts and scalars are combined through `fn`.  The
+ * reference has no counterpart (single process). */
+skm_status skm_set_shard(skm_handle* h, uint64_t n_global, uint64_t row_offset, skm_allreduce_fn fn, void* user);
+
+/* ---- single operators of the path, for callers that hold their own state and for parity tests.
+ * All arguments in host memory; each call uploads, runs the kernels and downloads. ------------- */
+
+/* ADSamplingPruner::Rotate, matrix branch (adsampling.h:191-215): out = x * m^T. */
+skm_status skm_op_rotate(int device, const float* m, const float* x, uint64_t n, uint64_t d, float* out);
+/* ADSamplingPruner::Unrotate, matrix branch (adsampling.h:273-298): out = x * m. */
+skm_status skm_op_unrotate(int device, const float* m, const float* x, uint64_t n, uint64_t d, float* out);
+/* BatchComputer::FindNearestNeighbor (include/superkmeans/distance_computers/batch_computers.h:104-171)
+ * with the norms of SuperKMeans::Assign. */
+skm_status skm_op_find_nearest(int device, const float* x, const float* y, uint64_t n, uint64_t k, uint64_t d, uint32_t* out_knn, float* out_dist);
+/* BatchComputer::FindNearestNeighborWithPruning (batch_computers.h:297-409) on rotated inputs;
+ * knn_io holds the previous assignment on entry.  not_pruned_out: per-point survivor counts. */
+skm_status skm_op_find_nearest_pruned(int device, const float* x, const float* y, uint64_t n, uint64_t k, uint64_t d, float epsilon0, uint32_t partial_d,
+                                      uint32_t* knn_io, float* dist_out, uint64_t* not_pruned_out);
+/* SuperKMeans::UpdateCentroids + ComputeCost (superkmeans.h:729-765, :973-981): per-cluster row
+ * sums and sizes, and the float64 sum of `dist` (dist and wcss_out may be NULL). */
+skm_status skm_op_update_centroids(int device, const float* x, const uint32_t* assign, const float* dist, uint64_t n, uint64_t k, uint64_t d, float* sums_out,
+                                   uint32_t* counts_out, double* wcss_out);
+/* PDXLayout::PDXify<false> (include/superkmeans/pdx/layout.h:155-232). */
+skm_status skm_op_pdxify(int device, const float* in, uint64_t n, uint64_t d, float* out);
+
+/* ---- host-side decisions of the path (no GPU needed) ---------------------------------------- */
+
+/* PDXLayout::GetDimensionSplit (layout.h:115-140). */
+void skm_host_dimension_split(uint64_t d, uint64_t* horizontal_d, uint64_t* vertical_d);
+/* ADSamplingPruner::InitializeRatios (adsampling.h:93-99): d + 1 floats. */
+void skm_host_ratios(uint64_t d, float epsilon0, float* out);
+/* Forgy indices of GenerateCentroids (superkmeans.h:1110-1123): k indices. */
+void skm_host_forgy_indices(uint64_t n_points, uint64_t k, uint32_t seed, uint64_t* out);
+/* SplitClusters (superkmeans.h:890-928; hierarchical_superkmeans.h:579-678): updates sizes in
+ * place, writes up to `cap` operations as (dst, src, kind) triples, returns n_split through
+ * *n_split and the number of operations through *n_ops. */
+skm_status skm_host_split_clusters(uint32_t* sizes, uint64_t n_samples, uint64_t n_clusters, uint32_t seed, int hierarchical, uint32_t* ops_out, uint64_t cap, uint64_t* n_ops,
+                                   uint64_t* n_split);
+/* TunePartialD (superkmeans.h:1230-1258): returns the new d'. */
+uint32_t skm_host_tune_partial_d(double not_pruned_total, uint64_t n_samples, uint64_t n_y, uint32_t partial_d, uint32_t vertical_d, float min_pct, float max_pct,
+                                 float adjustment, float* avg_out);
+/* ArrangeFineClusters (hierarchical_superkmeans.h:718-761). */
+void skm_host_arrange_fine_clusters(uint64_t n_clusters, uint64_t n_meso, uint64_t n_samples, const uint32_t* meso_sizes, uint64_t* out);
+/* Offset of (row, dim) in the PDX-blocked copy (layout.h:155-232). */
+uint64_t skm_host_pdx_offset(uint64_t row, uint64_t dim, uint64_t n, uint64_t d);
+/* The seed-derived rotation matrix (adsampling.h:76-85), d x d row-major. */
+void skm_host_rotation_matrix(uint64_t d, uint32_t seed, float* out);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* SKM_B200_H */

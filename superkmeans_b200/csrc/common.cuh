@@ -1,0 +1,109 @@
+// Shared declarations of the CUDA side: error handling, launch parameter structs and the
+// launcher prototypes implemented in kernels.cu and used by engine.cu.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+
+namespace skmb {
+
+struct CudaError : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+
+inline void cuda_check(cudaError_t e, const char* what, const char* file, int line) {
+    if (e != cudaSuccess) {
+        throw CudaError(std::string(what) + ": " + cudaGetErrorString(e) + " (" + file + ":" + std::to_string(line) + ")");
+    }
+}
+#define SKM_CUDA(x) ::skmb::cuda_check((x), #x, __FILE__, __LINE__)
+
+constexpr int kTileM = 128;        // points per CTA tile
+constexpr int kTileN = 128;        // centroids per GEMM sub-tile (SIMT path)
+constexpr int kChunk = 1024;       // centroids per pruning chunk (reference VECTOR_CHUNK_SIZE)
+constexpr int kHBlock = 64;        // dimensions per horizontal block (reference H_DIM_SIZE)
+constexpr int kUpdateTile = 1024;  // sorted points per segmented-sum tile
+
+// ---------------------------------------------------------------------------------------------
+// Launchers (all asynchronous on `stream`; pointers are device pointers unless stated otherwise)
+// ---------------------------------------------------------------------------------------------
+
+// out[i] = sum_{j < upto} x[i*ld + j]^2
+void launch_row_sqnorms(const float* x, size_t n, size_t ld, size_t upto, float* out, cudaStream_t stream);
+
+// out[n x n_out] = a[n x k_dim] * b[n_out x k_dim]^T, all row-major with leading dimensions lda,
+// ldb, ldo (NT GEMM).  Used for rotation (b = M) and un-rotation (b = M^T).
+void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, float* out, size_t ldo, size_t n, size_t n_out, size_t k_dim, cudaStream_t stream);
+
+// out[j*n + i] = in[i*n + j]
+void launch_transpose_square(const float* in, float* out, size_t n, cudaStream_t stream);
+
+// Exact nearest centroid: dist = ||x||^2 + ||y||^2 - 2 x.y over all d dims, first minimum inside a
+// 1024-centroid batch, strict < across batches, clamped at 0 when stored.
+void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist, cudaStream_t stream);
+
+struct PrunedParams {
+    const float* x;             // n x d rotated points
+    const float* y;             // k x d rotated centroids, row-major
+    const float* y_pdx;         // k x d PDX-blocked copy of y
+    const float* y_aux;         // k x vertical_d row-major copy of the first vertical_d dims
+    const float* norms_x;       // partial norms (first partial_d dims)
+    const float* norms_y;       // partial norms (first partial_d dims)
+    const float* ratios;        // d + 1 ADSampling ratios
+    uint32_t* knn;              // in: previous assignment, out: new assignment
+    float* dist;                // out: distance to the new assignment
+    uint32_t* not_pruned;       // out: per-point count of first-test survivors (added)
+    uint2* scratch;             // candidate lists, pruned_scratch_elems() entries
+    size_t n, k, d;
+    uint32_t partial_d, vertical_d, horizontal_d;
+};
+int pruned_grid_size(int device);
+size_t pruned_scratch_elems(int grid);
+void launch_assign_pruned(const PrunedParams& p, int grid, cudaStream_t stream);
+
+// Centroid update -------------------------------------------------------------------------------
+struct UpdateWorkspace {
+    uint32_t* keys_a = nullptr;   // n
+    uint32_t* keys_b = nullptr;   // n
+    uint32_t* vals_a = nullptr;   // n
+    uint32_t* vals_b = nullptr;   // n
+    uint32_t* digit_table = nullptr;  // 256 * n_units
+    uint32_t* seg_offsets = nullptr;  // k + 1
+    float* tile_partials = nullptr;   // n_tiles * 2 * d
+    double* block_sums = nullptr;     // reduction partials (>= 1024)
+    size_t n_cap = 0, k_cap = 0, d = 0;
+};
+size_t update_sort_units(size_t n);
+size_t update_tiles(size_t n);
+
+// counts[c] = |{i : assign[i] == c}|, sums[c] = sum of x rows assigned to c (deterministic order),
+// *wcss = sum_i dist[i] (double), *not_pruned_total = sum_i not_pruned[i] (may be null).
+void launch_update(const float* x, const uint32_t* assign, const float* dist, const uint32_t* not_pruned, size_t n, size_t k, size_t d, UpdateWorkspace& ws, float* sums, uint32_t* counts, double* wcss, unsigned long long* not_pruned_total, cudaStream_t stream);
+
+// c[i][:] *= 1/counts[i] for non-empty clusters
+void launch_scale_by_counts(float* c, const uint32_t* counts, size_t k, size_t d, cudaStream_t stream);
+
+struct SplitOpDev {
+    uint32_t dst, src, kind;
+    float wc;
+};
+void launch_apply_split_ops(float* c, size_t d, const SplitOpDev* ops, size_t n_ops, cudaStream_t stream);
+void launch_normalize_rows(float* c, size_t k, size_t d, cudaStream_t stream);
+
+// PDX-blocked copy and first-vertical_d copy of a row-major k x d matrix
+void launch_pdxify(const float* c, float* pdx, float* aux, size_t k, size_t d, size_t vertical_d, cudaStream_t stream);
+
+// *out = sum_c ||a[c] - b[c]||^2
+void launch_shift(const float* a, const float* b, size_t k, size_t d, double* block_sums, double* out, cudaStream_t stream);
+
+// out[i][:] = in[idx[i]][:]
+void launch_gather_rows(const float* in, const uint64_t* idx, float* out, size_t n_out, size_t d, cudaStream_t stream);
+void launch_gather_f32(const float* in, const uint64_t* idx, float* out, size_t n_out, cudaStream_t stream);
+// out[idx[i]] = in[i] + offset
+void launch_scatter_u32_offset(const uint32_t* in, const uint64_t* idx, uint32_t* out, size_t n, uint32_t offset, cudaStream_t stream);
+
+} // namespace skmb

@@ -1,0 +1,1013 @@
+// Host orchestration: see engine.h.  Every step cites the reference code it reproduces
+// (paths relative to the SuperKMeans repository, include/superkmeans/...).
+#include "engine.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <iostream>
+#include <numeric>
+#include <random>
+
+namespace skmb {
+
+namespace {
+
+struct DeviceGuard {
+    int prev = 0;
+    explicit DeviceGuard(int dev) {
+        SKM_CUDA(cudaGetDevice(&prev));
+        if (prev != dev) SKM_CUDA(cudaSetDevice(dev));
+        else prev = -1;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+__global__ void u64_to_f64_kernel(const unsigned long long* in, double* out) { *out = static_cast<double>(*in); }
+
+// Rows per staging chunk when streaming a host matrix through the GPU.
+size_t chunk_rows_for(size_t d, size_t n) {
+    const size_t target_bytes = size_t{256} << 20;
+    size_t rows = std::max<size_t>(1024, target_bytes / (d * sizeof(float)));
+    rows = (rows / kTileM) * kTileM;
+    return std::max<size_t>(kTileM, std::min(rows, std::max<size_t>(n, 1)));
+}
+
+void ensure_positive(bool ok, const char* name) {
+    if (!ok) throw std::invalid_argument(std::string("Value must be positive: ") + name);
+}
+
+int resolve_device(int device) {
+    if (device >= 0) return device;
+    int cur = 0;
+    SKM_CUDA(cudaGetDevice(&cur));
+    return cur;
+}
+
+} // namespace
+
+// -------------------------------------------------------------------------------------------------
+// Construction (superkmeans.h:123-140, hierarchical_superkmeans.h:43-66)
+// -------------------------------------------------------------------------------------------------
+Engine::Engine(const skm_config& cfg, size_t n_clusters, size_t d, bool hierarchical, int device)
+    : cfg_(cfg), k_(n_clusters), d_(d), hierarchical_(hierarchical), device_(0) {
+    ensure_positive(n_clusters > 0, "n_clusters");
+    ensure_positive(d > 0, "dimensionality");
+    ensure_positive(cfg.iters > 0, "config.iters");
+    ensure_positive(cfg.sampling_fraction > 0, "config.sampling_fraction");
+    if (cfg.sampling_fraction > 1.0) throw std::invalid_argument("sampling_fraction must be <= 1.0");
+    if (hierarchical) {
+        ensure_positive(cfg.iters_mesoclustering > 0, "config.iters_mesoclustering");
+        ensure_positive(cfg.iters_fineclustering > 0, "config.iters_fineclustering");
+    }
+    if (cfg_.data_already_rotated) cfg_.unrotate_centroids = 0;
+    epsilon0_ = hierarchical ? kHierarchicalPrunerInitialThreshold : kPrunerInitialThreshold;
+    const DimensionSplit split = dimension_split(d);
+    vertical_d_ = static_cast<uint32_t>(split.vertical_d);
+    horizontal_d_ = static_cast<uint32_t>(split.horizontal_d);
+
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        throw CudaError("no CUDA device is available: this engine has no CPU path");
+    }
+    device_ = resolve_device(device);
+    if (device_ >= count) throw std::invalid_argument("device ordinal out of range");
+    DeviceGuard guard(device_);
+    SKM_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+    SKM_CUDA(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
+    const std::vector<float> ratios = make_ratios(d, epsilon0_);
+    SKM_CUDA(cudaMemcpy(ratios_dev_.ensure(d + 1), ratios.data(), sizeof(float) * (d + 1), cudaMemcpyHostToDevice));
+    scalars_dev_.ensure(8);
+    np_total_dev_.ensure(1);
+    scalars_host_.ensure(8);
+    if (hierarchical && n_clusters <= 128 && !cfg.suppress_warnings) {
+        std::cout << "WARNING: n_clusters <= 128 is not recommended for HierarchicalSuperKMeans. "
+                     "Consider using at least 128 clusters."
+                  << std::endl;
+    }
+}
+
+Engine::~Engine() {
+    cudaSetDevice(device_);
+    if (stream_) cudaStreamDestroy(stream_);
+    if (copy_stream_) cudaStreamDestroy(copy_stream_);
+}
+
+const std::vector<skm_iter_stats>& Engine::stats(int phase) const {
+    switch (phase) {
+        case SKM_STATS_MESO: return stats_meso_;
+        case SKM_STATS_FINE: return stats_fine_;
+        case SKM_STATS_REFINE: return stats_refine_;
+        default: return stats_flat_;
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
+// Rotation (adsampling.h:76-85, :191-215, :273-298)
+// -------------------------------------------------------------------------------------------------
+void Engine::ensure_rotation() {
+    if (rotation_ready_) return;
+    if (rotation_host_.empty()) rotation_host_ = make_rotation_matrix(d_, cfg_.seed);
+    SKM_CUDA(cudaMemcpyAsync(m_dev_.ensure(d_ * d_), rotation_host_.data(), sizeof(float) * d_ * d_, cudaMemcpyHostToDevice, stream_));
+    mt_dev_.ensure(d_ * d_);
+    launch_transpose_square(m_dev_.get(), mt_dev_.get(), d_, stream_);
+    sync();
+    rotation_ready_ = true;
+}
+
+void Engine::set_rotation(const float* m_host) {
+    DeviceGuard guard(device_);
+    rotation_host_.assign(m_host, m_host + d_ * d_);
+    rotation_ready_ = false;
+    ensure_rotation();
+}
+
+void Engine::get_rotation(float* m_out) {
+    DeviceGuard guard(device_);
+    ensure_rotation();
+    std::memcpy(m_out, rotation_host_.data(), sizeof(float) * d_ * d_);
+}
+
+void Engine::set_shard(size_t n_global, size_t row_offset, skm_allreduce_fn fn, void* user) {
+    shard_n_global_ = n_global;
+    shard_row_offset_ = row_offset;
+    allreduce_fn_ = fn;
+    allreduce_user_ = user;
+}
+
+void Engine::allreduce(void* buf, size_t count, int dtype) {
+    if (!allreduce_fn_) return;
+    sync();
+    if (allreduce_fn_(allreduce_user_, buf, count, dtype) != 0) {
+        throw std::runtime_error("all-reduce callback reported a failure");
+    }
+}
+
+// dst[n x d] (device) = rotate(src).  Host sources are streamed through two staging buffers so
+// that the copy of chunk i+1 overlaps the rotation of chunk i.
+void Engine::rotate_to_device(const float* src, bool src_on_device, size_t n, float* dst) {
+    if (n == 0) return;
+    ensure_rotation();
+    if (src_on_device) {
+        launch_gemm_nt(src, d_, m_dev_.get(), d_, dst, d_, n, d_, d_, stream_);
+        return;
+    }
+    const size_t rows = chunk_rows_for(d_, n);
+    DeviceBuffer<float> raw[2];
+    raw[0].ensure(rows * d_);
+    if (n > rows) raw[1].ensure(rows * d_);
+    cudaEvent_t copied[2], consumed[2];
+    for (int i = 0; i < 2; ++i) {
+        SKM_CUDA(cudaEventCreateWithFlags(&copied[i], cudaEventDisableTiming));
+        SKM_CUDA(cudaEventCreateWithFlags(&consumed[i], cudaEventDisableTiming));
+    }
+    size_t ci = 0;
+    for (size_t r0 = 0; r0 < n; r0 += rows, ++ci) {
+        const int b = static_cast<int>(ci & 1);
+        const size_t cnt = std::min(rows, n - r0);
+        if (ci >= 2) SKM_CUDA(cudaStreamWaitEvent(copy_stream_, consumed[b], 0));
+        SKM_CUDA(cudaMemcpyAsync(raw[b].get(), src + r0 * d_, sizeof(float) * cnt * d_, cudaMemcpyHostToDevice, copy_stream_));
+        SKM_CUDA(cudaEventRecord(copied[b], copy_stream_));
+        SKM_CUDA(cudaStreamWaitEvent(stream_, copied[b], 0));
+        launch_gemm_nt(raw[b].get(), d_, m_dev_.get(), d_, dst + r0 * d_, d_, cnt, d_, d_, stream_);
+        SKM_CUDA(cudaEventRecord(consumed[b], stream_));
+    }
+    sync();
+    for (int i = 0; i < 2; ++i) {
+        cudaEventDestroy(copied[i]);
+        cudaEventDestroy(consumed[i]);
+    }
+}
+
+void Engine::upload_rows(const float* src, bool src_on_device, size_t n, float* dst) {
+    if (n == 0) return;
+    SKM_CUDA(cudaMemcpyAsync(dst, src, sizeof(float) * n * d_, src_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, stream_));
+    sync();
+}
+
+void Engine::prepare_update_workspace(size_t n, size_t k) {
+    const size_t units = update_sort_units(n);
+    const size_t tiles = update_tiles(n);
+    ws_.keys_a = ws_keys_a_.ensure(n);
+    ws_.keys_b = ws_keys_b_.ensure(n);
+    ws_.vals_a = ws_vals_a_.ensure(n);
+    ws_.vals_b = ws_vals_b_.ensure(n);
+    ws_.digit_table = ws_table_.ensure(256 * units + (256 * units) / 2048 + 64);
+    ws_.seg_offsets = ws_offsets_.ensure(k + 1);
+    ws_.tile_partials = ws_partials_.ensure(tiles * 2 * d_);
+    ws_.block_sums = ws_block_sums_.ensure(2048);
+    ws_.n_cap = n;
+    ws_.k_cap = k;
+    ws_.d = d_;
+}
+
+// -------------------------------------------------------------------------------------------------
+// Initial centroids (superkmeans.h:1100-1142): Forgy rows, optionally rotated, into c_prev_.
+// -------------------------------------------------------------------------------------------------
+void Engine::generate_centroids_from_host(const float* data, bool on_device, size_t n_points_global, size_t k_cur, bool rotate) {
+    const std::vector<size_t> idx = forgy_indices(n_points_global, k_cur, cfg_.seed);
+    DeviceBuffer<float> raw;
+    raw.ensure(k_cur * d_);
+    const bool sharded = allreduce_fn_ != nullptr;
+    const size_t n_local = n_samples_;
+    if (on_device && !sharded) {
+        std::vector<uint64_t> idx64(idx.begin(), idx.end());
+        DeviceBuffer<uint64_t> idx_dev;
+        SKM_CUDA(cudaMemcpyAsync(idx_dev.ensure(k_cur), idx64.data(), sizeof(uint64_t) * k_cur, cudaMemcpyHostToDevice, stream_));
+        launch_gather_rows(data, idx_dev.get(), raw.get(), k_cur, d_, stream_);
+        sync();
+    } else {
+        // Rows owned by other shards stay zero and arrive through the sum all-reduce.
+        std::vector<float> host(k_cur * d_, 0.0f);
+        for (size_t i = 0; i < k_cur; ++i) {
+            size_t g = idx[i];
+            if (sharded) {
+                if (g < shard_row_offset_ || g >= shard_row_offset_ + n_local) continue;
+                g -= shard_row_offset_;
+            }
+            if (on_device) {
+                SKM_CUDA(cudaMemcpy(&host[i * d_], data + g * d_, sizeof(float) * d_, cudaMemcpyDeviceToHost));
+            } else {
+                std::memcpy(&host[i * d_], data + g * d_, sizeof(float) * d_);
+            }
+        }
+        SKM_CUDA(cudaMemcpyAsync(raw.get(), host.data(), sizeof(float) * k_cur * d_, cudaMemcpyHostToDevice, stream_));
+        sync();
+        if (sharded) allreduce(raw.get(), k_cur * d_, 0);
+    }
+    if (rotate) {
+        ensure_rotation();
+        launch_gemm_nt(raw.get(), d_, m_dev_.get(), d_, c_prev_.get(), d_, k_cur, d_, d_, stream_);
+    } else {
+        SKM_CUDA(cudaMemcpyAsync(c_prev_.get(), raw.get(), sizeof(float) * k_cur * d_, cudaMemcpyDeviceToDevice, stream_));
+    }
+    sync();
+}
+
+// Fine-clustering variant (hierarchical_superkmeans.h:333-342): rows of an already rotated device
+// buffer, no rotation.
+void Engine::generate_centroids_from_device_rows(const float* dev_rows, size_t n_points, size_t k_cur) {
+    const std::vector<size_t> idx = forgy_indices(n_points, k_cur, cfg_.seed);
+    std::vector<uint64_t> idx64(idx.begin(), idx.end());
+    DeviceBuffer<uint64_t> idx_dev;
+    SKM_CUDA(cudaMemcpyAsync(idx_dev.ensure(k_cur), idx64.data(), sizeof(uint64_t) * k_cur, cudaMemcpyHostToDevice, stream_));
+    launch_gather_rows(dev_rows, idx_dev.get(), c_prev_.get(), k_cur, d_, stream_);
+    sync();
+}
+
+// -------------------------------------------------------------------------------------------------
+// One pruned assignment pass (batch_computers.h:297-409)
+// -------------------------------------------------------------------------------------------------
+void Engine::run_pruned_pass(const float* x, size_t n, size_t k_cur, const float* y, const float* norms_x, const float* norms_y, uint32_t* knn, float* dist, uint32_t* not_pruned) {
+    if (pruned_grid_ == 0) pruned_grid_ = pruned_grid_size(device_);
+    pruned_scratch_.ensure(pruned_scratch_elems(pruned_grid_));
+    PrunedParams p{};
+    p.x = x;
+    p.y = y;
+    p.y_pdx = c_pdx_.get();
+    p.y_aux = c_aux_.get();
+    p.norms_x = norms_x;
+    p.norms_y = norms_y;
+    p.ratios = ratios_dev_.get();
+    p.knn = knn;
+    p.dist = dist;
+    p.not_pruned = not_pruned;
+    p.scratch = pruned_scratch_.get();
+    p.n = n;
+    p.k = k_cur;
+    p.d = d_;
+    p.partial_d = partial_d_;
+    p.vertical_d = vertical_d_;
+    p.horizontal_d = horizontal_d_;
+    launch_assign_pruned(p, pruned_grid_, stream_);
+}
+
+// -------------------------------------------------------------------------------------------------
+// ConsolidateCentroids (superkmeans.h:936-968): mean, split, optional normalisation, PDX copies.
+// counts_host_ holds this iteration's (globally reduced) cluster sizes.
+// -------------------------------------------------------------------------------------------------
+void Engine::consolidate(size_t n_samples_global, size_t k_cur) {
+    launch_scale_by_counts(c_cur_.get(), counts_.get(), k_cur, d_, stream_);
+    sizes_host_.assign(counts_host_.get(), counts_host_.get() + k_cur);
+    if (!split_can_terminate(sizes_host_, n_samples_global, k_cur)) {
+        throw std::runtime_error("cannot repopulate empty clusters: no cluster holds more than one point");
+    }
+    std::vector<SplitOp> ops;
+    n_split_ = hierarchical_ ? split_clusters_hierarchical(sizes_host_, n_samples_global, k_cur, cfg_.seed, ops)
+                             : split_clusters_flat(sizes_host_, n_samples_global, k_cur, cfg_.seed, ops);
+    if (!ops.empty()) {
+        static_assert(sizeof(SplitOp) == sizeof(SplitOpDev), "layout");
+        SKM_CUDA(cudaMemcpyAsync(split_ops_dev_.ensure(ops.size()), ops.data(), sizeof(SplitOp) * ops.size(), cudaMemcpyHostToDevice, stream_));
+        launch_apply_split_ops(c_cur_.get(), d_, split_ops_dev_.get(), ops.size(), stream_);
+        sync();  // `ops` must outlive the asynchronous copy
+    }
+    if (cfg_.angular) launch_normalize_rows(c_cur_.get(), k_cur, d_, stream_);
+    launch_pdxify(c_cur_.get(), c_pdx_.get(), c_aux_.get(), k_cur, d_, vertical_d_, stream_);
+}
+
+// -------------------------------------------------------------------------------------------------
+// RunIteration<GEMM_ONLY> (superkmeans.h:786-879)
+// -------------------------------------------------------------------------------------------------
+void Engine::run_iteration(bool gemm_only, const IterationInput& in, size_t iter_idx, bool is_first, std::vector<skm_iter_stats>& target) {
+    if (!is_first) c_cur_.swap(c_prev_);
+    const size_t n = in.n_samples, k_cur = in.n_clusters;
+    float* norms = in.norms;
+    if (gemm_only) {
+        launch_row_sqnorms(c_prev_.get(), k_cur, d_, d_, centroid_norms_.get(), stream_);
+        launch_assign_full(in.x, c_prev_.get(), n, k_cur, d_, norms, centroid_norms_.get(), assignments_.get(), distances_.get(), stream_);
+    } else {
+        launch_row_sqnorms(c_prev_.get(), k_cur, d_, partial_d_, centroid_norms_.get(), stream_);
+        run_pruned_pass(in.x, n, k_cur, c_prev_.get(), norms, centroid_norms_.get(), assignments_.get(), distances_.get(), not_pruned_.get());
+    }
+    // UpdateCentroids + ComputeCost (superkmeans.h:729-765, :973-981)
+    launch_update(in.x, assignments_.get(), distances_.get(), gemm_only ? nullptr : not_pruned_.get(), n, k_cur, d_, ws_, c_cur_.get(), counts_.get(), scalars_dev_.get(),
+                  gemm_only ? nullptr : np_total_dev_.get(), stream_);
+    if (!gemm_only) {
+        u64_to_f64_kernel<<<1, 1, 0, stream_>>>(np_total_dev_.get(), scalars_dev_.get() + 1);
+        SKM_CUDA(cudaGetLastError());
+    }
+    if (allreduce_fn_) {
+        allreduce(c_cur_.get(), k_cur * d_, 0);
+        allreduce(counts_.get(), k_cur, 2);
+        allreduce(scalars_dev_.get(), 2, 1);
+    }
+    SKM_CUDA(cudaMemcpyAsync(counts_host_.ensure(k_), counts_.get(), sizeof(uint32_t) * k_cur, cudaMemcpyDeviceToHost, stream_));
+    SKM_CUDA(cudaMemcpyAsync(scalars_host_.get(), scalars_dev_.get(), sizeof(double) * 2, cudaMemcpyDeviceToHost, stream_));
+    sync();
+    const double wcss = scalars_host_.get()[0];
+
+    float avg_not_pruned = -1.0f;
+    const uint32_t old_partial_d = partial_d_;
+    if (!gemm_only) {
+        const TuneResult t = tune_partial_d(scalars_host_.get()[1], in.n_samples_global, k_cur, partial_d_, vertical_d_, cfg_.min_not_pruned_pct, cfg_.max_not_pruned_pct,
+                                            cfg_.adjustment_factor_for_partial_d);
+        avg_not_pruned = t.avg_not_pruned_pct;
+        partial_d_ = t.new_partial_d;
+        if (t.changed) launch_row_sqnorms(in.x, n, d_, partial_d_, norms, stream_);
+    }
+    consolidate(in.n_samples_global, k_cur);
+
+    prev_cost_ = cost_;
+    cost_ = static_cast<float>(wcss);
+    last_cost_f64_ = wcss;
+    // ComputeShift (superkmeans.h:988-998)
+    launch_shift(c_cur_.get(), c_prev_.get(), k_cur, d_, ws_.block_sums, scalars_dev_.get() + 2, stream_);
+    SKM_CUDA(cudaMemcpyAsync(scalars_host_.get() + 2, scalars_dev_.get() + 2, sizeof(double), cudaMemcpyDeviceToHost, stream_));
+    sync();
+    shift_ = static_cast<float>(scalars_host_.get()[2]);
+
+    skm_iter_stats s{};
+    s.iteration = iter_idx + 1;
+    s.objective = cost_;
+    s.shift = shift_;
+    s.split = n_split_;
+    s.recall = 0.0f;
+    s.is_gemm_only = gemm_only ? 1 : 0;
+    s.not_pruned_pct = gemm_only ? -1.0f : avg_not_pruned;
+    s.partial_d = gemm_only ? 0u : old_partial_d;
+    target.push_back(s);
+    if (cfg_.verbose) {
+        std::cout << "Iteration " << iter_idx + 1 << " | Objective: " << cost_ << " | Shift: " << shift_ << " | Split: " << n_split_;
+        if (gemm_only) std::cout << " [GEMM-only]";
+        else std::cout << " | Not Pruned %: " << avg_not_pruned * 100.0f << " | d': " << old_partial_d << " -> " << partial_d_;
+        std::cout << std::endl;
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
+// Train
+// -------------------------------------------------------------------------------------------------
+void Engine::train(const float* data, size_t n, bool on_device, const float* queries, size_t n_queries, float* centroids_out) {
+    DeviceGuard guard(device_);
+    ensure_positive(n > 0, "n");
+    if (trained_) throw std::runtime_error("The clustering has already been trained");
+    const size_t n_global = allreduce_fn_ ? shard_n_global_ : n;
+    if (hierarchical_) {
+        if (n_queries > 0 && !cfg_.suppress_warnings) {
+            std::cout << "WARNING: Early Termination by Recall is not supported in HierarchicalSuperKMeans" << std::endl;
+        }
+    }
+    if (n_global < k_) throw std::runtime_error("The number of points should be at least as large as the number of clusters");
+    if (!hierarchical_) {
+        if (n_queries > 0 && queries == nullptr && !cfg_.sample_queries) {
+            throw std::invalid_argument("Queries must be provided if n_queries > 0 and sample_queries is false");
+        }
+        if (n_queries > 0) {
+            throw std::runtime_error("recall-driven early termination (queries) is not available in this engine");
+        }
+    }
+    if (allreduce_fn_ && cfg_.sampling_fraction != 1.0f) {
+        throw std::runtime_error("sharded training requires sampling_fraction == 1.0");
+    }
+    if (allreduce_fn_ && hierarchical_) {
+        throw std::runtime_error("sharded training is available for the flat algorithm only");
+    }
+    if (hierarchical_) train_hierarchical(data, n, on_device, centroids_out);
+    else train_flat(data, n, on_device, centroids_out);
+}
+
+// Copies (and rotates unless the data is pre-rotated) the training rows into x_rot_; with sampling
+// the rows are the first n_samples entries of the shuffle (superkmeans.h:1385-1443).
+static void gather_host_rows(const float* data, const size_t* idx, size_t cnt, size_t d, float* out) {
+#pragma omp parallel for
+    for (size_t i = 0; i < cnt; ++i) std::memcpy(out + i * d, data + idx[i] * d, sizeof(float) * d);
+}
+
+void Engine::train_flat(const float* data, size_t n, bool on_device, float* centroids_out) {
+    stats_flat_.clear();
+    const size_t n_global = allreduce_fn_ ? shard_n_global_ : n;
+    const size_t n_samples_global = n_vectors_to_sample(n_global, k_, cfg_.sampling_fraction, cfg_.max_points_per_cluster, false);
+    if (n_samples_global < k_) {
+        throw std::runtime_error("Not enough samples to train. Try increasing the sampling_fraction or max_points_per_cluster");
+    }
+    n_samples_ = allreduce_fn_ ? n : n_samples_global;
+    const bool rotate = !cfg_.data_already_rotated;
+    partial_d_ = initial_partial_d(vertical_d_);
+
+    c_cur_.ensure(k_ * d_);
+    c_prev_.ensure(k_ * d_);
+    c_pdx_.ensure(k_ * d_);
+    c_aux_.ensure(k_ * static_cast<size_t>(vertical_d_) + 1);
+    centroid_norms_.ensure(k_);
+    counts_.ensure(k_);
+    counts_host_.ensure(k_);
+    assignments_.ensure(n_samples_);
+    distances_.ensure(n_samples_);
+    not_pruned_.ensure(n_samples_);
+    data_norms_.ensure(n_samples_);
+    x_rot_.ensure(n_samples_ * d_);
+    prepare_update_workspace(n_samples_, k_);
+
+    // GenerateCentroids picks among the first n_samples rows of the caller's data (:221-222).
+    generate_centroids_from_host(data, on_device, n_samples_global, k_, rotate);
+
+    if (n_samples_global < n_global) {
+        sampled_indices_ = sampling_permutation(n, cfg_.seed);
+        const size_t rows = chunk_rows_for(d_, n_samples_);
+        if (on_device) {
+            DeviceBuffer<uint64_t> idx_dev;
+            DeviceBuffer<float> raw;
+            idx_dev.ensure(rows);
+            raw.ensure(rows * d_);
+            std::vector<uint64_t> idx64(rows);
+            for (size_t r0 = 0; r0 < n_samples_; r0 += rows) {
+                const size_t cnt = std::min(rows, n_samples_ - r0);
+                for (size_t i = 0; i < cnt; ++i) idx64[i] = sampled_indices_[r0 + i];
+                SKM_CUDA(cudaMemcpyAsync(idx_dev.get(), idx64.data(), sizeof(uint64_t) * cnt, cudaMemcpyHostToDevice, stream_));
+                float* dst = rotate ? raw.get() : x_rot_.get() + r0 * d_;
+                launch_gather_rows(data, idx_dev.get(), dst, cnt, d_, stream_);
+                if (rotate) rotate_to_device(raw.get(), true, cnt, x_rot_.get() + r0 * d_);
+                sync();
+            }
+        } else {
+            std::vector<float> staged(rows * d_);
+            for (size_t r0 = 0; r0 < n_samples_; r0 += rows) {
+                const size_t cnt = std::min(rows, n_samples_ - r0);
+                gather_host_rows(data, sampled_indices_.data() + r0, cnt, d_, staged.data());
+                if (rotate) rotate_to_device(staged.data(), false, cnt, x_rot_.get() + r0 * d_);
+                else upload_rows(staged.data(), false, cnt, x_rot_.get() + r0 * d_);
+            }
+        }
+    } else {
+        if (rotate) rotate_to_device(data, on_device, n_samples_, x_rot_.get());
+        else upload_rows(data, on_device, n_samples_, x_rot_.get());
+    }
+    sync();
+
+    launch_row_sqnorms(x_rot_.get(), n_samples_, d_, d_, data_norms_.get(), stream_);
+
+    const bool always_gemm_only = d_ < kDimensionThresholdForPruning || cfg_.use_blas_only || k_ <= kNClustersThresholdForPruning;
+    bool partial_norms_computed = false;
+    IterationInput in{x_rot_.get(), n_samples_, n_samples_global, k_, data_norms_.get()};
+    for (size_t iter = 0; iter < cfg_.iters; ++iter) {
+        const bool gemm_only = (iter == 0) || always_gemm_only;
+        if (!gemm_only && !partial_norms_computed) {
+            launch_row_sqnorms(x_rot_.get(), n_samples_, d_, partial_d_, data_norms_.get(), stream_);
+            partial_norms_computed = true;
+        }
+        run_iteration(gemm_only, in, iter, iter == 0, stats_flat_);
+        if (cfg_.early_termination && should_stop_early(shift_, cost_, prev_cost_, cfg_.tol, iter)) break;
+    }
+    trained_ = true;
+    output_centroids(centroids_out);
+    x_rot_.release();
+    ws_partials_.release();
+}
+
+// GetOutputCentroids (superkmeans.h:1341-1351)
+void Engine::output_centroids(float* out_host) {
+    if (cfg_.unrotate_centroids) {
+        ensure_rotation();
+        DeviceBuffer<float> tmp;
+        tmp.ensure(k_ * d_);
+        launch_gemm_nt(c_cur_.get(), d_, mt_dev_.get(), d_, tmp.get(), d_, k_, d_, d_, stream_);
+        SKM_CUDA(cudaMemcpyAsync(out_host, tmp.get(), sizeof(float) * k_ * d_, cudaMemcpyDeviceToHost, stream_));
+        sync();
+    } else {
+        SKM_CUDA(cudaMemcpyAsync(out_host, c_cur_.get(), sizeof(float) * k_ * d_, cudaMemcpyDeviceToHost, stream_));
+        sync();
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
+// HierarchicalSuperKMeans::Train (hierarchical_superkmeans.h:84-541)
+// -------------------------------------------------------------------------------------------------
+void Engine::train_hierarchical(const float* data, size_t n, bool on_device, float* centroids_out) {
+    stats_meso_.clear();
+    stats_fine_.clear();
+    stats_refine_.clear();
+    n_meso_ = n_mesoclusters(k_);
+    n_samples_ = n_vectors_to_sample(n, k_, cfg_.sampling_fraction, cfg_.max_points_per_cluster, true);
+    if (n_samples_ < k_) {
+        throw std::runtime_error("Not enough samples to train. Try increasing the sampling_fraction or max_points_per_cluster");
+    }
+    const size_t n_all = n_samples_;
+    const bool rotate = !cfg_.data_already_rotated;
+    partial_d_ = initial_partial_d(vertical_d_);
+    const uint32_t initial_pd = partial_d_;
+
+    c_cur_.ensure(k_ * d_);
+    c_prev_.ensure(k_ * d_);
+    c_pdx_.ensure(k_ * d_);
+    c_aux_.ensure(k_ * static_cast<size_t>(vertical_d_) + 1);
+    centroid_norms_.ensure(k_);
+    counts_.ensure(k_);
+    counts_host_.ensure(k_);
+    assignments_.ensure(n);
+    distances_.ensure(n);
+    not_pruned_.ensure(n_all);
+    data_norms_.ensure(n_all);
+    full_norms_.ensure(n_all);
+    final_assignments_.ensure(n_all);
+    final_centroids_.ensure(k_ * d_);
+    x_rot_.ensure(n_all * d_);
+    prepare_update_workspace(n_all, k_);
+
+    // ---- phase 1: mesoclustering (:161-257)
+    generate_centroids_from_host(data, on_device, n_all, n_meso_, rotate);
+    if (n_all < n) {
+        sampled_indices_ = sampling_permutation(n, cfg_.seed);
+        const size_t rows = chunk_rows_for(d_, n_all);
+        std::vector<float> staged;
+        DeviceBuffer<uint64_t> idx_dev;
+        DeviceBuffer<float> raw;
+        std::vector<uint64_t> idx64;
+        if (on_device) {
+            idx_dev.ensure(rows);
+            raw.ensure(rows * d_);
+            idx64.resize(rows);
+        } else {
+            staged.resize(rows * d_);
+        }
+        for (size_t r0 = 0; r0 < n_all; r0 += rows) {
+            const size_t cnt = std::min(rows, n_all - r0);
+            if (on_device) {
+                for (size_t i = 0; i < cnt; ++i) idx64[i] = sampled_indices_[r0 + i];
+                SKM_CUDA(cudaMemcpyAsync(idx_dev.get(), idx64.data(), sizeof(uint64_t) * cnt, cudaMemcpyHostToDevice, stream_));
+                float* dst = rotate ? raw.get() : x_rot_.get() + r0 * d_;
+                launch_gather_rows(data, idx_dev.get(), dst, cnt, d_, stream_);
+                if (rotate) rotate_to_device(raw.get(), true, cnt, x_rot_.get() + r0 * d_);
+                sync();
+            } else {
+                gather_host_rows(data, sampled_indices_.data() + r0, cnt, d_, staged.data());
+                if (rotate) rotate_to_device(staged.data(), false, cnt, x_rot_.get() + r0 * d_);
+                else upload_rows(staged.data(), false, cnt, x_rot_.get() + r0 * d_);
+            }
+        }
+    } else {
+        if (rotate) rotate_to_device(data, on_device, n_all, x_rot_.get());
+        else upload_rows(data, on_device, n_all, x_rot_.get());
+    }
+    sync();
+    launch_row_sqnorms(x_rot_.get(), n_all, d_, d_, data_norms_.get(), stream_);
+    SKM_CUDA(cudaMemcpyAsync(full_norms_.get(), data_norms_.get(), sizeof(float) * n_all, cudaMemcpyDeviceToDevice, stream_));
+
+    {
+        const bool always_gemm_only = d_ < kDimensionThresholdForPruning || cfg_.use_blas_only || n_meso_ <= kNClustersThresholdForPruning;
+        bool partial_norms_computed = false;
+        IterationInput in{x_rot_.get(), n_all, n_all, n_meso_, data_norms_.get()};
+        for (size_t iter = 0; iter < cfg_.iters_mesoclustering; ++iter) {
+            const bool gemm_only = (iter == 0) || always_gemm_only;
+            if (!gemm_only && !partial_norms_computed) {
+                launch_row_sqnorms(x_rot_.get(), n_all, d_, partial_d_, data_norms_.get(), stream_);
+                partial_norms_computed = true;
+            }
+            run_iteration(gemm_only, in, iter, iter == 0, stats_meso_);
+            if (cfg_.early_termination && should_stop_early(shift_, cost_, prev_cost_, cfg_.tol, iter)) break;
+        }
+    }
+
+    // ---- partition the points by mesocluster (:260-286).  The sizes are cluster_sizes as left by
+    // the last split, exactly as in the reference; writes that would leave the index array (possible
+    // only when that split moved sizes around) are dropped.
+    const std::vector<uint32_t> meso_sizes(sizes_host_.begin(), sizes_host_.begin() + n_meso_);
+    std::vector<uint32_t> meso_assign(n_all);
+    SKM_CUDA(cudaMemcpyAsync(meso_assign.data(), assignments_.get(), sizeof(uint32_t) * n_all, cudaMemcpyDeviceToHost, stream_));
+    sync();
+    std::vector<uint64_t> flat(n_all, 0);
+    std::vector<size_t> offsets(n_meso_ + 1, 0);
+    for (size_t m = 0; m < n_meso_; ++m) offsets[m + 1] = offsets[m] + meso_sizes[m];
+    {
+        std::vector<size_t> next = offsets;
+        for (size_t i = 0; i < n_all; ++i) {
+            const size_t pos = next[meso_assign[i]]++;
+            if (pos < n_all) flat[pos] = i;
+        }
+    }
+    SKM_CUDA(cudaMemcpyAsync(meso_indices_dev_.ensure(n_all), flat.data(), sizeof(uint64_t) * n_all, cudaMemcpyHostToDevice, stream_));
+    sync();
+
+    // ---- phase 2: fine clustering, one mesocluster after the other (:301-425)
+    const std::vector<size_t> fine_nums = arrange_fine_clusters(k_, n_meso_, n_all, meso_sizes);
+    const size_t max_meso = *std::max_element(meso_sizes.begin(), meso_sizes.end());
+    meso_buffer_.ensure(std::max<size_t>(max_meso, 1) * d_);
+    meso_norms_.ensure(std::max<size_t>(max_meso, 1));
+    size_t fine_offset = 0;
+    for (size_t m = 0; m < n_meso_; ++m) {
+        const size_t n_fine = fine_nums[m];
+        if (n_fine == 0) continue;
+        partial_d_ = initial_pd;
+        const size_t msize = std::min<size_t>(meso_sizes[m], n_all - std::min(offsets[m], n_all));
+        n_samples_ = msize;
+        if (msize < n_fine) {
+            throw std::runtime_error("a mesocluster holds fewer points than the fine clusters allotted to it");
+        }
+        const uint64_t* idx = meso_indices_dev_.get() + offsets[m];
+        launch_gather_rows(x_rot_.get(), idx, meso_buffer_.get(), msize, d_, stream_);      // CompactMesoclusterToBuffer (:685-704)
+        launch_gather_f32(full_norms_.get(), idx, meso_norms_.get(), msize, stream_);
+        generate_centroids_from_device_rows(meso_buffer_.get(), msize, n_fine);
+
+        const bool always_gemm_only = d_ < kDimensionThresholdForPruning || cfg_.use_blas_only || n_fine <= kNClustersThresholdForPruning;
+        bool partial_norms_computed = false;
+        IterationInput in{meso_buffer_.get(), msize, msize, n_fine, meso_norms_.get()};
+        for (size_t iter = 0; iter < cfg_.iters_fineclustering; ++iter) {
+            const bool gemm_only = (iter == 0) || always_gemm_only;
+            if (!gemm_only && !partial_norms_computed) {
+                launch_row_sqnorms(meso_buffer_.get(), msize, d_, partial_d_, meso_norms_.get(), stream_);
+                partial_norms_computed = true;
+            }
+            run_iteration(gemm_only, in, iter, iter == 0, stats_fine_);
+            if (cfg_.early_termination && should_stop_early(shift_, cost_, prev_cost_, cfg_.tol, iter)) break;
+        }
+        // GetTrueAssignmentsFromIndirectionBuffer (:763-779) and the centroid copy (:416-423)
+        launch_scatter_u32_offset(assignments_.get(), idx, final_assignments_.get(), msize, static_cast<uint32_t>(fine_offset), stream_);
+        SKM_CUDA(cudaMemcpyAsync(final_centroids_.get() + fine_offset * d_, c_cur_.get(), sizeof(float) * n_fine * d_, cudaMemcpyDeviceToDevice, stream_));
+        fine_offset += n_fine;
+    }
+
+    // ---- phase 3: refinement over all clusters (:434-516)
+    n_samples_ = n_all;
+    partial_d_ = std::max<uint32_t>(kMinPartialD, vertical_d_ / 3);
+    SKM_CUDA(cudaMemcpyAsync(c_cur_.get(), final_centroids_.get(), sizeof(float) * k_ * d_, cudaMemcpyDeviceToDevice, stream_));   // SetupCentroids (:788-815)
+    launch_pdxify(c_cur_.get(), c_pdx_.get(), c_aux_.get(), k_, d_, vertical_d_, stream_);
+    SKM_CUDA(cudaMemcpyAsync(c_prev_.get(), final_centroids_.get(), sizeof(float) * k_ * d_, cudaMemcpyDeviceToDevice, stream_));
+    SKM_CUDA(cudaMemcpyAsync(assignments_.get(), final_assignments_.get(), sizeof(uint32_t) * n_all, cudaMemcpyDeviceToDevice, stream_));
+    {
+        const bool always_gemm_only = d_ < kDimensionThresholdForPruning || k_ <= kNClustersThresholdForPruning;
+        bool partial_norms_computed = false;
+        IterationInput in{x_rot_.get(), n_all, n_all, k_, data_norms_.get()};
+        for (size_t iter = 0; iter < cfg_.iters_refinement; ++iter) {
+            if (!always_gemm_only && !partial_norms_computed) {
+                launch_row_sqnorms(x_rot_.get(), n_all, d_, partial_d_, data_norms_.get(), stream_);
+                partial_norms_computed = true;
+            } else if (always_gemm_only && !partial_norms_computed) {
+                // data_norms_ still holds whatever the mesoclustering left; GEMM-only needs full norms.
+                SKM_CUDA(cudaMemcpyAsync(data_norms_.get(), full_norms_.get(), sizeof(float) * n_all, cudaMemcpyDeviceToDevice, stream_));
+                partial_norms_computed = true;
+            }
+            run_iteration(always_gemm_only, in, iter, false, stats_refine_);
+        }
+    }
+    sync();
+    trained_ = true;
+    output_centroids(centroids_out);
+    x_rot_.release();
+    meso_buffer_.release();
+    ws_partials_.release();
+}
+
+// -------------------------------------------------------------------------------------------------
+// Assign (superkmeans.h:346-382): stateless brute force in the caller's domain, streamed in row
+// chunks so that host inputs of any size fit.
+// -------------------------------------------------------------------------------------------------
+void Engine::assign(const float* vectors, const float* centroids, size_t n, size_t n_centroids, bool on_device, uint32_t* out) {
+    DeviceGuard guard(device_);
+    if (n == 0) return;
+    if (n_centroids == 0) throw std::invalid_argument("Value must be positive: n_centroids");
+    DeviceBuffer<float> c_dev_own, cn;
+    const float* c_dev = centroids;
+    if (!on_device) {
+        SKM_CUDA(cudaMemcpyAsync(c_dev_own.ensure(n_centroids * d_), centroids, sizeof(float) * n_centroids * d_, cudaMemcpyHostToDevice, stream_));
+        c_dev = c_dev_own.get();
+    }
+    launch_row_sqnorms(c_dev, n_centroids, d_, d_, cn.ensure(n_centroids), stream_);
+    if (on_device) {
+        DeviceBuffer<float> xn, dist;
+        launch_row_sqnorms(vectors, n, d_, d_, xn.ensure(n), stream_);
+        launch_assign_full(vectors, c_dev, n, n_centroids, d_, xn.get(), cn.get(), out, dist.ensure(n), stream_);
+        sync();
+        return;
+    }
+    const size_t rows = chunk_rows_for(d_, n);
+    DeviceBuffer<float> xb[2], xn[2], dist[2];
+    DeviceBuffer<uint32_t> knn[2];
+    cudaEvent_t copied[2], consumed[2];
+    for (int i = 0; i < 2; ++i) {
+        xb[i].ensure(rows * d_);
+        xn[i].ensure(rows);
+        dist[i].ensure(rows);
+        knn[i].ensure(rows);
+        SKM_CUDA(cudaEventCreateWithFlags(&copied[i], cudaEventDisableTiming));
+        SKM_CUDA(cudaEventCreateWithFlags(&consumed[i], cudaEventDisableTiming));
+    }
+    size_t ci = 0;
+    for (size_t r0 = 0; r0 < n; r0 += rows, ++ci) {
+        const int b = static_cast<int>(ci & 1);
+        const size_t cnt = std::min(rows, n - r0);
+        if (ci >= 2) SKM_CUDA(cudaStreamWaitEvent(copy_stream_, consumed[b], 0));
+        SKM_CUDA(cudaMemcpyAsync(xb[b].get(), vectors + r0 * d_, sizeof(float) * cnt * d_, cudaMemcpyHostToDevice, copy_stream_));
+        SKM_CUDA(cudaEventRecord(copied[b], copy_stream_));
+        SKM_CUDA(cudaStreamWaitEvent(stream_, copied[b], 0));
+        launch_row_sqnorms(xb[b].get(), cnt, d_, d_, xn[b].get(), stream_);
+        launch_assign_full(xb[b].get(), c_dev, cnt, n_centroids, d_, xn[b].get(), cn.get(), knn[b].get(), dist[b].get(), stream_);
+        SKM_CUDA(cudaMemcpyAsync(out + r0, knn[b].get(), sizeof(uint32_t) * cnt, cudaMemcpyDeviceToHost, stream_));
+        SKM_CUDA(cudaEventRecord(consumed[b], stream_));
+    }
+    sync();
+    for (int i = 0; i < 2; ++i) {
+        cudaEventDestroy(copied[i]);
+        cudaEventDestroy(consumed[i]);
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
+// AssignTrainingPoints (superkmeans.h:397-564)
+// -------------------------------------------------------------------------------------------------
+void Engine::assign_training_points(const float* vectors, const float* centroids, size_t n, size_t n_centroids, bool on_device, uint32_t* out) {
+    DeviceGuard guard(device_);
+    if (!trained_) throw std::runtime_error("AssignTrainingPoints requires SuperKMeans to be trained first");
+    if (cfg_.use_blas_only || d_ < kDimensionThresholdForPruning || k_ <= kNClustersThresholdForPruning) {
+        if (!cfg_.suppress_warnings) {
+            std::cout << "WARNING: AssignTrainingPoints cannot use pruning, falling back to brute force Assign" << std::endl;
+        }
+        assign(vectors, centroids, n, n_centroids, on_device, out);
+        return;
+    }
+    if (n == 0) return;
+    partial_d_ = initial_partial_d(vertical_d_);
+    launch_row_sqnorms(c_cur_.get(), k_, d_, partial_d_, centroid_norms_.get(), stream_);
+
+    // Seeds: one starting centroid per vector.
+    std::vector<uint32_t> seeds(n);
+    const bool store_state = (cfg_.sampling_fraction == 1.0f);
+    if (cfg_.sampling_fraction == 1.0f) {
+        if (n > assignments_.capacity()) throw std::runtime_error("AssignTrainingPoints needs the vectors used in Train()");
+        SKM_CUDA(cudaMemcpyAsync(seeds.data(), assignments_.get(), sizeof(uint32_t) * n, cudaMemcpyDeviceToHost, stream_));
+        sync();
+    } else {
+        if (sampled_indices_.size() != n) throw std::runtime_error("AssignTrainingPoints needs the vectors used in Train()");
+        std::vector<uint32_t> trained_assign(n_samples_);
+        SKM_CUDA(cudaMemcpyAsync(trained_assign.data(), assignments_.get(), sizeof(uint32_t) * n_samples_, cudaMemcpyDeviceToHost, stream_));
+        sync();
+        size_t cur = 0;
+        for (; cur < n_samples_; ++cur) seeds[sampled_indices_[cur]] = trained_assign[cur];
+        if (cfg_.sampling_fraction <= 0.8f && on_device) {
+            throw std::runtime_error("AssignTrainingPoints with sampling_fraction <= 0.8 needs host vectors");
+        }
+        if (cfg_.sampling_fraction > 0.8f) {
+            // Size-proportional random seeds (:477-484).
+            std::mt19937 rng(cfg_.seed + 1);
+            std::discrete_distribution<uint32_t> cluster_dist(sizes_host_.begin(), sizes_host_.begin() + k_);
+            for (; cur < n; ++cur) seeds[sampled_indices_[cur]] = cluster_dist(rng);
+        } else {
+            // Two-level seeds (:505-542): cluster the centroids into sqrt(k) groups and start every
+            // unsampled vector at one representative centroid of its group.
+            std::vector<float> cent_host(n_centroids * d_), vec_host_own;
+            if (on_device) {
+                SKM_CUDA(cudaMemcpy(cent_host.data(), centroids, sizeof(float) * n_centroids * d_, cudaMemcpyDeviceToHost));
+            } else {
+                std::memcpy(cent_host.data(), centroids, sizeof(float) * n_centroids * d_);
+            }
+            skm_config tmp{};
+            skm_default_config(&tmp, 0);
+            tmp.iters = 10;
+            tmp.sampling_fraction = 1.0f;
+            tmp.use_blas_only = 0;
+            tmp.verbose = cfg_.verbose;
+            tmp.suppress_warnings = cfg_.suppress_warnings;
+            tmp.seed = cfg_.seed;
+            tmp.angular = cfg_.angular;
+            tmp.data_already_rotated = cfg_.data_already_rotated;
+            const size_t n_meso = static_cast<size_t>(std::sqrt(n_centroids));
+            Engine nested(tmp, n_meso, d_, false, device_);
+            if (!rotation_host_.empty()) nested.set_rotation(rotation_host_.data());
+            std::vector<float> meso_centroids(n_meso * d_);
+            nested.train(cent_host.data(), n_centroids, false, nullptr, 0, meso_centroids.data());
+            std::vector<uint32_t> meso_assign(n), cent_to_meso(n_centroids);
+            nested.assign(vectors, meso_centroids.data(), n, n_meso, false, meso_assign.data());
+            nested.assign(cent_host.data(), meso_centroids.data(), n_centroids, n_meso, false, cent_to_meso.data());
+            std::vector<uint32_t> meso_to_original(n_meso, 0);
+            for (size_t c = 0; c < n_centroids; ++c) meso_to_original[cent_to_meso[c]] = static_cast<uint32_t>(c);
+            for (; cur < n; ++cur) {
+                const size_t orig = sampled_indices_[cur];
+                seeds[orig] = meso_to_original[meso_assign[orig]];
+            }
+        }
+    }
+
+    if (store_state) {
+        assignments_.ensure(n);
+        distances_.ensure(n);
+    }
+    const size_t rows = chunk_rows_for(d_, n);
+    DeviceBuffer<float> xr, xn, dist;
+    DeviceBuffer<uint32_t> knn, np;
+    xr.ensure(rows * d_);
+    xn.ensure(rows);
+    dist.ensure(rows);
+    knn.ensure(rows);
+    np.ensure(rows);
+    for (size_t r0 = 0; r0 < n; r0 += rows) {
+        const size_t cnt = std::min(rows, n - r0);
+        if (cfg_.data_already_rotated) upload_rows(vectors + r0 * d_, on_device, cnt, xr.get());
+        else rotate_to_device(vectors + r0 * d_, on_device, cnt, xr.get());
+        launch_row_sqnorms(xr.get(), cnt, d_, partial_d_, xn.get(), stream_);
+        SKM_CUDA(cudaMemcpyAsync(knn.get(), seeds.data() + r0, sizeof(uint32_t) * cnt, cudaMemcpyHostToDevice, stream_));
+        run_pruned_pass(xr.get(), cnt, k_, c_cur_.get(), xn.get(), centroid_norms_.get(), knn.get(), dist.get(), np.get());
+        SKM_CUDA(cudaMemcpyAsync(out + r0, knn.get(), sizeof(uint32_t) * cnt, on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, stream_));
+        if (store_state) {
+            SKM_CUDA(cudaMemcpyAsync(assignments_.get() + r0, knn.get(), sizeof(uint32_t) * cnt, cudaMemcpyDeviceToDevice, stream_));
+            SKM_CUDA(cudaMemcpyAsync(distances_.get() + r0, dist.get(), sizeof(float) * cnt, cudaMemcpyDeviceToDevice, stream_));
+        }
+        sync();
+    }
+}
+
+void Engine::get_assignments(uint32_t* out, size_t n) {
+    DeviceGuard guard(device_);
+    if (n > assignments_.capacity()) throw std::invalid_argument("more assignments requested than the engine holds");
+    SKM_CUDA(cudaMemcpy(out, assignments_.get(), sizeof(uint32_t) * n, cudaMemcpyDeviceToHost));
+}
+
+void Engine::get_distances(float* out, size_t n) {
+    DeviceGuard guard(device_);
+    if (n > distances_.capacity()) throw std::invalid_argument("more distances requested than the engine holds");
+    SKM_CUDA(cudaMemcpy(out, distances_.get(), sizeof(float) * n, cudaMemcpyDeviceToHost));
+}
+
+void Engine::get_rotated_centroids(float* out) {
+    DeviceGuard guard(device_);
+    if (!trained_) throw std::runtime_error("the model has not been trained");
+    SKM_CUDA(cudaMemcpy(out, c_cur_.get(), sizeof(float) * k_ * d_, cudaMemcpyDeviceToHost));
+}
+
+// -------------------------------------------------------------------------------------------------
+// Stateless operators
+// -------------------------------------------------------------------------------------------------
+namespace {
+struct OpContext {
+    DeviceGuard guard;
+    cudaStream_t stream = nullptr;
+    explicit OpContext(int device) : guard(resolve_device(device)) { SKM_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking)); }
+    ~OpContext() {
+        if (stream) cudaStreamDestroy(stream);
+    }
+    template <class T>
+    T* upload(DeviceBuffer<T>& buf, const T* host, size_t count) {
+        T* p = buf.ensure(count);
+        if (count) SKM_CUDA(cudaMemcpyAsync(p, host, sizeof(T) * count, cudaMemcpyHostToDevice, stream));
+        return p;
+    }
+    template <class T>
+    void download(T* host, const T* dev, size_t count) {
+        if (count) SKM_CUDA(cudaMemcpyAsync(host, dev, sizeof(T) * count, cudaMemcpyDeviceToHost, stream));
+    }
+    void sync() { SKM_CUDA(cudaStreamSynchronize(stream)); }
+};
+} // namespace
+
+void Engine::op_rotate(int device, const float* m, const float* x, size_t n, size_t d, float* out, bool inverse) {
+    OpContext ctx(device);
+    DeviceBuffer<float> md, mtd, xd, od;
+    ctx.upload(md, m, d * d);
+    const float* b = md.get();
+    if (inverse) {
+        launch_transpose_square(md.get(), mtd.ensure(d * d), d, ctx.stream);
+        b = mtd.get();
+    }
+    ctx.upload(xd, x, n * d);
+    launch_gemm_nt(xd.get(), d, b, d, od.ensure(n * d), d, n, d, d, ctx.stream);
+    ctx.download(out, od.get(), n * d);
+    ctx.sync();
+}
+
+void Engine::op_find_nearest(int device, const float* x, const float* y, size_t n, size_t k, size_t d, uint32_t* out_knn, float* out_dist) {
+    OpContext ctx(device);
+    DeviceBuffer<float> xd, yd, nx, ny, dist;
+    DeviceBuffer<uint32_t> knn;
+    ctx.upload(xd, x, n * d);
+    ctx.upload(yd, y, k * d);
+    launch_row_sqnorms(xd.get(), n, d, d, nx.ensure(n), ctx.stream);
+    launch_row_sqnorms(yd.get(), k, d, d, ny.ensure(k), ctx.stream);
+    launch_assign_full(xd.get(), yd.get(), n, k, d, nx.get(), ny.get(), knn.ensure(n), dist.ensure(n), ctx.stream);
+    ctx.download(out_knn, knn.get(), n);
+    ctx.download(out_dist, dist.get(), n);
+    ctx.sync();
+}
+
+void Engine::op_find_nearest_pruned(int device, const float* x, const float* y, size_t n, size_t k, size_t d, float eps0, uint32_t partial_d, uint32_t* knn_io, float* dist_out,
+                                    uint64_t* not_pruned_out) {
+    const DimensionSplit split = dimension_split(d);
+    if (split.horizontal_d == 0) throw std::invalid_argument("the pruned search needs d > 64");
+    if (partial_d == 0 || partial_d > split.vertical_d) throw std::invalid_argument("partial_d must be in [1, vertical_d]");
+    for (size_t i = 0; i < n; ++i)
+        if (knn_io[i] >= k) throw std::invalid_argument("previous assignment out of range");
+    OpContext ctx(device);
+    DeviceBuffer<float> xd, yd, nx, ny, pdx, aux, dist, ratios_d;
+    DeviceBuffer<uint32_t> knn, np;
+    DeviceBuffer<uint2> scratch;
+    const std::vector<float> ratios = make_ratios(d, eps0);
+    ctx.upload(xd, x, n * d);
+    ctx.upload(yd, y, k * d);
+    ctx.upload(ratios_d, ratios.data(), d + 1);
+    ctx.upload(knn, knn_io, n);
+    launch_row_sqnorms(xd.get(), n, d, partial_d, nx.ensure(n), ctx.stream);
+    launch_row_sqnorms(yd.get(), k, d, partial_d, ny.ensure(k), ctx.stream);
+    launch_pdxify(yd.get(), pdx.ensure(k * d), aux.ensure(k * split.vertical_d + 1), k, d, split.vertical_d, ctx.stream);
+    int dev = 0;
+    SKM_CUDA(cudaGetDevice(&dev));
+    const int grid = pruned_grid_size(dev);
+    PrunedParams p{};
+    p.x = xd.get();
+    p.y = yd.get();
+    p.y_pdx = pdx.get();
+    p.y_aux = aux.get();
+    p.norms_x = nx.get();
+    p.norms_y = ny.get();
+    p.ratios = ratios_d.get();
+    p.knn = knn.get();
+    p.dist = dist.ensure(n);
+    p.not_pruned = np.ensure(n);
+    p.scratch = scratch.ensure(pruned_scratch_elems(grid));
+    p.n = n;
+    p.k = k;
+    p.d = d;
+    p.partial_d = partial_d;
+    p.vertical_d = static_cast<uint32_t>(split.vertical_d);
+    p.horizontal_d = static_cast<uint32_t>(split.horizontal_d);
+    launch_assign_pruned(p, grid, ctx.stream);
+    std::vector<uint32_t> np_host(n);
+    ctx.download(knn_io, knn.get(), n);
+    ctx.download(dist_out, dist.get(), n);
+    ctx.download(np_host.data(), np.get(), n);
+    ctx.sync();
+    for (size_t i = 0; i < n; ++i) not_pruned_out[i] = np_host[i];
+}
+
+void Engine::op_update(int device, const float* x, const uint32_t* assign, const float* dist, size_t n, size_t k, size_t d, float* sums_out, uint32_t* counts_out, double* wcss_out) {
+    for (size_t i = 0; i < n; ++i)
+        if (assign[i] >= k) throw std::invalid_argument("assignment out of range");
+    OpContext ctx(device);
+    DeviceBuffer<float> xd, dd, sums, partials;
+    DeviceBuffer<uint32_t> ad, counts, ka, kb, va, vb, table, offs;
+    DeviceBuffer<double> block_sums, wcss;
+    ctx.upload(xd, x, n * d);
+    ctx.upload(ad, assign, n);
+    std::vector<float> zeros;
+    if (dist) ctx.upload(dd, dist, n);
+    else {
+        zeros.assign(n, 0.f);
+        ctx.upload(dd, zeros.data(), n);
+    }
+    UpdateWorkspace ws;
+    const size_t units = update_sort_units(n), tiles = update_tiles(n);
+    ws.keys_a = ka.ensure(n);
+    ws.keys_b = kb.ensure(n);
+    ws.vals_a = va.ensure(n);
+    ws.vals_b = vb.ensure(n);
+    ws.digit_table = table.ensure(256 * units + (256 * units) / 2048 + 64);
+    ws.seg_offsets = offs.ensure(k + 1);
+    ws.tile_partials = partials.ensure(std::max<size_t>(tiles, 1) * 2 * d);
+    ws.block_sums = block_sums.ensure(2048);
+    launch_update(xd.get(), ad.get(), dd.get(), nullptr, n, k, d, ws, sums.ensure(k * d), counts.ensure(k), wcss.ensure(1), nullptr, ctx.stream);
+    ctx.download(sums_out, sums.get(), k * d);
+    ctx.download(counts_out, counts.get(), k);
+    double w = 0.0;
+    ctx.download(&w, wcss.get(), 1);
+    ctx.sync();
+    if (wcss_out) *wcss_out = w;
+}
+
+void Engine::op_pdxify(int device, const float* in, size_t n, size_t d, float* out) {
+    OpContext ctx(device);
+    DeviceBuffer<float> id, od;
+    ctx.upload(id, in, n * d);
+    launch_pdxify(id.get(), od.ensure(n * d), nullptr, n, d, dimension_split(d).vertical_d, ctx.stream);
+    ctx.download(out, od.get(), n * d);
+    ctx.sync();
+}
+
+} // namespace skmb

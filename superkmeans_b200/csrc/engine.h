@@ -1,0 +1,198 @@
+// Host orchestration of the k-means hot path: owns the device state and drives the kernels in the
+// same order as the reference's Train / RunIteration / Assign / AssignTrainingPoints.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/skm_b200.h"
+#include "common.cuh"
+#include "host_logic.h"
+
+namespace skmb {
+
+template <class T>
+class DeviceBuffer {
+  public:
+    DeviceBuffer() = default;
+    DeviceBuffer(const DeviceBuffer&) = delete;
+    DeviceBuffer& operator=(const DeviceBuffer&) = delete;
+    ~DeviceBuffer() { release(); }
+    void release() {
+        if (p_) cudaFree(p_);
+        p_ = nullptr;
+        cap_ = 0;
+    }
+    // Grows (never shrinks) to at least `count` elements; contents are not preserved on growth.
+    T* ensure(size_t count) {
+        if (count > cap_) {
+            release();
+            SKM_CUDA(cudaMalloc(&p_, sizeof(T) * (count ? count : 1)));
+            cap_ = count;
+        }
+        return p_;
+    }
+    T* get() const { return p_; }
+    size_t capacity() const { return cap_; }
+    void swap(DeviceBuffer& o) {
+        std::swap(p_, o.p_);
+        std::swap(cap_, o.cap_);
+    }
+
+  private:
+    T* p_ = nullptr;
+    size_t cap_ = 0;
+};
+
+template <class T>
+class PinnedBuffer {
+  public:
+    PinnedBuffer() = default;
+    PinnedBuffer(const PinnedBuffer&) = delete;
+    PinnedBuffer& operator=(const PinnedBuffer&) = delete;
+    ~PinnedBuffer() { release(); }
+    void release() {
+        if (p_) cudaFreeHost(p_);
+        p_ = nullptr;
+        cap_ = 0;
+    }
+    T* ensure(size_t count) {
+        if (count > cap_) {
+            release();
+            SKM_CUDA(cudaMallocHost(&p_, sizeof(T) * (count ? count : 1)));
+            cap_ = count;
+        }
+        return p_;
+    }
+    T* get() const { return p_; }
+
+  private:
+    T* p_ = nullptr;
+    size_t cap_ = 0;
+};
+
+class Engine {
+  public:
+    Engine(const skm_config& cfg, size_t n_clusters, size_t d, bool hierarchical, int device);
+    ~Engine();
+
+    void set_rotation(const float* m_host);
+    void get_rotation(float* m_out);
+    void set_shard(size_t n_global, size_t row_offset, skm_allreduce_fn fn, void* user);
+
+    void train(const float* data, size_t n, bool on_device, const float* queries, size_t n_queries, float* centroids_out);
+    void assign(const float* vectors, const float* centroids, size_t n, size_t n_centroids, bool on_device, uint32_t* out);
+    void assign_training_points(const float* vectors, const float* centroids, size_t n, size_t n_centroids, bool on_device, uint32_t* out);
+
+    void get_assignments(uint32_t* out, size_t n);
+    void get_distances(float* out, size_t n);
+    void get_rotated_centroids(float* out);
+
+    size_t n_clusters() const { return k_; }
+    bool trained() const { return trained_; }
+    float sampling_fraction() const { return cfg_.sampling_fraction; }
+    size_t n_mesoclusters_value() const { return n_meso_; }
+    double last_objective_f64() const { return last_cost_f64_; }
+    const std::vector<skm_iter_stats>& stats(int phase) const;
+    int device() const { return device_; }
+
+    // Stateless operators (used by the skm_op_* entry points).
+    static void op_rotate(int device, const float* m, const float* x, size_t n, size_t d, float* out, bool inverse);
+    static void op_find_nearest(int device, const float* x, const float* y, size_t n, size_t k, size_t d, uint32_t* out_knn, float* out_dist);
+    static void op_find_nearest_pruned(int device, const float* x, const float* y, size_t n, size_t k, size_t d, float eps0, uint32_t partial_d, uint32_t* knn_io, float* dist_out,
+                                       uint64_t* not_pruned_out);
+    static void op_update(int device, const float* x, const uint32_t* assign, const float* dist, size_t n, size_t k, size_t d, float* sums_out, uint32_t* counts_out, double* wcss_out);
+    static void op_pdxify(int device, const float* in, size_t n, size_t d, float* out);
+
+  private:
+    struct IterationInput {
+        const float* x;       // device, rotated, n_samples x d
+        size_t n_samples;     // local rows
+        size_t n_samples_global;
+        size_t n_clusters;
+        float* norms;         // device, full or partial norms of x (rewritten when d' changes)
+    };
+
+    void ensure_rotation();
+    void rotate_to_device(const float* src, bool src_on_device, size_t n, float* dst);
+    void upload_rows(const float* src, bool src_on_device, size_t n, float* dst);
+    void prepare_update_workspace(size_t n, size_t k);
+    void run_iteration(bool gemm_only, const IterationInput& in, size_t iter_idx, bool is_first, std::vector<skm_iter_stats>& target);
+    void run_pruned_pass(const float* x, size_t n, size_t k_cur, const float* y, const float* norms_x, const float* norms_y, uint32_t* knn, float* dist, uint32_t* not_pruned);
+    void consolidate(size_t n_samples_global, size_t k_cur);
+    void generate_centroids_from_host(const float* data, bool on_device, size_t n_points_global, size_t k_cur, bool rotate);
+    void generate_centroids_from_device_rows(const float* dev_rows, size_t n_points, size_t k_cur);
+    void train_flat(const float* data, size_t n, bool on_device, float* centroids_out);
+    void train_hierarchical(const float* data, size_t n, bool on_device, float* centroids_out);
+    void output_centroids(float* out_host);
+    void allreduce(void* buf, size_t count, int dtype);
+    void sync() { SKM_CUDA(cudaStreamSynchronize(stream_)); }
+
+    skm_config cfg_;
+    size_t k_, d_;
+    bool hierarchical_;
+    int device_;
+    cudaStream_t stream_ = nullptr;
+    cudaStream_t copy_stream_ = nullptr;
+
+    // sharding
+    size_t shard_n_global_ = 0, shard_row_offset_ = 0;
+    skm_allreduce_fn allreduce_fn_ = nullptr;
+    void* allreduce_user_ = nullptr;
+
+    // pruner state
+    float epsilon0_;
+    std::vector<float> rotation_host_;  // d x d, empty until needed
+    bool rotation_ready_ = false;
+    DeviceBuffer<float> m_dev_, mt_dev_, ratios_dev_;
+    uint32_t vertical_d_ = 0, horizontal_d_ = 0, partial_d_ = 0;
+
+    // iteration state
+    bool trained_ = false;
+    size_t n_samples_ = 0;      // rows held locally
+    size_t n_split_ = 0;
+    float prev_cost_ = 0.f, cost_ = 0.f, shift_ = 0.f;
+    double last_cost_f64_ = 0.0;
+    size_t n_meso_ = 0;
+
+    DeviceBuffer<float> x_rot_;          // training rows (rotated)
+    DeviceBuffer<float> data_norms_;     // full or partial norms of the training rows
+    DeviceBuffer<float> c_cur_, c_prev_; // row-major centroids (horizontal_centroids / prev_centroids)
+    DeviceBuffer<float> c_pdx_, c_aux_;  // PDX-blocked copy and first-vertical_d copy
+    DeviceBuffer<float> centroid_norms_;
+    DeviceBuffer<uint32_t> counts_;
+    DeviceBuffer<uint32_t> assignments_, not_pruned_;
+    DeviceBuffer<float> distances_;
+    DeviceBuffer<uint2> pruned_scratch_;
+    int pruned_grid_ = 0;
+    DeviceBuffer<SplitOpDev> split_ops_dev_;
+    DeviceBuffer<double> scalars_dev_;   // [0] wcss, [1] not-pruned total (as double), [2] shift
+    DeviceBuffer<unsigned long long> np_total_dev_;
+    PinnedBuffer<double> scalars_host_;
+    PinnedBuffer<uint32_t> counts_host_;
+    std::vector<uint32_t> sizes_host_;   // cluster_sizes after the last split
+
+    // update workspace
+    UpdateWorkspace ws_;
+    DeviceBuffer<uint32_t> ws_keys_a_, ws_keys_b_, ws_vals_a_, ws_vals_b_, ws_table_, ws_offsets_;
+    DeviceBuffer<float> ws_partials_;
+    DeviceBuffer<double> ws_block_sums_;
+
+    // hierarchical extras
+    DeviceBuffer<float> full_norms_;      // immutable_data_norms
+    DeviceBuffer<float> meso_buffer_;
+    DeviceBuffer<float> meso_norms_;
+    DeviceBuffer<uint64_t> meso_indices_dev_;
+    DeviceBuffer<uint32_t> final_assignments_;
+    DeviceBuffer<float> final_centroids_;
+
+    // sampling
+    std::vector<size_t> sampled_indices_;
+
+    std::vector<skm_iter_stats> stats_flat_, stats_meso_, stats_fine_, stats_refine_;
+};
+
+} // namespace skmb

@@ -1,0 +1,159 @@
+"""End-to-end parity of Train / Assign / AssignTrainingPoints with the compiled reference on the same
+data, seed and rotation matrix, through the C ABI (north-star gates: centroids 1e-4 relative L2,
+>= 99.9 % identical assignments, WCSS 1e-4 relative)."""
+import numpy as np
+import pytest
+
+from tests import datagen
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel_l2(a, b):
+    return float(np.linalg.norm(a.astype(np.float64) - b.astype(np.float64)) / np.linalg.norm(b.astype(np.float64)))
+
+
+def _wcss64(x, c, a):
+    return float(((x.astype(np.float64) - c[a].astype(np.float64)) ** 2).sum())
+
+
+def _pair(ref, skm, x, k, hier=False, **kw):
+    d = x.shape[1]
+    rcfg = ref.default_config(hier, **kw)
+    rk = ref.RefKMeans(k, d, rcfg, hierarchical=hier, trace=True)
+    rc = rk.train(x)
+    cfg = skm.default_config(hier, **kw)
+    e = skm.Engine(k, d, cfg, hierarchical=hier)
+    e.set_rotation(rk.rotation_matrix())
+    c = e.train(x)
+    return rk, rc, e, c
+
+
+def _check_stats(rs, es, rel=1e-4):
+    assert len(rs) == len(es)
+    for r, s in zip(rs, es):
+        assert r["iteration"] == s.iteration
+        assert r["is_gemm_only"] == bool(s.is_gemm_only)
+        assert r["partial_d"] == s.partial_d, (r, s.partial_d)
+        assert r["split"] == s.split
+        assert abs(r["objective"] - s.objective) <= rel * r["objective"]
+        if not r["is_gemm_only"]:
+            assert abs(r["not_pruned_pct"] - s.not_pruned_pct) <= 2e-3 * r["not_pruned_pct"] + 1e-7
+
+
+@pytest.mark.parametrize("n,d,k,seed", [(20000, 128, 300, 1), (8000, 64, 100, 2), (15000, 256, 256, 3)])
+def test_flat_train_gemm_only_matches_reference(ref, n, d, k, seed):
+    """use_blas_only / small k / small d: exact Lloyd iterations (superkmeans.h:276-283)."""
+    import superkmeans_b200 as skm
+
+    x = datagen.gaussian_mixture(n, d, k, 0.3, seed)
+    rk, rc, e, c = _pair(ref, skm, x, k, iters=6, sampling_fraction=1.0, early_termination=0, seed=seed, use_blas_only=1)
+    _check_stats(rk.stats(), e.stats(0))
+    assert _rel_l2(c, rc) < 1e-4
+    ra, a = rk.assignments(), e.assignments()
+    assert (ra == a).mean() >= 0.999
+    assert abs(_wcss64(x, c, a) - _wcss64(x, rc, ra)) <= 1e-4 * _wcss64(x, rc, ra)
+
+
+@pytest.mark.parametrize("n,d,k,seed", [(30000, 256, 600, 4), (20000, 768, 1100, 5), (12000, 130, 520, 6)])
+def test_flat_train_pruned_matches_reference(ref, n, d, k, seed):
+    import superkmeans_b200 as skm
+
+    x = datagen.gaussian_mixture(n, d, k, 0.3, seed)
+    rk, rc, e, c = _pair(ref, skm, x, k, iters=8, sampling_fraction=1.0, early_termination=0, seed=seed)
+    rs, es = rk.stats(), e.stats(0)
+    assert any(not r["is_gemm_only"] for r in rs)
+    _check_stats(rs, es)
+    ra, a = rk.assignments(), e.assignments()
+    agree = float((ra == a).mean())
+    w, rw = _wcss64(x, c, a), _wcss64(x, rc, ra)
+    assert abs(w - rw) <= 1e-4 * rw, (w, rw)
+    assert agree >= 0.999, agree
+    assert _rel_l2(c, rc) < 1e-4
+    # Assign (brute force, caller's domain) and AssignTrainingPoints (pruned, trained state)
+    asg, rasg = e.assign(x, c), rk.assign(x, rc)
+    assert (asg == rasg).mean() >= 0.999
+    atp, ratp = e.assign_training_points(x, c), rk.assign_training_points(x, rc)
+    assert (atp == ratp).mean() >= 0.999
+    # tests/test_assign.cpp:152-155: fast assignment agrees with brute force on >= 98 % of the points
+    assert (atp == asg).mean() >= 0.98
+
+
+def test_flat_train_sampled_and_early_termination(ref):
+    """Library defaults: sampling_fraction 0.3, max_points_per_cluster 256, early termination on."""
+    import superkmeans_b200 as skm
+
+    n, d, k = 30000, 128, 64
+    x = datagen.gaussian_mixture(n, d, k, 0.3, 8)
+    rk, rc, e, c = _pair(ref, skm, x, k, seed=8)
+    _check_stats(rk.stats(), e.stats(0))
+    assert _rel_l2(c, rc) < 1e-4
+    assert e.is_trained and e.n_clusters == k
+    with pytest.raises(RuntimeError, match="already been trained"):
+        e.train(x)
+
+
+def test_train_errors_match_reference_classes(ref):
+    import superkmeans_b200 as skm
+
+    x = datagen.gaussian_mixture(50, 32, 5, 0.3, 9)
+    e = skm.Engine(100, 32, skm.default_config(False, sampling_fraction=1.0))
+    with pytest.raises(RuntimeError, match="at least as large as the number of clusters"):
+        e.train(x)
+    e = skm.Engine(40, 32, skm.default_config(False, sampling_fraction=0.5))
+    with pytest.raises(RuntimeError, match="Not enough samples"):
+        e.train(x)
+    e = skm.Engine(10, 32)
+    with pytest.raises(RuntimeError, match="trained first"):
+        e.assign_training_points(x, x[:10])
+
+
+@pytest.mark.parametrize("n,d,k,seed", [(40000, 128, 400, 10), (30000, 256, 1024, 11)])
+def test_hierarchical_train_matches_reference(ref, n, d, k, seed):
+    import superkmeans_b200 as skm
+
+    x = datagen.gaussian_mixture(n, d, k, 0.3, seed)
+    rk, rc, e, c = _pair(ref, skm, x, k, hier=True, early_termination=0, seed=seed)
+    assert e.n_mesoclusters == rk.n_mesoclusters()
+    for phase in (1, 2, 3):
+        _check_stats(rk.stats(phase), e.stats(phase))
+    # tests/test_hierarchical_superkmeans.cpp:237-295: one stats entry per mesocluster iteration
+    assert len(e.stats(2)) == e.n_mesoclusters * 5
+    ra, a = rk.final_assignments(), e.assignments()
+    assert (ra == a).mean() >= 0.999
+    assert _rel_l2(c, rc) < 1e-4
+    asg, rasg = e.assign(x, c), rk.assign(x, rc)
+    assert (asg == rasg).mean() >= 0.999
+
+
+def test_same_seed_is_bit_reproducible():
+    # tests/test_hierarchical_superkmeans.cpp:492-528, python/tests/test_superkmeans.py:182-197
+    import superkmeans_b200 as skm
+
+    x = datagen.gaussian_mixture(20000, 256, 500, 0.3, 12)
+    outs = []
+    for _ in range(2):
+        e = skm.Engine(500, 256, skm.default_config(False, iters=5, sampling_fraction=1.0, seed=3))
+        outs.append(e.train(x))
+    np.testing.assert_array_equal(outs[0], outs[1])
+
+
+def test_python_surface():
+    # python/tests/test_superkmeans.py: shapes, dtypes, validation, auto hierarchical switch
+    import superkmeans_b200 as skm
+
+    x = datagen.gaussian_mixture(5000, 64, 20, 0.3, 13)
+    km = skm.SuperKMeans(n_clusters=20, dimensionality=64)
+    assert not km.is_trained_ and km.n_clusters_ == 20
+    c = km.train(x)
+    assert c.shape == (20, 64) and c.dtype == np.float32
+    assert km.is_trained_ and km.hierarchical_ is False
+    a = km.assign(x, c)
+    assert a.shape == (5000,) and a.dtype == np.uint32 and a.max() < 20
+    with pytest.raises(ValueError):
+        km.assign(x.astype(np.float64), c)
+    with pytest.raises(ValueError):
+        km.assign(x[:, :32], c)
+    with pytest.raises(ValueError):
+        skm.SuperKMeans(20, 64).train(x[:, :10])
+    assert len(km.iteration_stats) >= 1
