@@ -126,6 +126,26 @@ skm_status skm_get_rotated_centroids(skm_handle* h, float* out);
 /* Objective of the last iteration accumulated in float64 (the reference sums float32). */
 double skm_last_objective_f64(const skm_handle* h);
 
+/* Optional per-iteration snapshots of the training state, for step-wise comparison with another
+ * implementation: what RunIteration (superkmeans.h:786-879) leaves behind after each call.  Sizes:
+ * centroids n_clusters x d (rotated space, after the split), assign / dist n_samples, sizes_pre /
+ * sizes_post n_clusters (cluster_sizes before and after SplitClusters).  Any output may be NULL.
+ * The reference exposes this state only to subclasses (protected members). */
+skm_status skm_set_trace(skm_handle* h, int enabled);
+uint64_t skm_trace_count(const skm_handle* h);
+skm_status skm_trace_get(const skm_handle* h, uint64_t idx, uint64_t* n_samples, uint64_t* n_clusters, uint32_t* partial_d_next, float* centroids, uint32_t* assign, float* dist,
+                         uint32_t* sizes_pre, uint32_t* sizes_post);
+
+/* Device time per phase of the path, measured with CUDA events on the engine's stream and summed
+ * since creation or the last reset.  Phases follow the reference profiler's sections
+ * (include/superkmeans/profiler.h, SKM_PROFILE_SCOPE names): 0 rotator, 1 norms_calc,
+ * 2 search/1st_blas (exact assignment), 3 search (pruned assignment), 4 update_centroids,
+ * 5 consolidate, 6 shift, 7 whole Train call. */
+skm_status skm_get_phase_time(const skm_handle* h, int phase, double* ms, uint64_t* calls);
+skm_status skm_reset_phase_times(skm_handle* h);
+/* Kernels launched by this library in the calling process so far. */
+uint64_t skm_kernel_launches(void);
+
 /* Sharded training: this handle holds rows [row_offset, row_offset + n_local) of a global data set
  * of n_global rows; per-iteration sums, counts and scalars are combined through `fn`.  The
  * reference has no counterpart (single process). */

@@ -86,6 +86,13 @@ SIGNATURES = {
     "skm_get_distances": (C.c_int, [C.c_void_p, f32p, C.c_uint64]),
     "skm_get_rotated_centroids": (C.c_int, [C.c_void_p, f32p]),
     "skm_last_objective_f64": (C.c_double, [C.c_void_p]),
+    "skm_set_trace": (C.c_int, [C.c_void_p, C.c_int]),
+    "skm_trace_count": (C.c_uint64, [C.c_void_p]),
+    "skm_trace_get": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint32), C.c_void_p, C.c_void_p, C.c_void_p,
+                                C.c_void_p, C.c_void_p]),
+    "skm_get_phase_time": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
+    "skm_reset_phase_times": (C.c_int, [C.c_void_p]),
+    "skm_kernel_launches": (C.c_uint64, []),
     "skm_set_shard": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, ALLREDUCE_FN, C.c_void_p]),
     "skm_op_rotate": (C.c_int, [C.c_int, f32p, f32p, C.c_uint64, C.c_uint64, f32p]),
     "skm_op_unrotate": (C.c_int, [C.c_int, f32p, f32p, C.c_uint64, C.c_uint64, f32p]),
@@ -107,7 +114,7 @@ SIGNATURES = {
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m superkmeans_b200.build` (needs nvcc). "
+            f"{LIB_PATH} is missing: build it with `python superkmeans_b200/build.py` (needs nvcc). "
             "This package has no CPU implementation."
         )
     lib = C.CDLL(LIB_PATH)

@@ -1,4 +1,4 @@
-"""Builds libskm_b200.so in-tree with nvcc for sm_100a.  Run as `python -m superkmeans_b200.build`."""
+"""Builds libskm_b200.so in-tree with nvcc for sm_100a.  Run as `python superkmeans_b200/build.py` (by path: importing the package needs the library)."""
 from __future__ import annotations
 
 import os

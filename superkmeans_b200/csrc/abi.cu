@@ -153,6 +153,47 @@ skm_status skm_get_rotated_centroids(skm_handle* h, float* out) {
     return guarded(h->err, [&] { h->engine->get_rotated_centroids(out); });
 }
 
+skm_status skm_get_phase_time(const skm_handle* h, int phase, double* ms, uint64_t* calls) {
+    SKM_NEED(h);
+    if (phase < 0 || phase >= skmb::PH_COUNT) return SKM_INVALID_ARGUMENT;
+    if (ms) *ms = h->engine->timers().ms[phase];
+    if (calls) *calls = h->engine->timers().calls[phase];
+    return SKM_OK;
+}
+
+skm_status skm_reset_phase_times(skm_handle* h) {
+    SKM_NEED(h);
+    h->engine->reset_timers();
+    return SKM_OK;
+}
+
+skm_status skm_set_trace(skm_handle* h, int enabled) {
+    SKM_NEED(h);
+    h->engine->set_trace(enabled != 0);
+    return SKM_OK;
+}
+
+uint64_t skm_trace_count(const skm_handle* h) { return (h && h->engine) ? h->engine->trace().size() : 0; }
+
+skm_status skm_trace_get(const skm_handle* h, uint64_t idx, uint64_t* n_samples, uint64_t* n_clusters, uint32_t* partial_d_next, float* centroids, uint32_t* assign, float* dist,
+                         uint32_t* sizes_pre, uint32_t* sizes_post) {
+    SKM_NEED(h);
+    const auto& tr = h->engine->trace();
+    if (idx >= tr.size()) return SKM_INVALID_ARGUMENT;
+    const auto& s = tr[idx];
+    if (n_samples) *n_samples = s.n_samples;
+    if (n_clusters) *n_clusters = s.n_clusters;
+    if (partial_d_next) *partial_d_next = s.partial_d_next;
+    if (centroids) std::memcpy(centroids, s.centroids.data(), sizeof(float) * s.centroids.size());
+    if (assign) std::memcpy(assign, s.assign.data(), sizeof(uint32_t) * s.assign.size());
+    if (dist) std::memcpy(dist, s.dist.data(), sizeof(float) * s.dist.size());
+    if (sizes_pre) std::memcpy(sizes_pre, s.sizes_pre.data(), sizeof(uint32_t) * s.sizes_pre.size());
+    if (sizes_post) std::memcpy(sizes_post, s.sizes_post.data(), sizeof(uint32_t) * s.sizes_post.size());
+    return SKM_OK;
+}
+
+uint64_t skm_kernel_launches(void) { return skmb::kernel_launch_count(); }
+
 skm_status skm_set_shard(skm_handle* h, uint64_t n_global, uint64_t row_offset, skm_allreduce_fn fn, void* user) {
     SKM_NEED(h);
     return guarded(h->err, [&] { h->engine->set_shard(n_global, row_offset, fn, user); });

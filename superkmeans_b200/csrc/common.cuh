@@ -22,6 +22,9 @@ inline void cuda_check(cudaError_t e, const char* what, const char* file, int li
 }
 #define SKM_CUDA(x) ::skmb::cuda_check((x), #x, __FILE__, __LINE__)
 
+unsigned long long kernel_launch_count();
+void note_kernel_launch();
+
 constexpr int kTileM = 128;        // points per CTA tile
 constexpr int kTileN = 128;        // centroids per GEMM sub-tile (SIMT path)
 constexpr int kChunk = 1024;       // centroids per pruning chunk (reference VECTOR_CHUNK_SIZE)

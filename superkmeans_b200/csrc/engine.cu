@@ -49,6 +49,66 @@ int resolve_device(int device) {
 } // namespace
 
 // -------------------------------------------------------------------------------------------------
+// Phase timers
+// -------------------------------------------------------------------------------------------------
+PhaseTimers::~PhaseTimers() {
+    for (auto& p : pending_) {
+        cudaEventDestroy(p.a);
+        cudaEventDestroy(p.b);
+    }
+    for (auto& p : open_) {
+        cudaEventDestroy(p.a);
+        cudaEventDestroy(p.b);
+    }
+    for (auto e : pool_) cudaEventDestroy(e);
+}
+
+cudaEvent_t PhaseTimers::get() {
+    if (!pool_.empty()) {
+        cudaEvent_t e = pool_.back();
+        pool_.pop_back();
+        return e;
+    }
+    cudaEvent_t e;
+    SKM_CUDA(cudaEventCreate(&e));
+    return e;
+}
+
+void PhaseTimers::begin(int phase, cudaStream_t s) {
+    Pending p{phase, get(), get()};
+    SKM_CUDA(cudaEventRecord(p.a, s));
+    open_.push_back(p);
+}
+
+void PhaseTimers::end(cudaStream_t s) {
+    if (open_.empty()) return;
+    Pending p = open_.back();
+    open_.pop_back();
+    cudaEventRecord(p.b, s);
+    pending_.push_back(p);
+}
+
+void PhaseTimers::flush() {
+    for (auto& p : pending_) {
+        float t = 0.f;
+        if (cudaEventElapsedTime(&t, p.a, p.b) == cudaSuccess) {
+            ms[p.phase] += t;
+            calls[p.phase] += 1;
+        }
+        pool_.push_back(p.a);
+        pool_.push_back(p.b);
+    }
+    pending_.clear();
+}
+
+void PhaseTimers::reset() {
+    for (int i = 0; i < PH_COUNT; ++i) {
+        ms[i] = 0.0;
+        calls[i] = 0;
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
 // Construction (superkmeans.h:123-140, hierarchical_superkmeans.h:43-66)
 // -------------------------------------------------------------------------------------------------
 Engine::Engine(const skm_config& cfg, size_t n_clusters, size_t d, bool hierarchical, int device)
@@ -152,9 +212,11 @@ void Engine::rotate_to_device(const float* src, bool src_on_device, size_t n, fl
     if (n == 0) return;
     ensure_rotation();
     if (src_on_device) {
+        PhaseScope ps(*this, PH_ROTATE);
         launch_gemm_nt(src, d_, m_dev_.get(), d_, dst, d_, n, d_, d_, stream_);
         return;
     }
+    PhaseScope ps_total(*this, PH_ROTATE);
     const size_t rows = chunk_rows_for(d_, n);
     DeviceBuffer<float> raw[2];
     raw[0].ensure(rows * d_);
@@ -317,17 +379,23 @@ void Engine::run_iteration(bool gemm_only, const IterationInput& in, size_t iter
     float* norms = in.norms;
     if (gemm_only) {
         launch_row_sqnorms(c_prev_.get(), k_cur, d_, d_, centroid_norms_.get(), stream_);
+        PhaseScope ps(*this, PH_ASSIGN_FULL);
         launch_assign_full(in.x, c_prev_.get(), n, k_cur, d_, norms, centroid_norms_.get(), assignments_.get(), distances_.get(), stream_);
     } else {
         launch_row_sqnorms(c_prev_.get(), k_cur, d_, partial_d_, centroid_norms_.get(), stream_);
+        PhaseScope ps(*this, PH_ASSIGN_PRUNED);
         run_pruned_pass(in.x, n, k_cur, c_prev_.get(), norms, centroid_norms_.get(), assignments_.get(), distances_.get(), not_pruned_.get());
     }
     // UpdateCentroids + ComputeCost (superkmeans.h:729-765, :973-981)
-    launch_update(in.x, assignments_.get(), distances_.get(), gemm_only ? nullptr : not_pruned_.get(), n, k_cur, d_, ws_, c_cur_.get(), counts_.get(), scalars_dev_.get(),
-                  gemm_only ? nullptr : np_total_dev_.get(), stream_);
-    if (!gemm_only) {
-        u64_to_f64_kernel<<<1, 1, 0, stream_>>>(np_total_dev_.get(), scalars_dev_.get() + 1);
-        SKM_CUDA(cudaGetLastError());
+    {
+        PhaseScope ps(*this, PH_UPDATE);
+        launch_update(in.x, assignments_.get(), distances_.get(), gemm_only ? nullptr : not_pruned_.get(), n, k_cur, d_, ws_, c_cur_.get(), counts_.get(), scalars_dev_.get(),
+                      gemm_only ? nullptr : np_total_dev_.get(), stream_);
+        if (!gemm_only) {
+            u64_to_f64_kernel<<<1, 1, 0, stream_>>>(np_total_dev_.get(), scalars_dev_.get() + 1);
+            note_kernel_launch();
+            SKM_CUDA(cudaGetLastError());
+        }
     }
     if (allreduce_fn_) {
         allreduce(c_cur_.get(), k_cur * d_, 0);
@@ -346,18 +414,44 @@ void Engine::run_iteration(bool gemm_only, const IterationInput& in, size_t iter
                                             cfg_.adjustment_factor_for_partial_d);
         avg_not_pruned = t.avg_not_pruned_pct;
         partial_d_ = t.new_partial_d;
-        if (t.changed) launch_row_sqnorms(in.x, n, d_, partial_d_, norms, stream_);
+        if (t.changed) {
+            PhaseScope ps(*this, PH_NORMS);
+            launch_row_sqnorms(in.x, n, d_, partial_d_, norms, stream_);
+        }
     }
-    consolidate(in.n_samples_global, k_cur);
+    {
+        PhaseScope ps(*this, PH_CONSOLIDATE);
+        consolidate(in.n_samples_global, k_cur);
+    }
 
     prev_cost_ = cost_;
     cost_ = static_cast<float>(wcss);
     last_cost_f64_ = wcss;
     // ComputeShift (superkmeans.h:988-998)
-    launch_shift(c_cur_.get(), c_prev_.get(), k_cur, d_, ws_.block_sums, scalars_dev_.get() + 2, stream_);
+    {
+        PhaseScope ps(*this, PH_SHIFT);
+        launch_shift(c_cur_.get(), c_prev_.get(), k_cur, d_, ws_.block_sums, scalars_dev_.get() + 2, stream_);
+    }
     SKM_CUDA(cudaMemcpyAsync(scalars_host_.get() + 2, scalars_dev_.get() + 2, sizeof(double), cudaMemcpyDeviceToHost, stream_));
     sync();
     shift_ = static_cast<float>(scalars_host_.get()[2]);
+
+    if (trace_on_) {
+        Snapshot snap;
+        snap.n_samples = n;
+        snap.n_clusters = k_cur;
+        snap.partial_d_next = partial_d_;
+        snap.centroids.resize(k_cur * d_);
+        snap.assign.resize(n);
+        snap.dist.resize(n);
+        snap.sizes_pre.assign(counts_host_.get(), counts_host_.get() + k_cur);
+        snap.sizes_post.assign(sizes_host_.begin(), sizes_host_.begin() + k_cur);
+        SKM_CUDA(cudaMemcpyAsync(snap.centroids.data(), c_cur_.get(), sizeof(float) * k_cur * d_, cudaMemcpyDeviceToHost, stream_));
+        SKM_CUDA(cudaMemcpyAsync(snap.assign.data(), assignments_.get(), sizeof(uint32_t) * n, cudaMemcpyDeviceToHost, stream_));
+        SKM_CUDA(cudaMemcpyAsync(snap.dist.data(), distances_.get(), sizeof(float) * n, cudaMemcpyDeviceToHost, stream_));
+        sync();
+        trace_.push_back(std::move(snap));
+    }
 
     skm_iter_stats s{};
     s.iteration = iter_idx + 1;
@@ -405,8 +499,16 @@ void Engine::train(const float* data, size_t n, bool on_device, const float* que
     if (allreduce_fn_ && hierarchical_) {
         throw std::runtime_error("sharded training is available for the flat algorithm only");
     }
-    if (hierarchical_) train_hierarchical(data, n, on_device, centroids_out);
-    else train_flat(data, n, on_device, centroids_out);
+    timers_.begin(PH_TRAIN_TOTAL, stream_);
+    try {
+        if (hierarchical_) train_hierarchical(data, n, on_device, centroids_out);
+        else train_flat(data, n, on_device, centroids_out);
+    } catch (...) {
+        timers_.end(stream_);
+        throw;
+    }
+    timers_.end(stream_);
+    sync();
 }
 
 // Copies (and rotates unless the data is pre-rotated) the training rows into x_rot_; with sampling

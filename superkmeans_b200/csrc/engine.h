@@ -74,6 +74,32 @@ class PinnedBuffer {
     size_t cap_ = 0;
 };
 
+// Accumulating per-phase device timers (CUDA events on the engine's stream); names follow the
+// sections of the reference's profiler (profiler.h): rotator, norms_calc, search/1st_blas, search,
+// update_centroids, consolidate, shift.
+enum Phase { PH_ROTATE = 0, PH_NORMS, PH_ASSIGN_FULL, PH_ASSIGN_PRUNED, PH_UPDATE, PH_CONSOLIDATE, PH_SHIFT, PH_TRAIN_TOTAL, PH_COUNT };
+
+class PhaseTimers {
+  public:
+    ~PhaseTimers();
+    void begin(int phase, cudaStream_t s);
+    void end(cudaStream_t s);
+    void flush();  // call only after the stream has been synchronised
+    void reset();
+    double ms[PH_COUNT] = {};
+    uint64_t calls[PH_COUNT] = {};
+
+  private:
+    struct Pending {
+        int phase;
+        cudaEvent_t a, b;
+    };
+    cudaEvent_t get();
+    std::vector<Pending> pending_;
+    std::vector<Pending> open_;
+    std::vector<cudaEvent_t> pool_;
+};
+
 class Engine {
   public:
     Engine(const skm_config& cfg, size_t n_clusters, size_t d, bool hierarchical, int device);
@@ -98,6 +124,19 @@ class Engine {
     double last_objective_f64() const { return last_cost_f64_; }
     const std::vector<skm_iter_stats>& stats(int phase) const;
     int device() const { return device_; }
+    // Per-iteration snapshots for step-wise parity checks (what RunIteration leaves behind).
+    struct Snapshot {
+        uint64_t n_samples = 0, n_clusters = 0;
+        uint32_t partial_d_next = 0;
+        std::vector<float> centroids;
+        std::vector<uint32_t> assign;
+        std::vector<float> dist;
+        std::vector<uint32_t> sizes_pre, sizes_post;
+    };
+    void set_trace(bool on) { trace_on_ = on; }
+    const std::vector<Snapshot>& trace() const { return trace_; }
+    const PhaseTimers& timers() const { return timers_; }
+    void reset_timers() { timers_.reset(); }
 
     // Stateless operators (used by the skm_op_* entry points).
     static void op_rotate(int device, const float* m, const float* x, size_t n, size_t d, float* out, bool inverse);
@@ -129,7 +168,18 @@ class Engine {
     void train_hierarchical(const float* data, size_t n, bool on_device, float* centroids_out);
     void output_centroids(float* out_host);
     void allreduce(void* buf, size_t count, int dtype);
-    void sync() { SKM_CUDA(cudaStreamSynchronize(stream_)); }
+    void sync() {
+        SKM_CUDA(cudaStreamSynchronize(stream_));
+        timers_.flush();
+    }
+    struct PhaseScope {
+        Engine& e;
+        PhaseScope(Engine& eng, int phase) : e(eng) { e.timers_.begin(phase, e.stream_); }
+        ~PhaseScope() { e.timers_.end(e.stream_); }
+    };
+    PhaseTimers timers_;
+    bool trace_on_ = false;
+    std::vector<Snapshot> trace_;
 
     skm_config cfg_;
     size_t k_, d_;

@@ -9,9 +9,20 @@
 #include "common.cuh"
 #include "gemm_simt.cuh"
 
+#include <atomic>
 #include <cfloat>
 
 namespace skmb {
+
+// Number of kernels this library has launched in the process (reported by skm_kernel_launches).
+static std::atomic<unsigned long long> g_kernel_launches{0};
+unsigned long long kernel_launch_count() { return g_kernel_launches.load(); }
+void note_kernel_launch() { g_kernel_launches.fetch_add(1, std::memory_order_relaxed); }
+#define SKM_LAUNCH_CHECK()                                                                         \
+    do {                                                                                           \
+        note_kernel_launch();                                                                      \
+        SKM_CUDA(cudaGetLastError());                                                              \
+    } while (0)
 
 // =================================================================================================
 // Small helpers
@@ -64,7 +75,7 @@ void launch_row_sqnorms(const float* x, size_t n, size_t ld, size_t upto, float*
     if (n == 0) return;
     const unsigned grid = static_cast<unsigned>((n + 7) / 8);
     row_sqnorms_kernel<<<grid, 256, 0, stream>>>(x, n, ld, upto, out);
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
 }
 
 // =================================================================================================
@@ -106,7 +117,7 @@ void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, floa
     // The point dimension is on grid.x (limit 2^31-1); output columns on grid.y.
     dim3 grid(static_cast<unsigned>((n + kTileM - 1) / kTileM), static_cast<unsigned>((n_out + kTileN - 1) / kTileN));
     gemm_nt_kernel<<<grid, 256, 0, stream>>>(a, lda, b, ldb, out, ldo, n, n_out, k_dim);
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
 }
 
 __global__ void transpose_square_kernel(const float* __restrict__ in, float* __restrict__ out, size_t n) {
@@ -126,7 +137,7 @@ __global__ void transpose_square_kernel(const float* __restrict__ in, float* __r
 void launch_transpose_square(const float* in, float* out, size_t n, cudaStream_t stream) {
     dim3 grid(static_cast<unsigned>((n + 31) / 32), static_cast<unsigned>((n + 31) / 32));
     transpose_square_kernel<<<grid, dim3(32, 8), 0, stream>>>(in, out, n);
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
 }
 
 // =================================================================================================
@@ -221,7 +232,7 @@ void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size
     if (n == 0) return;
     const unsigned grid = static_cast<unsigned>((n + kTileM - 1) / kTileM);
     assign_full_kernel<<<grid, 256, 0, stream>>>(x, y, n, k, d, norms_x, norms_y, out_knn, out_dist);
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
 }
 
 // =================================================================================================
@@ -483,7 +494,7 @@ void launch_assign_pruned(const PrunedParams& p, int grid, cudaStream_t stream) 
     } else {
         assign_pruned_kernel<false><<<g, 256, 0, stream>>>(p);
     }
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
 }
 
 // =================================================================================================
@@ -595,12 +606,12 @@ static void exclusive_scan_u32(uint32_t* data, size_t n, uint32_t* totals_tmp, c
     if (n == 0) return;
     const size_t blocks = (n + 2047) / 2048;
     scan_block_kernel<<<static_cast<unsigned>(blocks), 1024, 0, stream>>>(data, n, totals_tmp);
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
     if (blocks > 1) {
         scan_totals_kernel<<<1, 1024, 0, stream>>>(totals_tmp, blocks);
-        SKM_CUDA(cudaGetLastError());
+        SKM_LAUNCH_CHECK();
         scan_add_kernel<<<static_cast<unsigned>(blocks), 1024, 0, stream>>>(data, n, totals_tmp);
-        SKM_CUDA(cudaGetLastError());
+        SKM_LAUNCH_CHECK();
     }
 }
 
@@ -852,10 +863,10 @@ void launch_update(
     for (int pass = 0; pass < passes; ++pass) {
         const int shift = pass * 8;
         sort_hist_kernel<<<unit_blocks, 256, 0, stream>>>(kin, n, shift, ws.digit_table, n_units);
-        SKM_CUDA(cudaGetLastError());
+        SKM_LAUNCH_CHECK();
         exclusive_scan_u32(ws.digit_table, 256 * n_units, scan_totals, stream);
         sort_scatter_kernel<<<unit_blocks, 256, 0, stream>>>(kin, vin, kout, vout, n, shift, ws.digit_table, n_units);
-        SKM_CUDA(cudaGetLastError());
+        SKM_LAUNCH_CHECK();
         kin = kout;
         vin = vout;
         kout = (kout == ws.keys_a) ? ws.keys_b : ws.keys_a;
@@ -864,27 +875,27 @@ void launch_update(
     const uint32_t* sorted_keys = kin;
     const uint32_t* order = vin;
     segment_offsets_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(sorted_keys, n, k, ws.seg_offsets);
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
     counts_from_offsets_kernel<<<static_cast<unsigned>((k + 255) / 256), 256, 0, stream>>>(ws.seg_offsets, k, counts);
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
     const size_t n_tiles = update_tiles(n);
     const unsigned slabs = static_cast<unsigned>((d + 1023) / 1024);
     const bool vec = (d % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
     if (vec) {
         segsum_tile_kernel<true><<<dim3(static_cast<unsigned>(n_tiles), slabs), 256, 0, stream>>>(x, sorted_keys, order, n, d, sums, ws.tile_partials);
-        SKM_CUDA(cudaGetLastError());
+        SKM_LAUNCH_CHECK();
         segsum_fix_kernel<true><<<dim3(static_cast<unsigned>(k), slabs), 256, 0, stream>>>(ws.seg_offsets, n, d, ws.tile_partials, sums);
     } else {
         segsum_tile_kernel<false><<<dim3(static_cast<unsigned>(n_tiles), slabs), 256, 0, stream>>>(x, sorted_keys, order, n, d, sums, ws.tile_partials);
-        SKM_CUDA(cudaGetLastError());
+        SKM_LAUNCH_CHECK();
         segsum_fix_kernel<false><<<dim3(static_cast<unsigned>(k), slabs), 256, 0, stream>>>(ws.seg_offsets, n, d, ws.tile_partials, sums);
     }
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
     if (wcss || not_pruned_total) {
         reduce_stats_kernel<<<kReduceBlocks, 256, 0, stream>>>(dist, not_pruned, n, ws.block_sums);
-        SKM_CUDA(cudaGetLastError());
+        SKM_LAUNCH_CHECK();
         reduce_final_kernel<<<1, 256, 0, stream>>>(ws.block_sums, kReduceBlocks, wcss, not_pruned ? not_pruned_total : nullptr);
-        SKM_CUDA(cudaGetLastError());
+        SKM_LAUNCH_CHECK();
     }
 }
 
@@ -903,7 +914,7 @@ __global__ void scale_by_counts_kernel(float* __restrict__ c, const uint32_t* __
 void launch_scale_by_counts(float* c, const uint32_t* counts, size_t k, size_t d, cudaStream_t stream) {
     if (k == 0) return;
     scale_by_counts_kernel<<<static_cast<unsigned>(k), 256, 0, stream>>>(c, counts, k, d);
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
 }
 
 // Every thread owns one dimension and replays the row operations in list order.
@@ -935,7 +946,7 @@ __global__ void apply_split_ops_kernel(float* __restrict__ c, size_t d, const Sp
 void launch_apply_split_ops(float* c, size_t d, const SplitOpDev* ops, size_t n_ops, cudaStream_t stream) {
     if (n_ops == 0) return;
     apply_split_ops_kernel<<<static_cast<unsigned>((d + 127) / 128), 128, 0, stream>>>(c, d, ops, n_ops);
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
 }
 
 // Spherical k-means post-processing (superkmeans.h:1357-1371): sequential-sum norm per row.
@@ -954,7 +965,7 @@ __global__ void normalize_rows_kernel(float* __restrict__ c, size_t k, size_t d)
 void launch_normalize_rows(float* c, size_t k, size_t d, cudaStream_t stream) {
     if (k == 0) return;
     normalize_rows_kernel<<<static_cast<unsigned>((k + 7) / 8), 256, 0, stream>>>(c, k, d);
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
 }
 
 __global__ void pdxify_kernel(const float* __restrict__ c, float* __restrict__ pdx, float* __restrict__ aux, size_t k, size_t d, size_t vertical_d) {
@@ -980,7 +991,7 @@ __global__ void pdxify_kernel(const float* __restrict__ c, float* __restrict__ p
 void launch_pdxify(const float* c, float* pdx, float* aux, size_t k, size_t d, size_t vertical_d, cudaStream_t stream) {
     if (k == 0) return;
     pdxify_kernel<<<static_cast<unsigned>(k), 256, 0, stream>>>(c, pdx, aux, k, d, vertical_d);
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
 }
 
 __global__ void __launch_bounds__(256) shift_kernel(const float* __restrict__ a, const float* __restrict__ b, size_t k, size_t d, double* __restrict__ block_sums) {
@@ -1010,9 +1021,9 @@ __global__ void __launch_bounds__(256) shift_kernel(const float* __restrict__ a,
 void launch_shift(const float* a, const float* b, size_t k, size_t d, double* block_sums, double* out, cudaStream_t stream) {
     const int blocks = static_cast<int>(min(static_cast<size_t>(kReduceBlocks), (k + 7) / 8));
     shift_kernel<<<blocks, 256, 0, stream>>>(a, b, k, d, block_sums);
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
     reduce_final_kernel<<<1, 256, 0, stream>>>(block_sums, blocks, out, nullptr);
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
 }
 
 // =================================================================================================
@@ -1028,7 +1039,7 @@ __global__ void gather_rows_kernel(const float* __restrict__ in, const uint64_t*
 void launch_gather_rows(const float* in, const uint64_t* idx, float* out, size_t n_out, size_t d, cudaStream_t stream) {
     if (n_out == 0) return;
     gather_rows_kernel<<<static_cast<unsigned>(n_out), 256, 0, stream>>>(in, idx, out, n_out, d);
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
 }
 
 __global__ void gather_f32_kernel(const float* __restrict__ in, const uint64_t* __restrict__ idx, float* __restrict__ out, size_t n_out) {
@@ -1039,7 +1050,7 @@ __global__ void gather_f32_kernel(const float* __restrict__ in, const uint64_t* 
 void launch_gather_f32(const float* in, const uint64_t* idx, float* out, size_t n_out, cudaStream_t stream) {
     if (n_out == 0) return;
     gather_f32_kernel<<<static_cast<unsigned>((n_out + 255) / 256), 256, 0, stream>>>(in, idx, out, n_out);
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
 }
 
 __global__ void scatter_u32_offset_kernel(const uint32_t* __restrict__ in, const uint64_t* __restrict__ idx, uint32_t* __restrict__ out, size_t n, uint32_t offset) {
@@ -1050,7 +1061,7 @@ __global__ void scatter_u32_offset_kernel(const uint32_t* __restrict__ in, const
 void launch_scatter_u32_offset(const uint32_t* in, const uint64_t* idx, uint32_t* out, size_t n, uint32_t offset, cudaStream_t stream) {
     if (n == 0) return;
     scatter_u32_offset_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(in, idx, out, n, offset);
-    SKM_CUDA(cudaGetLastError());
+    SKM_LAUNCH_CHECK();
 }
 
 } // namespace skmb

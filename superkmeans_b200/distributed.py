@@ -1,0 +1,56 @@
+"""Sharded training: one process per GPU, rows split evenly, one sum all-reduce per iteration.
+
+`torch.distributed` is used for the plumbing only (process group, NCCL over NVLink).  The engine
+calls back into `make_allreduce(...)`'s closure with a raw buffer pointer; the closure wraps it
+zero-copy in a tensor and runs `dist.all_reduce`.  With the gloo backend the same closure works on
+host buffers, which is how the protocol is tested without GPUs.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Callable, Tuple
+
+import numpy as np
+
+_DTYPES = {0: ("<f4", np.float32, 4), 1: ("<f8", np.float64, 8), 2: ("<i4", np.int32, 4)}
+
+
+def shard_bounds(n: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous, even split of [0, n): the first n % world ranks hold one extra row."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError("rank/world out of range")
+    base, extra = divmod(n, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+class _CudaView:
+    def __init__(self, ptr: int, count: int, typestr: str):
+        self.__cuda_array_interface__ = {"shape": (count,), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+def make_allreduce(device, group=None) -> Callable[[int, int, int], None]:
+    """Returns fn(ptr, count, dtype) that sums the buffer across the process group in place."""
+    import torch
+    import torch.distributed as dist
+
+    dev = torch.device(device)
+
+    def fn(ptr: int, count: int, dtype: int) -> None:
+        typestr, np_dtype, size = _DTYPES[dtype]
+        if dev.type == "cuda":
+            t = torch.as_tensor(_CudaView(ptr, count, typestr), device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+            torch.cuda.synchronize(dev)
+        else:
+            buf = (C.c_char * (count * size)).from_address(ptr)
+            t = torch.from_numpy(np.frombuffer(buf, dtype=np_dtype))
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+
+    return fn
+
+
+def train_sharded(engine, local_rows, n_local: int, n_global: int, row_offset: int, device, on_device: bool = True, group=None):
+    """Trains `engine` on this rank's rows; every rank returns the same centroids."""
+    engine.set_shard(n_global, row_offset, make_allreduce(device, group))
+    return engine.train(local_rows, n=n_local, on_device=on_device)

@@ -134,6 +134,38 @@ class Engine:
     def last_objective_f64(self) -> float:
         return float(lib.skm_last_objective_f64(self._h))
 
+    def set_trace(self, enabled: bool = True):
+        check(lib.skm_set_trace(self._h, int(enabled)), self._h)
+
+    def trace(self) -> list:
+        """Per-iteration snapshots as dicts (see skm_trace_get)."""
+        out = []
+        for i in range(int(lib.skm_trace_count(self._h))):
+            ns, nc, pd = C.c_uint64(), C.c_uint64(), C.c_uint32()
+            check(lib.skm_trace_get(self._h, i, C.byref(ns), C.byref(nc), C.byref(pd), None, None, None, None, None), self._h)
+            cen = np.empty((nc.value, self.d), dtype=np.float32)
+            asg = np.empty(ns.value, dtype=np.uint32)
+            dst = np.empty(ns.value, dtype=np.float32)
+            s0 = np.empty(nc.value, dtype=np.uint32)
+            s1 = np.empty(nc.value, dtype=np.uint32)
+            check(lib.skm_trace_get(self._h, i, None, None, None, cen.ctypes.data, asg.ctypes.data, dst.ctypes.data, s0.ctypes.data, s1.ctypes.data), self._h)
+            out.append(dict(n_samples=ns.value, n_clusters=nc.value, partial_d_next=pd.value, centroids=cen, assign=asg, dist=dst, sizes_pre=s0, sizes_post=s1))
+        return out
+
+    PHASES = ("rotator", "norms_calc", "search/1st_blas", "search", "update_centroids", "consolidate", "shift", "train")
+
+    def phase_times(self) -> dict:
+        """{phase name: (device milliseconds, calls)} accumulated since creation / reset."""
+        out = {}
+        for i, name in enumerate(self.PHASES):
+            ms, calls = C.c_double(), C.c_uint64()
+            check(lib.skm_get_phase_time(self._h, i, C.byref(ms), C.byref(calls)), self._h)
+            out[name] = (ms.value, int(calls.value))
+        return out
+
+    def reset_phase_times(self):
+        check(lib.skm_reset_phase_times(self._h), self._h)
+
     def stats(self, phase: int = 0) -> List[IterStats]:
         cnt = C.c_uint64()
         check(lib.skm_get_iteration_stats(self._h, phase, None, 0, C.byref(cnt)), self._h)
@@ -157,6 +189,10 @@ class Engine:
         out = np.empty((self.k, self.d), dtype=np.float32)
         check(lib.skm_get_rotated_centroids(self._h, out), self._h)
         return out
+
+
+def kernel_launches() -> int:
+    return int(lib.skm_kernel_launches())
 
 
 # ---- stateless operators (host arrays in, host arrays out) ------------------------------------
