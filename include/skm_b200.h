@@ -143,6 +143,11 @@ skm_status skm_trace_get(const skm_handle* h, uint64_t idx, uint64_t* n_samples,
  * 5 consolidate, 6 shift, 7 whole Train call. */
 skm_status skm_get_phase_time(const skm_handle* h, int phase, double* ms, uint64_t* calls);
 skm_status skm_reset_phase_times(skm_handle* h);
+/* Process-wide choice between the tcgen05 tensor-core kernels (1, default) and the fp32 SIMT kernels
+ * (0) for the dense products; both give fp32-accurate results.  Meant for profiling and A/B checks.
+ * No counterpart in the reference (it delegates to whatever BLAS is linked). */
+void skm_set_tensor_cores(int enabled);
+int skm_get_tensor_cores(void);
 /* Kernels launched by this library in the calling process so far. */
 uint64_t skm_kernel_launches(void);
 

@@ -6,6 +6,7 @@
 #include <string>
 
 #include "engine.h"
+#include "kernels_tc.cuh"
 
 using skmb::Engine;
 
@@ -191,6 +192,9 @@ skm_status skm_trace_get(const skm_handle* h, uint64_t idx, uint64_t* n_samples,
     if (sizes_post) std::memcpy(sizes_post, s.sizes_post.data(), sizeof(uint32_t) * s.sizes_post.size());
     return SKM_OK;
 }
+
+void skm_set_tensor_cores(int enabled) { skmb::tc::set_enabled(enabled != 0); }
+int skm_get_tensor_cores(void) { return skmb::tc::enabled() ? 1 : 0; }
 
 uint64_t skm_kernel_launches(void) { return skmb::kernel_launch_count(); }
 

@@ -47,7 +47,9 @@ void launch_transpose_square(const float* in, float* out, size_t n, cudaStream_t
 
 // Exact nearest centroid: dist = ||x||^2 + ||y||^2 - 2 x.y over all d dims, first minimum inside a
 // 1024-centroid batch, strict < across batches, clamped at 0 when stored.
-void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist, cudaStream_t stream);
+// top2_scratch (n entries, may be null) enables the tensor-core path: tcgen05 pass for the two best
+// candidates per row, then an fp32 refinement; without it the fp32 SIMT kernel runs.
+void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist, uint2* top2_scratch, cudaStream_t stream);
 
 struct PrunedParams {
     const float* x;             // n x d rotated points

@@ -1,6 +1,7 @@
 // Host orchestration: see engine.h.  Every step cites the reference code it reproduces
 // (paths relative to the SuperKMeans repository, include/superkmeans/...).
 #include "engine.h"
+#include "kernels_tc.cuh"
 
 #include <algorithm>
 #include <cmath>
@@ -37,6 +38,11 @@ size_t chunk_rows_for(size_t d, size_t n) {
 
 void ensure_positive(bool ok, const char* name) {
     if (!ok) throw std::invalid_argument(std::string("Value must be positive: ") + name);
+}
+
+void check_tc_error(cudaStream_t stream) {
+    const int code = tc::fetch_error(stream);
+    if (code != 0) throw CudaError("a tensor-core kernel gave up waiting on a barrier (code " + std::to_string(code) + ")");
 }
 
 int resolve_device(int device) {
@@ -380,7 +386,7 @@ void Engine::run_iteration(bool gemm_only, const IterationInput& in, size_t iter
     if (gemm_only) {
         launch_row_sqnorms(c_prev_.get(), k_cur, d_, d_, centroid_norms_.get(), stream_);
         PhaseScope ps(*this, PH_ASSIGN_FULL);
-        launch_assign_full(in.x, c_prev_.get(), n, k_cur, d_, norms, centroid_norms_.get(), assignments_.get(), distances_.get(), stream_);
+        launch_assign_full(in.x, c_prev_.get(), n, k_cur, d_, norms, centroid_norms_.get(), assignments_.get(), distances_.get(), top2_.ensure(n), stream_);
     } else {
         launch_row_sqnorms(c_prev_.get(), k_cur, d_, partial_d_, centroid_norms_.get(), stream_);
         PhaseScope ps(*this, PH_ASSIGN_PRUNED);
@@ -405,6 +411,7 @@ void Engine::run_iteration(bool gemm_only, const IterationInput& in, size_t iter
     SKM_CUDA(cudaMemcpyAsync(counts_host_.ensure(k_), counts_.get(), sizeof(uint32_t) * k_cur, cudaMemcpyDeviceToHost, stream_));
     SKM_CUDA(cudaMemcpyAsync(scalars_host_.get(), scalars_dev_.get(), sizeof(double) * 2, cudaMemcpyDeviceToHost, stream_));
     sync();
+    check_tc_error(stream_);
     const double wcss = scalars_host_.get()[0];
 
     float avg_not_pruned = -1.0f;
@@ -541,6 +548,7 @@ void Engine::train_flat(const float* data, size_t n, bool on_device, float* cent
     not_pruned_.ensure(n_samples_);
     data_norms_.ensure(n_samples_);
     x_rot_.ensure(n_samples_ * d_);
+    SKM_CUDA(cudaMemsetAsync(assignments_.get(), 0, sizeof(uint32_t) * n_samples_, stream_));
     prepare_update_workspace(n_samples_, k_);
 
     // GenerateCentroids picks among the first n_samples rows of the caller's data (:221-222).
@@ -595,6 +603,7 @@ void Engine::train_flat(const float* data, size_t n, bool on_device, float* cent
     }
     trained_ = true;
     output_centroids(centroids_out);
+    check_tc_error(stream_);
     x_rot_.release();
     ws_partials_.release();
 }
@@ -646,6 +655,7 @@ void Engine::train_hierarchical(const float* data, size_t n, bool on_device, flo
     final_assignments_.ensure(n_all);
     final_centroids_.ensure(k_ * d_);
     x_rot_.ensure(n_all * d_);
+    SKM_CUDA(cudaMemsetAsync(assignments_.get(), 0, sizeof(uint32_t) * n, stream_));
     prepare_update_workspace(n_all, k_);
 
     // ---- phase 1: mesoclustering (:161-257)
@@ -809,8 +819,9 @@ void Engine::assign(const float* vectors, const float* centroids, size_t n, size
     if (on_device) {
         DeviceBuffer<float> xn, dist;
         launch_row_sqnorms(vectors, n, d_, d_, xn.ensure(n), stream_);
-        launch_assign_full(vectors, c_dev, n, n_centroids, d_, xn.get(), cn.get(), out, dist.ensure(n), stream_);
+        launch_assign_full(vectors, c_dev, n, n_centroids, d_, xn.get(), cn.get(), out, dist.ensure(n), top2_.ensure(n), stream_);
         sync();
+        check_tc_error(stream_);
         return;
     }
     const size_t rows = chunk_rows_for(d_, n);
@@ -834,7 +845,7 @@ void Engine::assign(const float* vectors, const float* centroids, size_t n, size
         SKM_CUDA(cudaEventRecord(copied[b], copy_stream_));
         SKM_CUDA(cudaStreamWaitEvent(stream_, copied[b], 0));
         launch_row_sqnorms(xb[b].get(), cnt, d_, d_, xn[b].get(), stream_);
-        launch_assign_full(xb[b].get(), c_dev, cnt, n_centroids, d_, xn[b].get(), cn.get(), knn[b].get(), dist[b].get(), stream_);
+        launch_assign_full(xb[b].get(), c_dev, cnt, n_centroids, d_, xn[b].get(), cn.get(), knn[b].get(), dist[b].get(), top2_.ensure(rows), stream_);
         SKM_CUDA(cudaMemcpyAsync(out + r0, knn[b].get(), sizeof(uint32_t) * cnt, cudaMemcpyDeviceToHost, stream_));
         SKM_CUDA(cudaEventRecord(consumed[b], stream_));
     }
@@ -843,6 +854,7 @@ void Engine::assign(const float* vectors, const float* centroids, size_t n, size
         cudaEventDestroy(copied[i]);
         cudaEventDestroy(consumed[i]);
     }
+    check_tc_error(stream_);
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -1004,6 +1016,7 @@ void Engine::op_rotate(int device, const float* m, const float* x, size_t n, siz
     launch_gemm_nt(xd.get(), d, b, d, od.ensure(n * d), d, n, d, d, ctx.stream);
     ctx.download(out, od.get(), n * d);
     ctx.sync();
+    check_tc_error(ctx.stream);
 }
 
 void Engine::op_find_nearest(int device, const float* x, const float* y, size_t n, size_t k, size_t d, uint32_t* out_knn, float* out_dist) {
@@ -1014,10 +1027,12 @@ void Engine::op_find_nearest(int device, const float* x, const float* y, size_t 
     ctx.upload(yd, y, k * d);
     launch_row_sqnorms(xd.get(), n, d, d, nx.ensure(n), ctx.stream);
     launch_row_sqnorms(yd.get(), k, d, d, ny.ensure(k), ctx.stream);
-    launch_assign_full(xd.get(), yd.get(), n, k, d, nx.get(), ny.get(), knn.ensure(n), dist.ensure(n), ctx.stream);
+    DeviceBuffer<uint2> top2;
+    launch_assign_full(xd.get(), yd.get(), n, k, d, nx.get(), ny.get(), knn.ensure(n), dist.ensure(n), top2.ensure(n), ctx.stream);
     ctx.download(out_knn, knn.get(), n);
     ctx.download(out_dist, dist.get(), n);
     ctx.sync();
+    check_tc_error(ctx.stream);
 }
 
 void Engine::op_find_nearest_pruned(int device, const float* x, const float* y, size_t n, size_t k, size_t d, float eps0, uint32_t partial_d, uint32_t* knn_io, float* dist_out,

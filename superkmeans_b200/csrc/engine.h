@@ -217,6 +217,7 @@ class Engine {
     DeviceBuffer<uint32_t> assignments_, not_pruned_;
     DeviceBuffer<float> distances_;
     DeviceBuffer<uint2> pruned_scratch_;
+    DeviceBuffer<uint2> top2_;           // candidate pairs of the tensor-core exact assignment
     int pruned_grid_ = 0;
     DeviceBuffer<SplitOpDev> split_ops_dev_;
     DeviceBuffer<double> scalars_dev_;   // [0] wcss, [1] not-pruned total (as double), [2] shift

@@ -8,6 +8,7 @@
 //   consolidation               scale / split ops / pdxify / shift (superkmeans.h:936-998, layout.h:155-232)
 #include "common.cuh"
 #include "gemm_simt.cuh"
+#include "kernels_tc.cuh"
 
 #include <atomic>
 #include <cfloat>
@@ -114,6 +115,9 @@ __global__ void __launch_bounds__(256, 2) gemm_nt_kernel(
 
 void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, float* out, size_t ldo, size_t n, size_t n_out, size_t k_dim, cudaStream_t stream) {
     if (n == 0 || n_out == 0) return;
+    // The tensor-core store variant (tc::launch_gemm_nt) is not used here: its accumulator truncates, and
+    // a 1e-5 relative error in the rotated data would shift every later distance.  Rotation is 2*n*d^2
+    // flops, a small share of the assignment work, and runs on the fp32 kernel.
     // The point dimension is on grid.x (limit 2^31-1); output columns on grid.y.
     dim3 grid(static_cast<unsigned>((n + kTileM - 1) / kTileM), static_cast<unsigned>((n_out + kTileN - 1) / kTileN));
     gemm_nt_kernel<<<grid, 256, 0, stream>>>(a, lda, b, ldb, out, ldo, n, n_out, k_dim);
@@ -228,8 +232,12 @@ __global__ void __launch_bounds__(256, 2) assign_full_kernel(
     }
 }
 
-void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist, cudaStream_t stream) {
+void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist, uint2* top2_scratch, cudaStream_t stream) {
     if (n == 0) return;
+    if (top2_scratch && tc::eligible(x, d, y, d)) {
+        tc::launch_assign_full(x, y, n, k, d, norms_x, norms_y, out_knn, out_dist, top2_scratch, stream);
+        return;
+    }
     const unsigned grid = static_cast<unsigned>((n + kTileM - 1) / kTileM);
     assign_full_kernel<<<grid, 256, 0, stream>>>(x, y, n, k, d, norms_x, norms_y, out_knn, out_dist);
     SKM_LAUNCH_CHECK();

@@ -1,0 +1,567 @@
+// Tensor-core (tcgen05) GEMM kernels for sm_100a: X * Y^T with fp32 operands and fp32-level accuracy.
+//
+// Every fp32 operand value v is split in shared memory into hi = tf32(v) and lo = tf32(v - hi); the
+// product is accumulated as hi*hi + hi*lo + lo*hi (three kind::tf32 MMAs per k-step, fp32
+// accumulation in tensor memory), which restores fp32-level accuracy of the dot products.
+//
+// One persistent CTA per SM, 320 threads in four roles:
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of a 128 x 16 tile of X and a 256 x 16 tile of
+//               Y (64-byte swizzle) into a 4-stage ring;
+//   warp 1      MMA issuer: tcgen05.mma (M = 128, N = 256, K = 8) into one of two 256-column
+//               accumulators in tensor memory, tcgen05.commit to release stages / publish tiles;
+//   warps 2-5   splitters: rewrite each landed tile in place as its hi part and write the lo part
+//               beside it (element-wise, so the swizzle pattern never has to be decoded);
+//   warps 6-9   epilogue: tcgen05.ld, one thread per row.  Two epilogues: running arg-min of
+//               ||x||^2 + ||y||^2 - 2 x.y (exact assignment) and a plain store (rotation).
+// Rows / columns / k beyond the matrix edges are zero-filled by TMA, so any n, k and K work as long as
+// the row pitch is a multiple of 16 bytes.
+//
+// Every wait on an mbarrier is bounded: on expiry the kernel records an error code, all roles leave
+// their loops, tensor memory is released and the kernel returns.
+#include <cuda.h>
+
+#include <cfloat>
+#include <mutex>
+
+#include "common.cuh"
+#include "kernels_tc.cuh"
+
+namespace skmb {
+namespace tc {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 16;
+constexpr int STAGES = 4;
+constexpr int NUM_THREADS = 320;
+constexpr uint32_t A_TILE_BYTES = BM * BK * 4;   // 8192
+constexpr uint32_t B_TILE_BYTES = BN * BK * 4;   // 16384
+constexpr uint32_t STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;  // 49152
+constexpr uint32_t OFF_A_HI = 0, OFF_A_LO = A_TILE_BYTES, OFF_B_HI = 2 * A_TILE_BYTES, OFF_B_LO = 2 * A_TILE_BYTES + B_TILE_BYTES;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t SMEM_CTRL_BYTES = 9216;
+constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + 1024;  // + alignment slack
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
+
+// kind::tf32, fp32 accumulate, K-major A and B, N = 256, M = 128
+constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
+
+struct Ctrl {
+    uint64_t full[STAGES];
+    uint64_t conv[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    uint32_t pad;
+    float ny[4][2][BN];  // per epilogue warp, per accumulator buffer
+};
+static_assert(sizeof(Ctrl) <= SMEM_CTRL_BYTES, "control block too large");
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (after recording `code`) when the limit expires or another role has
+// already failed.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            atomicCAS(err, 0, code);
+            return false;
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* tmap, uint64_t* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_dst),
+                 "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile of 64-byte rows, 64-byte swizzle, 8-row groups 512
+// bytes apart (version 1 = Blackwell).
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFF);
+    d |= static_cast<uint64_t>(1) << 16;            // leading byte offset (unused with swizzle)
+    d |= static_cast<uint64_t>(512 >> 4) << 32;     // stride byte offset between 8-row groups
+    d |= static_cast<uint64_t>(1) << 46;            // descriptor version
+    d |= static_cast<uint64_t>(4) << 61;            // SWIZZLE_64B
+    return d;
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, "
+        "%25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
+          "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+__device__ __forceinline__ void split4(float4 v, float4& hi, float4& lo) {
+    hi.x = to_tf32(v.x); hi.y = to_tf32(v.y); hi.z = to_tf32(v.z); hi.w = to_tf32(v.w);
+    lo.x = to_tf32(v.x - hi.x); lo.y = to_tf32(v.y - hi.y); lo.z = to_tf32(v.z - hi.z); lo.w = to_tf32(v.w - hi.w);
+}
+
+struct Params {
+    size_t n;         // rows of X
+    size_t k;         // rows of Y
+    uint32_t kdim;    // reduction length
+    // arg-min epilogue
+    const float* norms_x;
+    const float* norms_y;
+    uint32_t* out_knn;
+    float* out_dist;
+    uint2* out_top2;  // per row: the two best candidate indices found by the tensor-core pass
+    // store epilogue
+    float* out;
+    size_t ldo;
+    int* error;
+};
+
+enum { MODE_ARGMIN = 0, MODE_STORE = 1 };
+
+template <int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t* smem = smem_raw + pad;
+    const uint32_t smem_base = raw_addr + pad;
+    Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + STAGES * STAGE_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&ctrl->full[s], 1);
+            mbar_init(&ctrl->conv[s], 128);
+            mbar_init(&ctrl->empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&ctrl->tmem_full[b], 1);
+            mbar_init(&ctrl->tmem_empty[b], 128);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_proxy_async();
+    }
+    if (warp == 1) tmem_alloc(&ctrl->tmem_base, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctrl->tmem_base;
+
+    const size_t n_row_tiles = (p.n + BM - 1) / BM;
+    const uint32_t n_col_tiles = static_cast<uint32_t>((p.k + BN - 1) / BN);
+    const uint32_t nkb = (p.kdim + BK - 1) / BK;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            uint32_t kbt = 0;
+            bool ok = true;
+            for (size_t rt = blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {
+                for (uint32_t nt = 0; nt < n_col_tiles && ok; ++nt) {
+                    for (uint32_t kb = 0; kb < nkb; ++kb, ++kbt) {
+                        const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
+                        if (!mbar_wait(&ctrl->empty[s], ph ^ 1u, p.error, 1)) {
+                            ok = false;
+                            break;
+                        }
+                        mbar_arrive_expect_tx(&ctrl->full[s], A_TILE_BYTES + B_TILE_BYTES);
+                        const uint32_t st = smem_base + s * STAGE_BYTES;
+                        tma_load_2d(st + OFF_A_HI, &tmap_x, &ctrl->full[s], static_cast<int>(kb * BK), static_cast<int>(rt * BM));
+                        tma_load_2d(st + OFF_B_HI, &tmap_y, &ctrl->full[s], static_cast<int>(kb * BK), static_cast<int>(nt * BN));
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            uint32_t kbt = 0, t = 0;
+            bool ok = true;
+            for (size_t rt = blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {
+                for (uint32_t nt = 0; nt < n_col_tiles && ok; ++nt, ++t) {
+                    const uint32_t b = t & 1u, tph = (t >> 1) & 1u;
+                    if (!mbar_wait(&ctrl->tmem_empty[b], tph ^ 1u, p.error, 2)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t acc = tmem_base + b * BN;
+                    for (uint32_t kb = 0; kb < nkb; ++kb, ++kbt) {
+                        const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
+                        if (!mbar_wait(&ctrl->conv[s], ph, p.error, 3)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t st = smem_base + s * STAGE_BYTES;
+#pragma unroll
+                        for (uint32_t kk = 0; kk < BK / 8; ++kk) {
+                            const uint64_t a_hi = make_desc(st + OFF_A_HI + kk * 32);
+                            const uint64_t a_lo = make_desc(st + OFF_A_LO + kk * 32);
+                            const uint64_t b_hi = make_desc(st + OFF_B_HI + kk * 32);
+                            const uint64_t b_lo = make_desc(st + OFF_B_LO + kk * 32);
+                            umma_tf32(acc, a_hi, b_hi, (kb | kk) != 0 ? 1u : 0u);
+                            umma_tf32(acc, a_hi, b_lo, 1u);
+                            umma_tf32(acc, a_lo, b_hi, 1u);
+                        }
+                        umma_commit(&ctrl->empty[s]);
+                    }
+                    if (ok) umma_commit(&ctrl->tmem_full[b]);
+                }
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------------------------------------------------------- hi / lo splitters
+        const int cid = threadIdx.x - 64;
+        uint32_t kbt = 0;
+        bool ok = true;
+        for (size_t rt = blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {
+            for (uint32_t nt = 0; nt < n_col_tiles && ok; ++nt) {
+                for (uint32_t kb = 0; kb < nkb; ++kb, ++kbt) {
+                    const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
+                    if (!mbar_wait(&ctrl->full[s], ph, p.error, 4)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* st = smem + s * STAGE_BYTES;
+                    float4* a_hi = reinterpret_cast<float4*>(st + OFF_A_HI);
+                    float4* a_lo = reinterpret_cast<float4*>(st + OFF_A_LO);
+                    float4* b_hi = reinterpret_cast<float4*>(st + OFF_B_HI);
+                    float4* b_lo = reinterpret_cast<float4*>(st + OFF_B_LO);
+#pragma unroll
+                    for (int i = 0; i < static_cast<int>(A_TILE_BYTES / 16 / 128); ++i) {
+                        float4 hi, lo;
+                        split4(a_hi[cid + 128 * i], hi, lo);
+                        a_hi[cid + 128 * i] = hi;
+                        a_lo[cid + 128 * i] = lo;
+                    }
+#pragma unroll
+                    for (int i = 0; i < static_cast<int>(B_TILE_BYTES / 16 / 128); ++i) {
+                        float4 hi, lo;
+                        split4(b_hi[cid + 128 * i], hi, lo);
+                        b_hi[cid + 128 * i] = hi;
+                        b_lo[cid + 128 * i] = lo;
+                    }
+                    fence_proxy_async();
+                    mbar_arrive(&ctrl->conv[s]);
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue
+        const uint32_t lane_base = 32u * (warp & 3);    // tensor-memory lanes this warp may read
+        const uint32_t row_in_tile = lane_base + lane;
+        uint32_t t = 0;
+        bool ok = true;
+        for (size_t rt = blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {
+            const size_t row = rt * BM + row_in_tile;
+            const bool row_valid = row < p.n;
+            // Best and runner-up of the tensor-core distances.  They are only candidates: the accumulator
+            // in tensor memory truncates, which biases long sums by up to ~1e-5 relative, so the winner and
+            // its distance are settled afterwards in fp32 by refine_top2_kernel.
+            float nx = 0.f, d1 = FLT_MAX, d2 = FLT_MAX;
+            uint32_t i1 = 0, i2 = 0xFFFFFFFFu;
+            if (MODE == MODE_ARGMIN && row_valid) nx = p.norms_x[row];
+            for (uint32_t nt = 0; nt < n_col_tiles && ok; ++nt, ++t) {
+                const uint32_t b = t & 1u, tph = (t >> 1) & 1u;
+                const size_t col0 = static_cast<size_t>(nt) * BN;
+                float* ny = ctrl->ny[warp & 3][b];
+                if (MODE == MODE_ARGMIN) {
+                    // each warp keeps its own copy, so no cross-warp barrier is needed
+                    for (int j = lane; j < BN; j += 32) ny[j] = (col0 + j < p.k) ? __ldg(p.norms_y + col0 + j) : 0.f;
+                    __syncwarp();
+                }
+                // warp-uniform outcome: the tensor-memory loads below must be executed by the whole warp
+                if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->tmem_full[b], tph, p.error, 5))) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + (lane_base << 16) + b * BN;
+#pragma unroll 1
+                for (int ch = 0; ch < BN / 32; ++ch) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + ch * 32, r);
+                    if (MODE == MODE_ARGMIN) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const size_t c = col0 + ch * 32 + j;
+                            if (c < p.k) {
+                                const float dist = fmaf(-2.0f, __uint_as_float(r[j]), nx) + ny[ch * 32 + j];
+                                if (dist < d2) {
+                                    if (dist < d1) {
+                                        d2 = d1;
+                                        i2 = i1;
+                                        d1 = dist;
+                                        i1 = static_cast<uint32_t>(c);
+                                    } else {
+                                        d2 = dist;
+                                        i2 = static_cast<uint32_t>(c);
+                                    }
+                                }
+                            }
+                        }
+                    } else if (row_valid) {
+                        float* orow = p.out + row * p.ldo + col0 + ch * 32;
+                        const size_t left = (col0 + ch * 32 < p.k) ? (p.k - (col0 + ch * 32)) : 0;
+                        if (left >= 32 && (p.ldo % 4 == 0)) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4*>(orow + j) =
+                                    make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (static_cast<size_t>(j) < left) orow[j] = __uint_as_float(r[j]);
+                        }
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(&ctrl->tmem_empty[b]);
+            }
+            if (MODE == MODE_ARGMIN && ok && row_valid) p.out_top2[row] = make_uint2(i1, i2);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// Settles the assignment in fp32: one warp per row recomputes ||x||^2 + ||y||^2 - 2 x.y for the two
+// candidates with fp32 fused multiply-adds, keeps the smaller (the lower index on a tie) and stores
+// the distance clamped at zero, as the reference does (batch_computers.h:160-166).
+__global__ void __launch_bounds__(256) refine_top2_kernel(
+    const float* __restrict__ x, const float* __restrict__ y, size_t n, size_t d, const float* __restrict__ norms_x, const float* __restrict__ norms_y,
+    const uint2* __restrict__ top2, uint32_t* __restrict__ out_knn, float* __restrict__ out_dist
+) {
+    const size_t row = static_cast<size_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (row >= n) return;
+    const int lane = threadIdx.x & 31;
+    const uint2 cand = top2[row];
+    const bool two = cand.y != 0xFFFFFFFFu;
+    const float* xr = x + row * d;
+    const float* y1 = y + static_cast<size_t>(cand.x) * d;
+    const float* y2 = y + static_cast<size_t>(two ? cand.y : cand.x) * d;
+    float a1 = 0.f, a2 = 0.f;
+    for (size_t j = static_cast<size_t>(lane) * 4; j < d; j += 128) {  // d % 4 == 0 on this path
+        const float4 xv = __ldg(reinterpret_cast<const float4*>(xr + j));
+        const float4 u = __ldg(reinterpret_cast<const float4*>(y1 + j));
+        const float4 v = __ldg(reinterpret_cast<const float4*>(y2 + j));
+        a1 = fmaf(xv.x, u.x, a1); a1 = fmaf(xv.y, u.y, a1); a1 = fmaf(xv.z, u.z, a1); a1 = fmaf(xv.w, u.w, a1);
+        a2 = fmaf(xv.x, v.x, a2); a2 = fmaf(xv.y, v.y, a2); a2 = fmaf(xv.z, v.z, a2); a2 = fmaf(xv.w, v.w, a2);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        a1 += __shfl_xor_sync(0xffffffffu, a1, o);
+        a2 += __shfl_xor_sync(0xffffffffu, a2, o);
+    }
+    if (lane == 0) {
+        const float nx = norms_x[row];
+        float e1 = fmaf(-2.0f, a1, nx) + norms_y[cand.x];
+        uint32_t w = cand.x;
+        if (two) {
+            const float e2 = fmaf(-2.0f, a2, nx) + norms_y[cand.y];
+            if (e2 < e1 || (e2 == e1 && cand.y < cand.x)) {
+                e1 = e2;
+                w = cand.y;
+            }
+        }
+        out_knn[row] = w;
+        out_dist[row] = fmaxf(0.0f, e1);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        }
+    });
+    if (!fn) throw CudaError("cuTensorMapEncodeTiled is not available from this driver");
+    return fn;
+}
+
+// Row-major fp32 matrix [rows][ld] of which the first `extent` columns are visible; boxes of 16
+// columns x box_rows rows, 64-byte swizzle, zero fill outside.
+CUtensorMap make_tmap(const float* base, size_t extent, size_t rows, size_t ld, uint32_t box_rows) {
+    CUtensorMap m;
+    const cuuint64_t dims[2] = {extent, rows};
+    const cuuint64_t strides[1] = {ld * sizeof(float)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                   CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw CudaError("cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
+    return m;
+}
+
+int* error_flag(int device) {
+    static std::mutex mu;
+    static int* flags[64] = {nullptr};
+    std::lock_guard<std::mutex> lock(mu);
+    if (!flags[device]) {
+        SKM_CUDA(cudaMalloc(&flags[device], sizeof(int)));
+        SKM_CUDA(cudaMemset(flags[device], 0, sizeof(int)));
+    }
+    return flags[device];
+}
+
+int sm_count(int device) {
+    int sms = 0;
+    SKM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    return sms;
+}
+
+template <int MODE>
+void launch(const CUtensorMap& tx, const CUtensorMap& ty, const Params& p, cudaStream_t stream) {
+    SKM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES)));
+    int device = 0;
+    SKM_CUDA(cudaGetDevice(&device));
+    const size_t row_tiles = (p.n + BM - 1) / BM;
+    const int grid = static_cast<int>(std::min<size_t>(row_tiles, static_cast<size_t>(sm_count(device))));
+    gemm_tc_kernel<MODE><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, ty, p);
+    note_kernel_launch();
+    SKM_CUDA(cudaGetLastError());
+}
+
+bool g_enabled = true;
+
+} // namespace
+
+void set_enabled(bool on) { g_enabled = on; }
+bool enabled() { return g_enabled; }
+
+bool eligible(const float* x, size_t ldx, const float* y, size_t ldy) {
+    if (!g_enabled) return false;
+    if (ldx % 4 != 0 || ldy % 4 != 0) return false;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(y) & 15)) return false;
+    return true;
+}
+
+void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist,
+                        uint2* top2_scratch, cudaStream_t stream) {
+    if (n == 0 || k == 0) return;
+    int device = 0;
+    SKM_CUDA(cudaGetDevice(&device));
+    const CUtensorMap tx = make_tmap(x, d, n, d, BM);
+    const CUtensorMap ty = make_tmap(y, d, k, d, BN);
+    Params p{};
+    p.n = n;
+    p.k = k;
+    p.kdim = static_cast<uint32_t>(d);
+    p.norms_x = norms_x;
+    p.norms_y = norms_y;
+    p.out_knn = out_knn;
+    p.out_dist = out_dist;
+    p.out_top2 = top2_scratch;
+    p.error = error_flag(device);
+    launch<MODE_ARGMIN>(tx, ty, p, stream);
+    refine_top2_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, d, norms_x, norms_y, top2_scratch, out_knn, out_dist);
+    note_kernel_launch();
+    SKM_CUDA(cudaGetLastError());
+}
+
+void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, float* out, size_t ldo, size_t n, size_t n_out, size_t k_dim, cudaStream_t stream) {
+    if (n == 0 || n_out == 0) return;
+    int device = 0;
+    SKM_CUDA(cudaGetDevice(&device));
+    const CUtensorMap tx = make_tmap(a, k_dim, n, lda, BM);
+    const CUtensorMap ty = make_tmap(b, k_dim, n_out, ldb, BN);
+    Params p{};
+    p.n = n;
+    p.k = n_out;
+    p.kdim = static_cast<uint32_t>(k_dim);
+    p.out = out;
+    p.ldo = ldo;
+    p.error = error_flag(device);
+    launch<MODE_STORE>(tx, ty, p, stream);
+}
+
+// Reads (and clears) the error code left by the last kernels on this device.  Synchronises `stream`.
+int fetch_error(cudaStream_t stream) {
+    int device = 0;
+    SKM_CUDA(cudaGetDevice(&device));
+    int* flag = error_flag(device);
+    int host = 0;
+    SKM_CUDA(cudaMemcpyAsync(&host, flag, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    SKM_CUDA(cudaStreamSynchronize(stream));
+    if (host != 0) SKM_CUDA(cudaMemsetAsync(flag, 0, sizeof(int), stream));
+    return host;
+}
+
+} // namespace tc
+} // namespace skmb

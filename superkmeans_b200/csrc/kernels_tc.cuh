@@ -1,0 +1,29 @@
+// Tensor-core (tcgen05 + TMA) variants of the dense kernels; see kernels_tc.cu.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace skmb {
+namespace tc {
+
+// Process-wide switch (on by default); off routes every dense kernel to the SIMT implementation.
+void set_enabled(bool on);
+bool enabled();
+
+// The TMA path needs 16-byte aligned bases and row pitches.
+bool eligible(const float* x, size_t ldx, const float* y, size_t ldy);
+
+// top2_scratch: n entries of device scratch (candidate pairs handed from the tensor-core pass to the
+// fp32 refinement).
+void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist,
+                        uint2* top2_scratch, cudaStream_t stream);
+void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, float* out, size_t ldo, size_t n, size_t n_out, size_t k_dim, cudaStream_t stream);
+
+// Error code (0 = none) recorded by a kernel whose bounded wait expired; clears it.  Synchronises.
+int fetch_error(cudaStream_t stream);
+
+} // namespace tc
+} // namespace skmb

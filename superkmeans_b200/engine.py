@@ -191,6 +191,15 @@ class Engine:
         return out
 
 
+def set_tensor_cores(enabled: bool) -> None:
+    """Route the dense products to the tcgen05 kernels (default) or to the fp32 SIMT kernels."""
+    lib.skm_set_tensor_cores(int(enabled))
+
+
+def tensor_cores_enabled() -> bool:
+    return bool(lib.skm_get_tensor_cores())
+
+
 def kernel_launches() -> int:
     return int(lib.skm_kernel_launches())
 

@@ -14,11 +14,14 @@ from tests import datagen
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def eng():
+@pytest.fixture(scope="module", params=["tensor_cores", "simt"])
+def eng(request):
+    """Every operator test runs twice: dense products on the tcgen05 kernels and on the SIMT kernels."""
     from superkmeans_b200 import engine
 
-    return engine
+    engine.set_tensor_cores(request.param == "tensor_cores")
+    yield engine
+    engine.set_tensor_cores(True)
 
 
 def _near_tie_ok(x, y, a, b, rel=1e-5):
