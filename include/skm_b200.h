@@ -148,6 +148,12 @@ skm_status skm_reset_phase_times(skm_handle* h);
  * No counterpart in the reference (it delegates to whatever BLAS is linked). */
 void skm_set_tensor_cores(int enabled);
 int skm_get_tensor_cores(void);
+/* How a pruned assignment pass divides its points between its two kernels: 0 (default) by the survival
+ * rate of the first ADSampling test on a sample of centroids, 1 all through the candidate-list kernel,
+ * 2 all through the dense-chain kernel.  The results do not depend on the choice (up to fp32 rounding);
+ * it exists for profiling and for testing each kernel on its own.  No counterpart in the reference. */
+void skm_set_prune_split(int mode);
+int skm_get_prune_split(void);
 /* Kernels launched by this library in the calling process so far. */
 uint64_t skm_kernel_launches(void);
 

@@ -93,6 +93,8 @@ SIGNATURES = {
     "skm_get_phase_time": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
     "skm_reset_phase_times": (C.c_int, [C.c_void_p]),
     "skm_kernel_launches": (C.c_uint64, []),
+    "skm_set_prune_split": (None, [C.c_int]),
+    "skm_get_prune_split": (C.c_int, []),
     "skm_set_tensor_cores": (None, [C.c_int]),
     "skm_get_tensor_cores": (C.c_int, []),
     "skm_set_shard": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, ALLREDUCE_FN, C.c_void_p]),

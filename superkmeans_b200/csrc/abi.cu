@@ -196,6 +196,9 @@ skm_status skm_trace_get(const skm_handle* h, uint64_t idx, uint64_t* n_samples,
 void skm_set_tensor_cores(int enabled) { skmb::tc::set_enabled(enabled != 0); }
 int skm_get_tensor_cores(void) { return skmb::tc::enabled() ? 1 : 0; }
 
+void skm_set_prune_split(int mode) { skmb::set_prune_split_mode(mode); }
+int skm_get_prune_split(void) { return skmb::prune_split_mode(); }
+
 uint64_t skm_kernel_launches(void) { return skmb::kernel_launch_count(); }
 
 skm_status skm_set_shard(skm_handle* h, uint64_t n_global, uint64_t row_offset, skm_allreduce_fn fn, void* user) {

@@ -24,6 +24,12 @@ inline void cuda_check(cudaError_t e, const char* what, const char* file, int li
 
 unsigned long long kernel_launch_count();
 void note_kernel_launch();
+// After every kernel launch: count it and surface launch-configuration errors.
+#define SKM_LAUNCH_CHECK()                                                                         \
+    do {                                                                                           \
+        ::skmb::note_kernel_launch();                                                              \
+        SKM_CUDA(cudaGetLastError());                                                              \
+    } while (0)
 
 constexpr int kTileM = 128;        // points per CTA tile
 constexpr int kTileN = 128;        // centroids per GEMM sub-tile (SIMT path)
@@ -34,6 +40,9 @@ constexpr int kUpdateTile = 1024;  // sorted points per segmented-sum tile
 // ---------------------------------------------------------------------------------------------
 // Launchers (all asynchronous on `stream`; pointers are device pointers unless stated otherwise)
 // ---------------------------------------------------------------------------------------------
+
+// In-place exclusive scan of n uint32 values; totals_tmp needs n / 2048 + 1 entries of scratch.
+void exclusive_scan_u32(uint32_t* data, size_t n, uint32_t* totals_tmp, cudaStream_t stream);
 
 // out[i] = sum_{j < upto} x[i*ld + j]^2
 void launch_row_sqnorms(const float* x, size_t n, size_t ld, size_t upto, float* out, cudaStream_t stream);
@@ -65,7 +74,43 @@ struct PrunedParams {
     uint2* scratch;             // candidate lists, pruned_scratch_elems() entries
     size_t n, k, d;
     uint32_t partial_d, vertical_d, horizontal_d;
+    const float* best_in = nullptr;     // optional: exact distance to the previous centroid, per point
+    const uint32_t* skip = nullptr;     // optional: 1 = leave this point to the dense kernel
 };
+
+// Work split of one pruned pass.  Points whose ADSampling test would keep a large share of the
+// centroids alive (their current centroid is far away, so every threshold is loose) cost one gathered
+// 64-dimension block per surviving pair and step in the candidate-list kernel; they are cheaper to
+// treat densely.  pruned_prepare computes the exact distance to the previous centroid for every point
+// and flags the expensive ones from the survival rate on a sample of 128 centroids;
+// assign_pruned_dense runs the same test chain for the flagged points with a tile GEMM over all
+// dimensions (no candidate lists).  The split changes only where the work is done, never the result.
+struct PruneSplitWorkspace {
+    float* best = nullptr;          // n
+    uint32_t* flags = nullptr;      // n   (1 = dense)
+    uint32_t* positions = nullptr;  // n + scan scratch  (exclusive scan of flags)
+    uint32_t* hard_idx = nullptr;   // n
+    float* sample = nullptr;        // 128 x d sampled centroid rows
+    float* sample_norms = nullptr;  // 128
+    float* chain_norms_y = nullptr; // k x n_checkpoints
+    uint32_t* n_hard_dev = nullptr; // 1
+    unsigned long long* alive_total = nullptr;  // 1: sampled pairs passing the first test
+    int n_sample = 128;
+    float ratio_first = 1.0f;       // ratios[partial_d], host copy
+};
+size_t prune_split_positions_elems(size_t n);
+uint32_t prune_chain_checkpoints(uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d);
+// out[i] = ||x_i - y_{knn[i]}||^2 accumulated directly in fp32 (no norm trick)
+void launch_exact_dist(const float* x, const float* y, const uint32_t* knn, size_t n, size_t d, float* out, cudaStream_t stream);
+// Cumulative squared norm of every row of m after each checkpoint of the chain: out[row][j], or
+// out[j][row] when `transposed`.
+void launch_chain_norms(const float* m, size_t rows, size_t d, uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d, bool transposed, float* out,
+                        cudaStream_t stream);
+// Fills ws.best and ws.flags / ws.hard_idx / *ws.n_hard_dev.
+void launch_pruned_prepare(const PrunedParams& p, PruneSplitWorkspace& ws, cudaStream_t stream);
+// Runs the dense chain for the n_hard points listed in ws.hard_idx.
+void launch_assign_pruned_dense(const PrunedParams& p, PruneSplitWorkspace& ws, size_t n_hard, cudaStream_t stream);
+
 int pruned_grid_size(int device);
 size_t pruned_scratch_elems(int grid);
 void launch_assign_pruned(const PrunedParams& p, int grid, cudaStream_t stream);

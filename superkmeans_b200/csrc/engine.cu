@@ -144,8 +144,8 @@ Engine::Engine(const skm_config& cfg, size_t n_clusters, size_t d, bool hierarch
     DeviceGuard guard(device_);
     SKM_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
     SKM_CUDA(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
-    const std::vector<float> ratios = make_ratios(d, epsilon0_);
-    SKM_CUDA(cudaMemcpy(ratios_dev_.ensure(d + 1), ratios.data(), sizeof(float) * (d + 1), cudaMemcpyHostToDevice));
+    ratios_host_ = make_ratios(d, epsilon0_);
+    SKM_CUDA(cudaMemcpy(ratios_dev_.ensure(d + 1), ratios_host_.data(), sizeof(float) * (d + 1), cudaMemcpyHostToDevice));
     scalars_dev_.ensure(8);
     np_total_dev_.ensure(1);
     scalars_host_.ensure(8);
@@ -329,9 +329,84 @@ void Engine::generate_centroids_from_device_rows(const float* dev_rows, size_t n
 // -------------------------------------------------------------------------------------------------
 // One pruned assignment pass (batch_computers.h:297-409)
 // -------------------------------------------------------------------------------------------------
+namespace {
+int g_prune_split_mode = 0;
+
+__global__ void fill_iota_kernel(uint32_t* idx, uint32_t* flags, size_t n, uint32_t flag_value) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) {
+        idx[i] = static_cast<uint32_t>(i);
+        flags[i] = flag_value;
+    }
+}
+} // namespace
+
+void set_prune_split_mode(int mode) { g_prune_split_mode = mode; }
+int prune_split_mode() { return g_prune_split_mode; }
+
+void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, int device, cudaStream_t stream) {
+    if (p.n == 0) return;
+    if (b.grid == 0) b.grid = pruned_grid_size(device);
+    const uint32_t n_ck = prune_chain_checkpoints(p.partial_d, p.vertical_d, p.horizontal_d);
+    PruneSplitWorkspace ws;
+    ws.best = b.best.ensure(p.n);
+    ws.flags = b.flags.ensure(p.n);
+    ws.positions = b.positions.ensure(prune_split_positions_elems(p.n));
+    ws.hard_idx = b.hard_idx.ensure(p.n);
+    ws.sample = b.sample.ensure(128 * p.d);
+    ws.sample_norms = b.sample_norms.ensure(128);
+    ws.chain_norms_y = b.chain_norms_y.ensure(p.k * n_ck);
+    ws.n_hard_dev = b.n_hard_dev.ensure(1);
+    ws.ratio_first = ratio_first;
+    ws.alive_total = b.alive_total.ensure(1);
+    launch_pruned_prepare(p, ws, stream);
+    const int n_sample = static_cast<int>(std::min<size_t>(p.k, 128));
+    const bool tc_ok = tc::eligible(p.x, p.d, p.y, p.d);
+    size_t n_hard = 0;
+    bool use_chain = false;
+    if (g_prune_split_mode == 0) {
+        unsigned long long* host = b.counters_host.ensure(2);
+        host[0] = 0;
+        host[1] = 0;
+        SKM_CUDA(cudaMemcpyAsync(&host[0], ws.alive_total, sizeof(unsigned long long), cudaMemcpyDeviceToHost, stream));
+        SKM_CUDA(cudaMemcpyAsync(&host[1], ws.n_hard_dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
+        SKM_CUDA(cudaStreamSynchronize(stream));
+        n_hard = static_cast<size_t>(host[1] & 0xFFFFFFFFull);
+        // Candidate lists cost one gathered block per surviving pair and step; the tensor-core chain costs a
+        // full product whatever survives.  Past roughly 0.8 % of surviving pairs the chain is cheaper.
+        const double survival = static_cast<double>(host[0]) / (static_cast<double>(p.n) * n_sample);
+        use_chain = tc_ok && survival > 0.008;
+    } else if (g_prune_split_mode == 3) {
+        if (!tc_ok) throw std::invalid_argument("the tensor-core chain needs 16-byte aligned rows (d % 4 == 0)");
+        use_chain = true;
+    } else {
+        const bool dense = g_prune_split_mode == 2;
+        fill_iota_kernel<<<static_cast<unsigned>((p.n + 255) / 256), 256, 0, stream>>>(ws.hard_idx, ws.flags, p.n, dense ? 1u : 0u);
+        note_kernel_launch();
+        SKM_CUDA(cudaGetLastError());
+        n_hard = dense ? p.n : 0;
+    }
+    if (use_chain) {
+        b.last_path = 3;
+        b.last_n_hard = p.n;
+        launch_chain_norms(p.x, p.n, p.d, p.partial_d, p.vertical_d, p.horizontal_d, false, b.chain_norms_x.ensure(p.n * n_ck), stream);
+        launch_chain_norms(p.y, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, true, ws.chain_norms_y, stream);
+        tc::launch_chain(p.x, p.y, p.n, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, b.chain_norms_x.get(), ws.chain_norms_y, p.ratios, ws.best, p.knn, p.dist,
+                         p.not_pruned, b.top2.ensure(p.n), stream);
+        return;
+    }
+    b.last_path = 1;
+    b.last_n_hard = n_hard;
+    p.best_in = ws.best;
+    p.skip = ws.flags;
+    if (n_hard < p.n) {
+        p.scratch = b.lists.ensure(pruned_scratch_elems(b.grid));
+        launch_assign_pruned(p, b.grid, stream);
+    }
+    launch_assign_pruned_dense(p, ws, n_hard, stream);
+}
+
 void Engine::run_pruned_pass(const float* x, size_t n, size_t k_cur, const float* y, const float* norms_x, const float* norms_y, uint32_t* knn, float* dist, uint32_t* not_pruned) {
-    if (pruned_grid_ == 0) pruned_grid_ = pruned_grid_size(device_);
-    pruned_scratch_.ensure(pruned_scratch_elems(pruned_grid_));
     PrunedParams p{};
     p.x = x;
     p.y = y;
@@ -343,14 +418,13 @@ void Engine::run_pruned_pass(const float* x, size_t n, size_t k_cur, const float
     p.knn = knn;
     p.dist = dist;
     p.not_pruned = not_pruned;
-    p.scratch = pruned_scratch_.get();
     p.n = n;
     p.k = k_cur;
     p.d = d_;
     p.partial_d = partial_d_;
     p.vertical_d = vertical_d_;
     p.horizontal_d = horizontal_d_;
-    launch_assign_pruned(p, pruned_grid_, stream_);
+    run_pruned_pass_on(p, prune_bufs_, ratios_host_[partial_d_], device_, stream_);
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -1045,7 +1119,6 @@ void Engine::op_find_nearest_pruned(int device, const float* x, const float* y, 
     OpContext ctx(device);
     DeviceBuffer<float> xd, yd, nx, ny, pdx, aux, dist, ratios_d;
     DeviceBuffer<uint32_t> knn, np;
-    DeviceBuffer<uint2> scratch;
     const std::vector<float> ratios = make_ratios(d, eps0);
     ctx.upload(xd, x, n * d);
     ctx.upload(yd, y, k * d);
@@ -1056,7 +1129,6 @@ void Engine::op_find_nearest_pruned(int device, const float* x, const float* y, 
     launch_pdxify(yd.get(), pdx.ensure(k * d), aux.ensure(k * split.vertical_d + 1), k, d, split.vertical_d, ctx.stream);
     int dev = 0;
     SKM_CUDA(cudaGetDevice(&dev));
-    const int grid = pruned_grid_size(dev);
     PrunedParams p{};
     p.x = xd.get();
     p.y = yd.get();
@@ -1068,14 +1140,14 @@ void Engine::op_find_nearest_pruned(int device, const float* x, const float* y, 
     p.knn = knn.get();
     p.dist = dist.ensure(n);
     p.not_pruned = np.ensure(n);
-    p.scratch = scratch.ensure(pruned_scratch_elems(grid));
     p.n = n;
     p.k = k;
     p.d = d;
     p.partial_d = partial_d;
     p.vertical_d = static_cast<uint32_t>(split.vertical_d);
     p.horizontal_d = static_cast<uint32_t>(split.horizontal_d);
-    launch_assign_pruned(p, grid, ctx.stream);
+    PrunePassBuffers bufs;
+    run_pruned_pass_on(p, bufs, ratios[partial_d], dev, ctx.stream);
     std::vector<uint32_t> np_host(n);
     ctx.download(knn_io, knn.get(), n);
     ctx.download(dist_out, dist.get(), n);

@@ -100,6 +100,26 @@ class PhaseTimers {
     std::vector<cudaEvent_t> pool_;
 };
 
+// Device buffers of one pruned assignment pass (candidate lists, work split) and the pass itself:
+// preparation, candidate-list kernel for the cheap points, dense chain for the expensive ones.
+struct PrunePassBuffers {
+    DeviceBuffer<uint2> lists, top2;
+    DeviceBuffer<float> best, sample, sample_norms, chain_norms_y;
+    DeviceBuffer<float> chain_norms_x;
+    DeviceBuffer<uint32_t> flags, positions, hard_idx, n_hard_dev;
+    DeviceBuffer<unsigned long long> alive_total;
+    PinnedBuffer<unsigned long long> counters_host;
+    int last_path = 0;   // 1 lists (+ dense for flagged points), 3 tensor-core chain
+    int grid = 0;
+    size_t last_n_hard = 0;
+};
+// mode: 0 = automatic (tensor-core chain for every point when the sampled survival rate is high, else
+// candidate lists with the flagged points on the dense SIMT chain), 1 = candidate lists for every point,
+// 2 = dense SIMT chain for every point, 3 = tensor-core chain for every point.
+void set_prune_split_mode(int mode);
+int prune_split_mode();
+void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, int device, cudaStream_t stream);
+
 class Engine {
   public:
     Engine(const skm_config& cfg, size_t n_clusters, size_t d, bool hierarchical, int device);
@@ -216,9 +236,9 @@ class Engine {
     DeviceBuffer<uint32_t> counts_;
     DeviceBuffer<uint32_t> assignments_, not_pruned_;
     DeviceBuffer<float> distances_;
-    DeviceBuffer<uint2> pruned_scratch_;
+    PrunePassBuffers prune_bufs_;
+    std::vector<float> ratios_host_;
     DeviceBuffer<uint2> top2_;           // candidate pairs of the tensor-core exact assignment
-    int pruned_grid_ = 0;
     DeviceBuffer<SplitOpDev> split_ops_dev_;
     DeviceBuffer<double> scalars_dev_;   // [0] wcss, [1] not-pruned total (as double), [2] shift
     DeviceBuffer<unsigned long long> np_total_dev_;

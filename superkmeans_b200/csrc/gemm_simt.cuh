@@ -30,10 +30,11 @@ struct GemmSmem {
 __device__ __forceinline__ int tile_row_of(int ty, int i) { return (i < 4) ? (ty * 4 + i) : (64 + ty * 4 + (i - 4)); }
 __device__ __forceinline__ int tile_col_of(int tx, int j) { return (j < 4) ? (tx * 4 + j) : (64 + tx * 4 + (j - 4)); }
 
-__device__ __forceinline__ float4 gemm_load4(const float* __restrict__ base, size_t ld, int row, int rows_valid, int k0, int K, bool vec_ok) {
+// `grow` is the row of the matrix that tile row `row` maps to (identity unless rows are indirect).
+__device__ __forceinline__ float4 gemm_load4(const float* __restrict__ base, size_t ld, int row, size_t grow, int rows_valid, int k0, int K, bool vec_ok) {
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (row < rows_valid && k0 < K) {
-        const float* p = base + static_cast<size_t>(row) * ld + k0;
+        const float* p = base + grow * ld + k0;
         if (vec_ok && k0 + 3 < K) {
             v = __ldg(reinterpret_cast<const float4*>(p));
         } else {
@@ -53,10 +54,15 @@ __device__ __forceinline__ void gemm_store4(float (*dst)[kGemmLd], int kq, int r
     dst[kq + 3][row] = v.w;
 }
 
-// acc[i][j] = sum_{k < K} A[tile_row_of(ty,i)][k] * B[tile_col_of(tx,j)][k]
-// A, B point at the first row of the tile.  Must be called by all 256 threads of the CTA.
-__device__ __forceinline__ void gemm_tile_nt(
-    const float* __restrict__ A, size_t lda, int m_valid, const float* __restrict__ B, size_t ldb, int n_valid, int K, GemmSmem& s, float (&acc)[8][8]
+// acc[i][j] (+)= sum_{k < K} A[row(tile_row_of(ty,i))][k] * B[tile_col_of(tx,j)][k]
+// A, B point at the first row of the tile (A at row 0 of the matrix when INDIRECT, in which case
+// row_idx[r] in shared memory names the matrix row of tile row r).  ZERO_ACC clears the accumulators
+// first; otherwise the products are added to what they hold, which lets a caller walk the reduction
+// dimension in several segments.  Must be called by all 256 threads of the CTA.
+template <bool ZERO_ACC, bool INDIRECT>
+__device__ __forceinline__ void gemm_tile_nt_ex(
+    const float* __restrict__ A, size_t lda, int m_valid, const uint32_t* row_idx, const float* __restrict__ B, size_t ldb, int n_valid, int K, GemmSmem& s,
+    float (&acc)[8][8]
 ) {
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;
@@ -64,16 +70,20 @@ __device__ __forceinline__ void gemm_tile_nt(
     const int kq = (tid & 3) * 4;    // 0,4,8,12
     const bool vec_a = (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
     const bool vec_b = (ldb % 4 == 0) && ((reinterpret_cast<uintptr_t>(B) & 15) == 0);
+    if (ZERO_ACC) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+            for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+    }
+    const size_t ga0 = INDIRECT ? ((lr < m_valid) ? row_idx[lr] : 0) : static_cast<size_t>(lr);
+    const size_t ga1 = INDIRECT ? ((lr + 64 < m_valid) ? row_idx[lr + 64] : 0) : static_cast<size_t>(lr + 64);
 
     const int nk = (K + kGemmBK - 1) / kGemmBK;
-    float4 ra0 = gemm_load4(A, lda, lr, m_valid, kq, K, vec_a);
-    float4 ra1 = gemm_load4(A, lda, lr + 64, m_valid, kq, K, vec_a);
-    float4 rb0 = gemm_load4(B, ldb, lr, n_valid, kq, K, vec_b);
-    float4 rb1 = gemm_load4(B, ldb, lr + 64, n_valid, kq, K, vec_b);
+    float4 ra0 = gemm_load4(A, lda, lr, ga0, m_valid, kq, K, vec_a);
+    float4 ra1 = gemm_load4(A, lda, lr + 64, ga1, m_valid, kq, K, vec_a);
+    float4 rb0 = gemm_load4(B, ldb, lr, lr, n_valid, kq, K, vec_b);
+    float4 rb1 = gemm_load4(B, ldb, lr + 64, lr + 64, n_valid, kq, K, vec_b);
     gemm_store4(s.a[0], kq, lr, ra0);
     gemm_store4(s.a[0], kq, lr + 64, ra1);
     gemm_store4(s.b[0], kq, lr, rb0);
@@ -85,10 +95,10 @@ __device__ __forceinline__ void gemm_tile_nt(
         const bool more = (ks + 1 < nk);
         if (more) {
             const int k0 = (ks + 1) * kGemmBK + kq;
-            ra0 = gemm_load4(A, lda, lr, m_valid, k0, K, vec_a);
-            ra1 = gemm_load4(A, lda, lr + 64, m_valid, k0, K, vec_a);
-            rb0 = gemm_load4(B, ldb, lr, n_valid, k0, K, vec_b);
-            rb1 = gemm_load4(B, ldb, lr + 64, n_valid, k0, K, vec_b);
+            ra0 = gemm_load4(A, lda, lr, ga0, m_valid, k0, K, vec_a);
+            ra1 = gemm_load4(A, lda, lr + 64, ga1, m_valid, k0, K, vec_a);
+            rb0 = gemm_load4(B, ldb, lr, lr, n_valid, k0, K, vec_b);
+            rb1 = gemm_load4(B, ldb, lr + 64, lr + 64, n_valid, k0, K, vec_b);
         }
 #pragma unroll
         for (int k = 0; k < kGemmBK; ++k) {
@@ -111,6 +121,12 @@ __device__ __forceinline__ void gemm_tile_nt(
         }
         __syncthreads();
     }
+}
+
+__device__ __forceinline__ void gemm_tile_nt(
+    const float* __restrict__ A, size_t lda, int m_valid, const float* __restrict__ B, size_t ldb, int n_valid, int K, GemmSmem& s, float (&acc)[8][8]
+) {
+    gemm_tile_nt_ex<true, false>(A, lda, m_valid, nullptr, B, ldb, n_valid, K, s, acc);
 }
 
 } // namespace skmb

@@ -7,6 +7,7 @@
 //   centroid update             radix sort + segmented sum  (superkmeans.h:729-765, :973-981)
 //   consolidation               scale / split ops / pdxify / shift (superkmeans.h:936-998, layout.h:155-232)
 #include "common.cuh"
+#include "device_utils.cuh"
 #include "gemm_simt.cuh"
 #include "kernels_tc.cuh"
 
@@ -19,32 +20,6 @@ namespace skmb {
 static std::atomic<unsigned long long> g_kernel_launches{0};
 unsigned long long kernel_launch_count() { return g_kernel_launches.load(); }
 void note_kernel_launch() { g_kernel_launches.fetch_add(1, std::memory_order_relaxed); }
-#define SKM_LAUNCH_CHECK()                                                                         \
-    do {                                                                                           \
-        note_kernel_launch();                                                                      \
-        SKM_CUDA(cudaGetLastError());                                                              \
-    } while (0)
-
-// =================================================================================================
-// Small helpers
-// =================================================================================================
-
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-
-// Monotone map float -> uint32 (preserves <), so that (key << 32 | index) orders by distance then
-// by index under an unsigned 64-bit minimum.
-__device__ __forceinline__ uint32_t float_to_ordered(float f) {
-    const uint32_t b = __float_as_uint(f);
-    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
-}
-__device__ __forceinline__ float ordered_to_float(uint32_t o) {
-    const uint32_t b = (o & 0x80000000u) ? (o & 0x7fffffffu) : ~o;
-    return __uint_as_float(b);
-}
 
 // =================================================================================================
 // Row squared norms over the first `upto` columns: one warp per row.
@@ -273,6 +248,7 @@ struct PrunedRowState {
     float prev_pd[kTileM];
     uint32_t prev_flag[kTileM];
     unsigned long long chunk_key[kTileM];
+    uint32_t active[kTileM];
     uint32_t list_count;
 };
 
@@ -362,7 +338,21 @@ __global__ void __launch_bounds__(256, 2) assign_pruned_kernel(const PrunedParam
         const int m_valid = static_cast<int>(min(static_cast<size_t>(kTileM), p.n - row0));
 
         // Exact distance to the previous centroid gives the first threshold (batch_computers.h:372-377).
+        // When the caller has computed it already (p.best_in) it is taken from there; rows flagged in
+        // p.skip belong to the dense kernel and are left untouched here.
+        if (p.best_in) {
+            if (tid < kTileM) {
+                const bool active = tid < m_valid && !(p.skip && p.skip[row0 + tid]);
+                st.best[tid] = active ? p.best_in[row0 + tid] : -1.0f;   // negative: no partial distance passes
+                st.bestidx[tid] = active ? p.knn[row0 + tid] : 0u;
+                st.prev[tid] = active ? p.knn[row0 + tid] : 0xFFFFFFFFu;
+                st.nxs[tid] = (tid < m_valid) ? p.norms_x[row0 + tid] : 0.f;
+                st.npc[tid] = 0;
+                st.active[tid] = active ? 1u : 0u;
+            }
+        } else
         for (int r = warp; r < kTileM; r += 8) {
+            if (lane == 0) st.active[r] = (r < m_valid) ? 1u : 0u;
             if (r < m_valid) {
                 const uint32_t pa = p.knn[row0 + r];
                 const float* __restrict__ xr = p.x + (row0 + r) * p.d;
@@ -474,7 +464,7 @@ __global__ void __launch_bounds__(256, 2) assign_pruned_kernel(const PrunedParam
             }
             __syncthreads();
         }
-        if (tid < m_valid) {
+        if (tid < m_valid && st.active[tid]) {
             p.knn[row0 + tid] = st.bestidx[tid];
             p.dist[row0 + tid] = st.best[tid];
             p.not_pruned[row0 + tid] = st.npc[tid];
@@ -610,7 +600,7 @@ __global__ void __launch_bounds__(1024) scan_add_kernel(uint32_t* __restrict__ d
     if (i0 + 1 < n) data[i0 + 1] += off;
 }
 
-static void exclusive_scan_u32(uint32_t* data, size_t n, uint32_t* totals_tmp, cudaStream_t stream) {
+void exclusive_scan_u32(uint32_t* data, size_t n, uint32_t* totals_tmp, cudaStream_t stream) {
     if (n == 0) return;
     const size_t blocks = (n + 2047) / 2048;
     scan_block_kernel<<<static_cast<unsigned>(blocks), 1024, 0, stream>>>(data, n, totals_tmp);

@@ -150,6 +150,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_ld128(uint32_t taddr, uint32_t (&r)[128]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x128.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63, %64, %65, %66, %67, %68, %69, %70, %71, %72, %73, %74, %75, %76, %77, %78, %79, %80, %81, %82, %83, %84, %85, %86, %87, %88, %89, %90, %91, %92, %93, %94, %95, %96, %97, %98, %99, %100, %101, %102, %103, %104, %105, %106, %107, %108, %109, %110, %111, %112, %113, %114, %115, %116, %117, %118, %119, %120, %121, %122, %123, %124, %125, %126, %127}, [%128];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63]), "=r"(r[64]), "=r"(r[65]), "=r"(r[66]), "=r"(r[67]), "=r"(r[68]), "=r"(r[69]), "=r"(r[70]), "=r"(r[71]), "=r"(r[72]), "=r"(r[73]), "=r"(r[74]), "=r"(r[75]), "=r"(r[76]), "=r"(r[77]), "=r"(r[78]), "=r"(r[79]), "=r"(r[80]), "=r"(r[81]), "=r"(r[82]), "=r"(r[83]), "=r"(r[84]), "=r"(r[85]), "=r"(r[86]), "=r"(r[87]), "=r"(r[88]), "=r"(r[89]), "=r"(r[90]), "=r"(r[91]), "=r"(r[92]), "=r"(r[93]), "=r"(r[94]), "=r"(r[95]), "=r"(r[96]), "=r"(r[97]), "=r"(r[98]), "=r"(r[99]), "=r"(r[100]), "=r"(r[101]), "=r"(r[102]), "=r"(r[103]), "=r"(r[104]), "=r"(r[105]), "=r"(r[106]), "=r"(r[107]), "=r"(r[108]), "=r"(r[109]), "=r"(r[110]), "=r"(r[111]), "=r"(r[112]), "=r"(r[113]), "=r"(r[114]), "=r"(r[115]), "=r"(r[116]), "=r"(r[117]), "=r"(r[118]), "=r"(r[119]), "=r"(r[120]), "=r"(r[121]), "=r"(r[122]), "=r"(r[123]), "=r"(r[124]), "=r"(r[125]), "=r"(r[126]), "=r"(r[127])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ float to_tf32(float x) {
     uint32_t r;
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
@@ -389,6 +398,444 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// =================================================================================================
+// Dense ADSampling chain on the tensor cores (pruned assignment without candidate lists).
+//
+// For a tile of 128 points and a chunk of 1024 centroids the reference evaluates, for every pair,
+// a sequence of tests "partial distance < best * ratio[dimensions seen]": after the first d'
+// dimensions, after every further 64 horizontal dimensions, and after the remaining vertical
+// dimensions (pdx/pdxearch.h:118-217); `best` is fixed inside the chunk and lowered at its end
+// (:290-324).  Here the partial distances come from accumulators that keep growing along that same
+// order of dimensions: the MMA warp walks the reduction dimension segment by segment and publishes
+// the accumulator after each one; the epilogue thread of a row reads it (without clearing it), turns
+// it into ||x||^2 + ||c||^2 - 2 x.c over the dimensions seen so far with precomputed cumulative norms,
+// and updates a bit mask of surviving centroids.  Two 256-centroid tiles are in flight on the two
+// accumulators, so the tensor pipe works on one while the other is being tested.  Every quantity a
+// row needs (survivor mask, survivor count, chunk minimum) is private to its thread.
+// =================================================================================================
+struct ChainParams {
+    size_t n, k;
+    uint32_t d, partial_d, vertical_d, horizontal_d;
+    uint32_t n_seg;                 // 1 + horizontal_d / 64 + (partial_d < vertical_d)
+    const float* chain_norms_x;     // n x n_seg cumulative squared norms of the points
+    const float* chain_norms_y;     // n_seg x k (checkpoint-major), of the centroids
+    const float* ratios;            // d + 1
+    const float* best_in;           // exact distance to the previous centroid
+    uint32_t* knn;                  // in: previous assignment, out: new
+    float* dist;
+    uint32_t* not_pruned;
+    uint2* top2;                    // out: the two smallest final distances seen by the chain, per point
+    int* error;
+};
+
+struct SegInfo {
+    uint32_t x_begin;   // first column fetched (multiple of 4)
+    uint32_t n_kb;      // 16-column blocks
+    uint32_t map;       // 0 = front (extent d'), 1 = vertical (extent vertical_d), 2 = full
+    uint32_t mask_below;  // columns below this value are zeroed in the first block (tail segment only)
+    uint32_t dims_after;
+};
+
+__device__ __forceinline__ SegInfo chain_segment(const ChainParams& p, uint32_t seg) {
+    SegInfo s;
+    const uint32_t n_h = p.horizontal_d / 64;
+    if (seg == 0) {
+        s.x_begin = 0;
+        s.n_kb = (p.partial_d + BK - 1) / BK;
+        s.map = 0;
+        s.mask_below = 0;
+        s.dims_after = p.partial_d;
+    } else if (seg <= n_h) {
+        s.x_begin = p.vertical_d + (seg - 1) * 64;
+        s.n_kb = 64 / BK;
+        s.map = 2;
+        s.mask_below = 0;
+        s.dims_after = p.partial_d + seg * 64;
+    } else {
+        s.x_begin = p.partial_d & ~3u;
+        s.n_kb = (p.vertical_d - s.x_begin + BK - 1) / BK;
+        s.map = 1;
+        s.mask_below = p.partial_d;
+        s.dims_after = p.d;
+    }
+    return s;
+}
+
+struct ChainMaps {
+    CUtensorMap x[3];
+    CUtensorMap y[3];
+};
+
+// Chain kernel geometry: 128 x 128 tiles (one x128 tensor-memory load brings a row's whole tile into
+// registers), six stages of {X hi, X lo, Y hi, Y lo}.
+constexpr int CBN = 128;
+constexpr int CSTAGES = 6;
+constexpr uint32_t C_TILE_BYTES = 128 * BK * 4;            // 8192 for X and for Y
+constexpr uint32_t CSTAGE_BYTES = 4 * C_TILE_BYTES;        // 32768
+constexpr uint32_t C_OFF_A_HI = 0, C_OFF_A_LO = C_TILE_BYTES, C_OFF_B_HI = 2 * C_TILE_BYTES, C_OFF_B_LO = 3 * C_TILE_BYTES;
+constexpr uint32_t C_SMEM_BYTES = CSTAGES * CSTAGE_BYTES + SMEM_CTRL_BYTES + 1024;
+constexpr uint32_t C_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((CBN >> 3) << 17) | ((BM >> 4) << 24);
+
+struct ChainCtrl {
+    uint64_t full[CSTAGES];
+    uint64_t conv[CSTAGES];
+    uint64_t empty[CSTAGES];
+    uint64_t acc_ready;    // MMA -> epilogue: the accumulator holds the chain up to this segment
+    uint64_t acc_loaded;   // epilogue -> MMA: every row has copied it to registers
+    uint32_t tmem_base;
+    uint32_t pad;
+    float ny[4][CBN];      // per epilogue warp: centroid norms of the current checkpoint
+};
+static_assert(sizeof(ChainCtrl) <= SMEM_CTRL_BYTES, "control block too large");
+
+__device__ __forceinline__ void umma_tf32_n128(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(C_IDESC), "r"(accumulate)
+        : "memory");
+}
+
+// Work units, walked identically by all roles: row tile -> chunk of 1024 centroids -> 128-centroid tile
+// -> segment of the chain.  The MMA warp issues a segment only after the epilogue has copied the
+// previous unit's accumulator to registers: tensor-memory loads queue behind MMAs already issued, so
+// letting the next unit's MMAs go first would stall every load for the length of a segment.
+__global__ void __launch_bounds__(NUM_THREADS, 1) chain_tc_kernel(const __grid_constant__ ChainMaps maps, const ChainParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t* smem = smem_raw + pad;
+    const uint32_t smem_base = raw_addr + pad;
+    ChainCtrl* ctrl = reinterpret_cast<ChainCtrl*>(smem + CSTAGES * CSTAGE_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < CSTAGES; ++s) {
+            mbar_init(&ctrl->full[s], 1);
+            mbar_init(&ctrl->conv[s], 128);
+            mbar_init(&ctrl->empty[s], 1);
+        }
+        mbar_init(&ctrl->acc_ready, 1);
+        mbar_init(&ctrl->acc_loaded, 128);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_proxy_async();
+    }
+    if (warp == 1) tmem_alloc(&ctrl->tmem_base, 128);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctrl->tmem_base;
+
+    const size_t n_row_tiles = (p.n + BM - 1) / BM;
+    const uint32_t n_chunks = static_cast<uint32_t>((p.k + kChunk - 1) / kChunk);
+
+#define CHAIN_FOR_EACH_UNIT(...)                                                                         \
+    for (size_t rt = blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {                              \
+        for (uint32_t chunk = 0; chunk < n_chunks && ok; ++chunk) {                                      \
+            const size_t c0 = static_cast<size_t>(chunk) * kChunk;                                       \
+            const uint32_t cs = static_cast<uint32_t>(min(static_cast<size_t>(kChunk), p.k - c0));       \
+            const uint32_t n_tiles = (cs + CBN - 1) / CBN;                                               \
+            for (uint32_t tile = 0; tile < n_tiles && ok; ++tile) {                                      \
+                for (uint32_t seg = 0; seg < p.n_seg && ok; ++seg) {                                     \
+                    const SegInfo si = chain_segment(p, seg);                                            \
+                    __VA_ARGS__                                                                          \
+                }                                                                                        \
+            }                                                                                            \
+        }                                                                                                \
+    }
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t kbt = 0;
+            bool ok = true;
+            CHAIN_FOR_EACH_UNIT({
+                const CUtensorMap* mx = &maps.x[si.map];
+                const CUtensorMap* my = &maps.y[si.map];
+                for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
+                    const uint32_t s = kbt % CSTAGES, ph = (kbt / CSTAGES) & 1u;
+                    if (!mbar_wait(&ctrl->empty[s], ph ^ 1u, p.error, 11)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&ctrl->full[s], 2 * C_TILE_BYTES);
+                    const uint32_t st = smem_base + s * CSTAGE_BYTES;
+                    const int xc = static_cast<int>(si.x_begin + kb * BK);
+                    tma_load_2d(st + C_OFF_A_HI, mx, &ctrl->full[s], xc, static_cast<int>(rt * BM));
+                    tma_load_2d(st + C_OFF_B_HI, my, &ctrl->full[s], xc, static_cast<int>(c0 + tile * CBN));
+                }
+            })
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t kbt = 0, unit = 0;
+            bool ok = true;
+            CHAIN_FOR_EACH_UNIT({
+                if (unit > 0 && !mbar_wait(&ctrl->acc_loaded, (unit - 1) & 1u, p.error, 12)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
+                    const uint32_t s = kbt % CSTAGES, ph = (kbt / CSTAGES) & 1u;
+                    if (!mbar_wait(&ctrl->conv[s], ph, p.error, 13)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t st = smem_base + s * CSTAGE_BYTES;
+#pragma unroll
+                    for (uint32_t kk = 0; kk < BK / 8; ++kk) {
+                        const uint64_t a_hi = make_desc(st + C_OFF_A_HI + kk * 32);
+                        const uint64_t a_lo = make_desc(st + C_OFF_A_LO + kk * 32);
+                        const uint64_t b_hi = make_desc(st + C_OFF_B_HI + kk * 32);
+                        const uint64_t b_lo = make_desc(st + C_OFF_B_LO + kk * 32);
+                        umma_tf32_n128(tmem_base, a_hi, b_hi, (seg | kb | kk) != 0 ? 1u : 0u);
+                        umma_tf32_n128(tmem_base, a_hi, b_lo, 1u);
+                        umma_tf32_n128(tmem_base, a_lo, b_hi, 1u);
+                    }
+                    umma_commit(&ctrl->empty[s]);
+                }
+                if (ok) umma_commit(&ctrl->acc_ready);
+                ++unit;
+            })
+        }
+    } else if (warp < 6) {
+        const int cid = threadIdx.x - 64;
+        uint32_t kbt = 0;
+        bool ok = true;
+        CHAIN_FOR_EACH_UNIT({
+            for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
+                const uint32_t s = kbt % CSTAGES, ph = (kbt / CSTAGES) & 1u;
+                if (!mbar_wait(&ctrl->full[s], ph, p.error, 14)) {
+                    ok = false;
+                    break;
+                }
+                uint8_t* st = smem + s * CSTAGE_BYTES;
+                float4* a_hi = reinterpret_cast<float4*>(st + C_OFF_A_HI);
+                float4* a_lo = reinterpret_cast<float4*>(st + C_OFF_A_LO);
+                float4* b_hi = reinterpret_cast<float4*>(st + C_OFF_B_HI);
+                float4* b_lo = reinterpret_cast<float4*>(st + C_OFF_B_LO);
+                const bool mask = (kb == 0) && (si.mask_below > si.x_begin);
+#pragma unroll
+                for (int i = 0; i < static_cast<int>(C_TILE_BYTES / 16 / 128); ++i) {
+                    const int q = cid + 128 * i;
+                    float4 v = a_hi[q];
+                    if (mask) {
+                        // 64-byte swizzle: 16-byte unit u of row r sits at unit u ^ ((r >> 1) & 3)
+                        const int r = q >> 2;
+                        const uint32_t col = si.x_begin + 4u * static_cast<uint32_t>((q & 3) ^ ((r >> 1) & 3));
+                        if (col + 0 < si.mask_below) v.x = 0.f;
+                        if (col + 1 < si.mask_below) v.y = 0.f;
+                        if (col + 2 < si.mask_below) v.z = 0.f;
+                        if (col + 3 < si.mask_below) v.w = 0.f;
+                    }
+                    float4 hi, lo;
+                    split4(v, hi, lo);
+                    a_hi[q] = hi;
+                    a_lo[q] = lo;
+                    split4(b_hi[q], hi, lo);
+                    b_hi[q] = hi;
+                    b_lo[q] = lo;
+                }
+                fence_proxy_async();
+                mbar_arrive(&ctrl->conv[s]);
+            }
+        })
+    } else {
+        const uint32_t lane_base = 32u * (warp & 3);
+        const uint32_t row_in_tile = lane_base + lane;
+        uint32_t unit = 0;
+        bool ok = true;
+        // per-row state (private to this thread)
+        size_t cur_rt = ~size_t{0};
+        uint32_t cur_chunk = 0xFFFFFFFFu;
+        size_t row = 0;
+        bool row_valid = false;
+        float best = -1.f, cb = FLT_MAX, t1 = FLT_MAX, t2 = FLT_MAX;
+        uint32_t bestidx = 0, prev = 0xFFFFFFFFu, npc = 0, cnt = 0, cbi = 0, i1 = 0xFFFFFFFFu, i2 = 0xFFFFFFFFu;
+        bool prev_first = false;
+        uint32_t alive[CBN / 32] = {0, 0, 0, 0};
+        float* ny = ctrl->ny[warp & 3];
+        auto close_chunk = [&]() {
+            npc += cnt;
+            // pdxearch.h:140-143: the previous centroid as the only survivor leaves the candidate untouched
+            if (cb < FLT_MAX && !(cnt == 1u && prev_first)) {
+                best = cb;
+                bestidx = cbi;
+            }
+            cnt = 0;
+            prev_first = false;
+            cb = FLT_MAX;
+            cbi = 0;
+        };
+        auto close_row = [&]() {
+            if (row_valid) {
+                p.knn[row] = bestidx;
+                p.dist[row] = best;
+                p.not_pruned[row] = npc;
+                p.top2[row] = make_uint2(i1, i2);
+            }
+        };
+        CHAIN_FOR_EACH_UNIT({
+            if (rt != cur_rt) {
+                if (cur_rt != ~size_t{0}) {
+                    close_chunk();
+                    close_row();
+                }
+                cur_rt = rt;
+                cur_chunk = chunk;
+                row = rt * BM + row_in_tile;
+                row_valid = row < p.n;
+                best = row_valid ? p.best_in[row] : -1.f;
+                prev = row_valid ? p.knn[row] : 0xFFFFFFFFu;
+                bestidx = row_valid ? prev : 0u;
+                npc = 0;
+                cnt = 0;
+                prev_first = false;
+                cb = FLT_MAX;
+                cbi = 0;
+                t1 = t2 = FLT_MAX;
+                i1 = i2 = 0xFFFFFFFFu;
+            } else if (chunk != cur_chunk) {
+                close_chunk();
+                cur_chunk = chunk;
+            }
+            const size_t col0 = c0 + static_cast<size_t>(tile) * CBN;
+            const uint32_t cols_valid = static_cast<uint32_t>(min(static_cast<size_t>(CBN), p.k - col0));
+            const float ratio = __ldg(p.ratios + si.dims_after);
+            const float thr = best * ratio;
+            const float nxv = row_valid ? __ldg(p.chain_norms_x + row * p.n_seg + seg) : 0.f;
+            const bool last = (seg + 1 == p.n_seg);
+            {
+                // this warp's copy of the tile's centroid norms at this checkpoint (fetched while the MMAs run)
+                const float* __restrict__ src = p.chain_norms_y + static_cast<size_t>(seg) * p.k + col0;
+                __syncwarp();
+                for (uint32_t j = lane; j < CBN; j += 32) ny[j] = (j < cols_valid) ? __ldg(src + j) : 0.f;
+                __syncwarp();
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->acc_ready, unit & 1u, p.error, 15))) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            uint32_t r[CBN];
+            tmem_ld128(tmem_base + (lane_base << 16), r);
+            tc_fence_before();
+            mbar_arrive(&ctrl->acc_loaded);
+            ++unit;
+            if (seg == 0) {
+#pragma unroll
+                for (uint32_t ch = 0; ch < CBN / 32; ++ch) {
+                    uint32_t word = 0;
+#pragma unroll
+                    for (uint32_t j = 0; j < 32; ++j) {
+                        const uint32_t cl = ch * 32 + j;
+                        const float pd = fmaf(-2.0f, __uint_as_float(r[cl]), nxv) + ny[cl];
+                        if (cl < cols_valid && pd < thr) {
+                            word |= 1u << j;
+                            if (static_cast<size_t>(prev) == col0 + cl) prev_first = true;
+                        }
+                    }
+                    cnt += __popc(word);
+                    alive[ch] = word;
+                }
+            } else {
+#pragma unroll
+                for (uint32_t ch = 0; ch < CBN / 32; ++ch) {
+                    uint32_t word = alive[ch];
+                    if (word == 0u) continue;
+#pragma unroll
+                    for (uint32_t j = 0; j < 32; ++j) {
+                        if (word & (1u << j)) {
+                            const uint32_t cl = ch * 32 + j;
+                            const float pd = fmaf(-2.0f, __uint_as_float(r[cl]), nxv) + ny[cl];
+                            if (last && pd < t2) {
+                                // runner-ups by the chain's own (slightly truncated) distances; the fp32
+                                // refinement afterwards decides among them and the chain's winner
+                                if (pd < t1) {
+                                    t2 = t1;
+                                    i2 = i1;
+                                    t1 = pd;
+                                    i1 = static_cast<uint32_t>(col0 + cl);
+                                } else {
+                                    t2 = pd;
+                                    i2 = static_cast<uint32_t>(col0 + cl);
+                                }
+                            }
+                            if (!(pd < thr)) {
+                                word &= ~(1u << j);
+                            } else if (last && pd < cb) {  // thr == best here (ratio[d] == 1)
+                                cb = pd;
+                                cbi = static_cast<uint32_t>(col0 + cl);
+                            }
+                        }
+                    }
+                    alive[ch] = word;
+                }
+            }
+        })
+        if (ok && cur_rt != ~size_t{0}) {
+            close_chunk();
+            close_row();
+        }
+    }
+#undef CHAIN_FOR_EACH_UNIT
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 128);
+}
+
+// After the chain: the exact squared distance (direct differences, fp32) of a point to the chain's
+// winner and to the two runner-ups; the smallest wins, the winner keeps its place on ties.
+__global__ void __launch_bounds__(256) refine_chain_kernel(const float* __restrict__ x, const float* __restrict__ y, size_t n, size_t d, const uint2* __restrict__ top2,
+                                                           uint32_t* __restrict__ knn, float* __restrict__ dist) {
+    const size_t row = static_cast<size_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (row >= n) return;
+    const int lane = threadIdx.x & 31;
+    const uint32_t w = knn[row];
+    const uint2 t = top2[row];
+    uint32_t cand[3] = {w, t.x, t.y};
+    if (cand[1] == 0xFFFFFFFFu || cand[1] == w) cand[1] = w;
+    if (cand[2] == 0xFFFFFFFFu || cand[2] == w) cand[2] = w;
+    const float* xr = x + row * d;
+    const float* y0 = y + static_cast<size_t>(cand[0]) * d;
+    const float* y1 = y + static_cast<size_t>(cand[1]) * d;
+    const float* y2 = y + static_cast<size_t>(cand[2]) * d;
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f;
+    for (size_t j = static_cast<size_t>(lane) * 4; j < d; j += 128) {
+        const float4 xv = __ldg(reinterpret_cast<const float4*>(xr + j));
+        const float4 a = __ldg(reinterpret_cast<const float4*>(y0 + j));
+        const float4 b = __ldg(reinterpret_cast<const float4*>(y1 + j));
+        const float4 c = __ldg(reinterpret_cast<const float4*>(y2 + j));
+        float u;
+        u = xv.x - a.x; s0 = fmaf(u, u, s0); u = xv.y - a.y; s0 = fmaf(u, u, s0); u = xv.z - a.z; s0 = fmaf(u, u, s0); u = xv.w - a.w; s0 = fmaf(u, u, s0);
+        u = xv.x - b.x; s1 = fmaf(u, u, s1); u = xv.y - b.y; s1 = fmaf(u, u, s1); u = xv.z - b.z; s1 = fmaf(u, u, s1); u = xv.w - b.w; s1 = fmaf(u, u, s1);
+        u = xv.x - c.x; s2 = fmaf(u, u, s2); u = xv.y - c.y; s2 = fmaf(u, u, s2); u = xv.z - c.z; s2 = fmaf(u, u, s2); u = xv.w - c.w; s2 = fmaf(u, u, s2);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
+    if (lane == 0) {
+        uint32_t bi = cand[0];
+        float bd = s0;
+        if (s1 < bd || (s1 == bd && cand[1] < bi && cand[1] != w && bi != w)) {
+            bd = s1;
+            bi = cand[1];
+        }
+        if (s2 < bd || (s2 == bd && cand[2] < bi && bi != w)) {
+            bd = s2;
+            bi = cand[2];
+        }
+        knn[row] = bi;
+        dist[row] = bd;
+    }
+}
+
 // Settles the assignment in fp32: one warp per row recomputes ||x||^2 + ||y||^2 - 2 x.y for the two
 // candidates with fp32 fused multiply-adds, keeps the smaller (the lower index on a tie) and stores
 // the distance clamped at zero, as the reference does (batch_computers.h:160-166).
@@ -422,7 +869,19 @@ __global__ void __launch_bounds__(256) refine_top2_kernel(
         float e1 = fmaf(-2.0f, a1, nx) + norms_y[cand.x];
         uint32_t w = cand.x;
         if (two) {
-            const float e2 = fmaf(-2.0f, a2, nx) + norms_y[cand.y];
+            float e2 = fmaf(-2.0f, a2, nx) + norms_y[cand.y];
+            if (fabsf(e1 - e2) <= 1e-4f * fmaxf(fabsf(e1), fabsf(e2))) {
+                // Near-tie (typically the twin centroids left by a cluster split): settle it with the dot
+                // products accumulated strictly in index order, the order of the fp32 SIMT kernel.
+                float s1 = 0.f, s2 = 0.f;
+                for (size_t j = 0; j < d; ++j) {
+                    const float xv = xr[j];
+                    s1 = fmaf(xv, y1[j], s1);
+                    s2 = fmaf(xv, y2[j], s2);
+                }
+                e1 = fmaf(-2.0f, s1, nx) + norms_y[cand.x];
+                e2 = fmaf(-2.0f, s2, nx) + norms_y[cand.y];
+            }
             if (e2 < e1 || (e2 == e1 && cand.y < cand.x)) {
                 e1 = e2;
                 w = cand.y;
@@ -549,6 +1008,46 @@ void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, floa
     p.ldo = ldo;
     p.error = error_flag(device);
     launch<MODE_STORE>(tx, ty, p, stream);
+}
+
+void launch_chain(const float* x, const float* y, size_t n, size_t k, size_t d, uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d, const float* chain_norms_x,
+                  const float* chain_norms_y, const float* ratios, const float* best_in, uint32_t* knn, float* dist, uint32_t* not_pruned, uint2* top2_scratch,
+                  cudaStream_t stream) {
+    if (n == 0 || k == 0) return;
+    int device = 0;
+    SKM_CUDA(cudaGetDevice(&device));
+    ChainMaps maps;
+    const size_t extents[3] = {partial_d, vertical_d, d};
+    for (int i = 0; i < 3; ++i) {
+        maps.x[i] = make_tmap(x, extents[i], n, d, BM);
+        maps.y[i] = make_tmap(y, extents[i], k, d, CBN);
+    }
+    ChainParams p{};
+    p.n = n;
+    p.k = k;
+    p.d = static_cast<uint32_t>(d);
+    p.partial_d = partial_d;
+    p.vertical_d = vertical_d;
+    p.horizontal_d = horizontal_d;
+    p.n_seg = 1u + horizontal_d / 64u + (partial_d < vertical_d ? 1u : 0u);
+    p.chain_norms_x = chain_norms_x;
+    p.chain_norms_y = chain_norms_y;
+    p.ratios = ratios;
+    p.best_in = best_in;
+    p.knn = knn;
+    p.dist = dist;
+    p.not_pruned = not_pruned;
+    p.top2 = top2_scratch;
+    p.error = error_flag(device);
+    SKM_CUDA(cudaFuncSetAttribute(chain_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(C_SMEM_BYTES)));
+    const size_t row_tiles = (n + BM - 1) / BM;
+    const int grid = static_cast<int>(std::min<size_t>(row_tiles, static_cast<size_t>(sm_count(device))));
+    chain_tc_kernel<<<grid, NUM_THREADS, C_SMEM_BYTES, stream>>>(maps, p);
+    note_kernel_launch();
+    SKM_CUDA(cudaGetLastError());
+    refine_chain_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, d, top2_scratch, knn, dist);
+    note_kernel_launch();
+    SKM_CUDA(cudaGetLastError());
 }
 
 // Reads (and clears) the error code left by the last kernels on this device.  Synchronises `stream`.

@@ -22,6 +22,15 @@ void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size
                         uint2* top2_scratch, cudaStream_t stream);
 void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, float* out, size_t ldo, size_t n, size_t n_out, size_t k_dim, cudaStream_t stream);
 
+// Pruned assignment for all n points as a dense ADSampling chain on the tensor cores.  chain_norms_x /
+// chain_norms_y hold, per row, the cumulative squared norm after each of the chain's checkpoints
+// (launch_chain_norms; point norms row-major, centroid norms checkpoint-major); best_in the exact distance to the previous centroid; knn the previous
+// assignment on entry and the new one on return.  The winner is settled, and its distance recomputed, in
+// fp32 among the chain's winner and its two runner-ups (top2_scratch: n entries).
+void launch_chain(const float* x, const float* y, size_t n, size_t k, size_t d, uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d, const float* chain_norms_x,
+                  const float* chain_norms_y, const float* ratios, const float* best_in, uint32_t* knn, float* dist, uint32_t* not_pruned, uint2* top2_scratch,
+                  cudaStream_t stream);
+
 // Error code (0 = none) recorded by a kernel whose bounded wait expired; clears it.  Synchronises.
 int fetch_error(cudaStream_t stream);
 

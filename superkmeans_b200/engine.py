@@ -51,7 +51,8 @@ class Engine:
         self.n_trained = 0
 
     def close(self):
-        if getattr(self, "_h", None):
+        # `lib` may already be gone when the interpreter is shutting down
+        if getattr(self, "_h", None) and lib is not None:
             lib.skm_destroy(self._h)
             self._h = None
 
@@ -198,6 +199,11 @@ def set_tensor_cores(enabled: bool) -> None:
 
 def tensor_cores_enabled() -> bool:
     return bool(lib.skm_get_tensor_cores())
+
+
+def set_prune_split(mode: int) -> None:
+    """0 = split points between the two pruned kernels automatically, 1 = candidate lists only, 2 = dense only."""
+    lib.skm_set_prune_split(int(mode))
 
 
 def kernel_launches() -> int:

@@ -112,9 +112,21 @@ def _trace(ref, n, d, k, iters, seed, hier=False, centers=None, **kw):
     return x, km, cent
 
 
+@pytest.mark.parametrize("split_mode", [0, 1, 2, 3], ids=["auto", "lists_only", "dense_simt_only", "tensor_core_chain"])
 @pytest.mark.parametrize("n,d,k", [(20000, 256, 512), (12000, 768, 1500), (6000, 130, 1030), (9000, 1024, 2100)])
-def test_pruned_step_matches_reference_teacher_forced(eng, ref, n, d, k):
-    """Every pruned iteration of a reference run, replayed from the reference's own inputs."""
+def test_pruned_step_matches_reference_teacher_forced(eng, ref, n, d, k, split_mode):
+    """Every pruned iteration of a reference run, replayed from the reference's own inputs, with the
+    points routed through the candidate-list kernel, the dense-chain kernel, or split between them."""
+    if split_mode == 3 and d % 4 != 0:
+        pytest.skip("the tensor-core chain needs d % 4 == 0")
+    eng.set_prune_split(split_mode)
+    try:
+        _pruned_step_check(eng, ref, n, d, k)
+    finally:
+        eng.set_prune_split(0)
+
+
+def _pruned_step_check(eng, ref, n, d, k):
     x, km, _ = _trace(ref, n, d, k, 5, 17)
     m = km.rotation_matrix()
     xr = eng.rotate(m, x)
