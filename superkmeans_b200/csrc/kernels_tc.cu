@@ -21,6 +21,8 @@
 #include <cuda.h>
 
 #include <cfloat>
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -426,6 +428,7 @@ struct ChainParams {
     uint32_t* not_pruned;
     uint2* top2;                    // out: the two smallest final distances seen by the chain, per point
     int* error;
+    long long* dbg;                 // optional cycle counters of CTA 0 (profiling aid), 16 slots
 };
 
 struct SegInfo {
@@ -484,7 +487,8 @@ struct ChainCtrl {
     uint64_t acc_loaded;   // epilogue -> MMA: every row has copied it to registers
     uint32_t tmem_base;
     uint32_t pad;
-    float ny[4][CBN];      // per epilogue warp: centroid norms of the current checkpoint
+    alignas(16) float ny[4][CBN];  // per epilogue warp: centroid norms of the current checkpoint (read as float4)
+    float seg_ratio[64];           // ratios[dimensions seen after segment s]
 };
 static_assert(sizeof(ChainCtrl) <= SMEM_CTRL_BYTES, "control block too large");
 
@@ -521,6 +525,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) chain_tc_kernel(const __grid_c
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
     }
+    if (threadIdx.x >= 64 && threadIdx.x < 64 + 64 && threadIdx.x - 64 < p.n_seg) {
+        ctrl->seg_ratio[threadIdx.x - 64] = __ldg(p.ratios + chain_segment(p, threadIdx.x - 64).dims_after);
+    }
     if (warp == 1) tmem_alloc(&ctrl->tmem_base, 128);
     tc_fence_before();
     __syncthreads();
@@ -549,15 +556,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) chain_tc_kernel(const __grid_c
         if (lane == 0) {
             uint32_t kbt = 0;
             bool ok = true;
+            long long p_wait_empty = 0;
             CHAIN_FOR_EACH_UNIT({
                 const CUtensorMap* mx = &maps.x[si.map];
                 const CUtensorMap* my = &maps.y[si.map];
                 for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
                     const uint32_t s = kbt % CSTAGES, ph = (kbt / CSTAGES) & 1u;
+                    const long long tp0 = clock64();
                     if (!mbar_wait(&ctrl->empty[s], ph ^ 1u, p.error, 11)) {
                         ok = false;
                         break;
                     }
+                    p_wait_empty += clock64() - tp0;
                     mbar_arrive_expect_tx(&ctrl->full[s], 2 * C_TILE_BYTES);
                     const uint32_t st = smem_base + s * CSTAGE_BYTES;
                     const int xc = static_cast<int>(si.x_begin + kb * BK);
@@ -565,23 +575,29 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) chain_tc_kernel(const __grid_c
                     tma_load_2d(st + C_OFF_B_HI, my, &ctrl->full[s], xc, static_cast<int>(c0 + tile * CBN));
                 }
             })
+            if (p.dbg && blockIdx.x == 0) p.dbg[9] = p_wait_empty;
         }
     } else if (warp == 1) {
         if (lane == 0) {
             uint32_t kbt = 0, unit = 0;
             bool ok = true;
+            long long m_wait_loaded = 0, m_wait_conv = 0;
             CHAIN_FOR_EACH_UNIT({
+                const long long tm0 = clock64();
                 if (unit > 0 && !mbar_wait(&ctrl->acc_loaded, (unit - 1) & 1u, p.error, 12)) {
                     ok = false;
                     break;
                 }
+                m_wait_loaded += clock64() - tm0;
                 tc_fence_after();
                 for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
                     const uint32_t s = kbt % CSTAGES, ph = (kbt / CSTAGES) & 1u;
+                    const long long tm1 = clock64();
                     if (!mbar_wait(&ctrl->conv[s], ph, p.error, 13)) {
                         ok = false;
                         break;
                     }
+                    m_wait_conv += clock64() - tm1;
                     tc_fence_after();
                     const uint32_t st = smem_base + s * CSTAGE_BYTES;
 #pragma unroll
@@ -599,18 +615,25 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) chain_tc_kernel(const __grid_c
                 if (ok) umma_commit(&ctrl->acc_ready);
                 ++unit;
             })
+            if (p.dbg && blockIdx.x == 0) {
+                p.dbg[4] = m_wait_loaded;
+                p.dbg[5] = m_wait_conv;
+            }
         }
     } else if (warp < 6) {
         const int cid = threadIdx.x - 64;
         uint32_t kbt = 0;
         bool ok = true;
+        long long s_wait_full = 0, s_total0 = clock64();
         CHAIN_FOR_EACH_UNIT({
             for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
                 const uint32_t s = kbt % CSTAGES, ph = (kbt / CSTAGES) & 1u;
+                const long long ts0 = clock64();
                 if (!mbar_wait(&ctrl->full[s], ph, p.error, 14)) {
                     ok = false;
                     break;
                 }
+                s_wait_full += clock64() - ts0;
                 uint8_t* st = smem + s * CSTAGE_BYTES;
                 float4* a_hi = reinterpret_cast<float4*>(st + C_OFF_A_HI);
                 float4* a_lo = reinterpret_cast<float4*>(st + C_OFF_A_LO);
@@ -642,6 +665,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) chain_tc_kernel(const __grid_c
                 mbar_arrive(&ctrl->conv[s]);
             }
         })
+        if (p.dbg && blockIdx.x == 0 && cid == 0) {
+            p.dbg[6] = s_wait_full;
+            p.dbg[7] = clock64() - s_total0;
+            p.dbg[8] = kbt;
+        }
     } else {
         const uint32_t lane_base = 32u * (warp & 3);
         const uint32_t row_in_tile = lane_base + lane;
@@ -657,6 +685,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) chain_tc_kernel(const __grid_c
         bool prev_first = false;
         uint32_t alive[CBN / 32] = {0, 0, 0, 0};
         float* ny = ctrl->ny[warp & 3];
+        long long dbg_wait = 0, dbg_ld = 0, dbg_other = 0, dbg_prev = clock64();
+        float nx_row[64];          // cumulative norms of this thread's row, one per checkpoint
+        float ny_next[CBN / 32];   // centroid norms of the next unit, fetched one unit ahead
+        bool ny_next_valid = false;
+        // centroid norms of unit (rt, chunk, tile, seg) for this lane: columns lane, lane+32, ...
+        auto fetch_ny = [&](uint32_t chunk_, uint32_t tile_, uint32_t seg_, float (&dst)[CBN / 32]) {
+            const size_t col0_ = static_cast<size_t>(chunk_) * kChunk + static_cast<size_t>(tile_) * CBN;
+            const float* __restrict__ src = p.chain_norms_y + static_cast<size_t>(seg_) * p.k + col0_;
+#pragma unroll
+            for (uint32_t q = 0; q < CBN / 32; ++q) dst[q] = (col0_ + q * 32 + lane < p.k) ? __ldg(src + q * 32 + lane) : 0.f;
+        };
         auto close_chunk = [&]() {
             npc += cnt;
             // pdxearch.h:140-143: the previous centroid as the only survivor leaves the candidate untouched
@@ -697,87 +736,142 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) chain_tc_kernel(const __grid_c
                 cbi = 0;
                 t1 = t2 = FLT_MAX;
                 i1 = i2 = 0xFFFFFFFFu;
+                for (uint32_t q = 0; q < p.n_seg; ++q) nx_row[q] = row_valid ? __ldg(p.chain_norms_x + row * p.n_seg + q) : 0.f;
             } else if (chunk != cur_chunk) {
                 close_chunk();
                 cur_chunk = chunk;
             }
             const size_t col0 = c0 + static_cast<size_t>(tile) * CBN;
             const uint32_t cols_valid = static_cast<uint32_t>(min(static_cast<size_t>(CBN), p.k - col0));
-            const float ratio = __ldg(p.ratios + si.dims_after);
-            const float thr = best * ratio;
-            const float nxv = row_valid ? __ldg(p.chain_norms_x + row * p.n_seg + seg) : 0.f;
+            const float thr = best * ctrl->seg_ratio[seg];
+            const float nxv = nx_row[seg];
             const bool last = (seg + 1 == p.n_seg);
             {
-                // this warp's copy of the tile's centroid norms at this checkpoint (fetched while the MMAs run)
-                const float* __restrict__ src = p.chain_norms_y + static_cast<size_t>(seg) * p.k + col0;
+                // this warp's copy of the tile's centroid norms at this checkpoint
+                float cur[CBN / 32];
+                if (ny_next_valid) {
+#pragma unroll
+                    for (uint32_t q = 0; q < CBN / 32; ++q) cur[q] = ny_next[q];
+                } else {
+                    fetch_ny(chunk, tile, seg, cur);
+                }
                 __syncwarp();
-                for (uint32_t j = lane; j < CBN; j += 32) ny[j] = (j < cols_valid) ? __ldg(src + j) : 0.f;
+#pragma unroll
+                for (uint32_t q = 0; q < CBN / 32; ++q) ny[q * 32 + lane] = cur[q];
                 __syncwarp();
+                // next unit: next segment of this tile, else the first segment of the next tile / chunk; a new
+                // row tile starts with a plain fetch
+                uint32_t nseg = seg + 1, ntile = tile, nchunk = chunk;
+                ny_next_valid = true;
+                if (nseg == p.n_seg) {
+                    nseg = 0;
+                    if (++ntile == n_tiles) {
+                        ntile = 0;
+                        if (++nchunk == n_chunks) ny_next_valid = false;
+                    }
+                }
+                if (ny_next_valid) fetch_ny(nchunk, ntile, nseg, ny_next);
             }
+            const long long tq0 = clock64();
             if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->acc_ready, unit & 1u, p.error, 15))) {
                 ok = false;
                 break;
             }
+            const long long tq1 = clock64();
             tc_fence_after();
             uint32_t r[CBN];
             tmem_ld128(tmem_base + (lane_base << 16), r);
             tc_fence_before();
             mbar_arrive(&ctrl->acc_loaded);
+            const long long tq2 = clock64();
+            dbg_wait += tq1 - tq0;
+            dbg_ld += tq2 - tq1;
+            dbg_other += tq0 - dbg_prev;
+            dbg_prev = tq2;
             ++unit;
+            // Branch-free pass over the 128 columns: bit j of pass[ch] = (partial distance < threshold).
+            // (A per-column branch would be taken by some lane almost always and its unrolled body does not
+            // fit the instruction cache; this form is ~5 instructions per column.)
+            uint32_t pass[CBN / 32];
+            float pdv[CBN];
+#pragma unroll
+            for (uint32_t ch = 0; ch < CBN / 32; ++ch) {
+                uint32_t w = 0;
+#pragma unroll
+                for (uint32_t j = 0; j < 32; j += 4) {
+                    const uint32_t cl = ch * 32 + j;
+                    const float4 nyv = *reinterpret_cast<const float4*>(ny + cl);
+                    const float p0 = fmaf(-2.0f, __uint_as_float(r[cl + 0]), nxv) + nyv.x;
+                    const float p1 = fmaf(-2.0f, __uint_as_float(r[cl + 1]), nxv) + nyv.y;
+                    const float p2 = fmaf(-2.0f, __uint_as_float(r[cl + 2]), nxv) + nyv.z;
+                    const float p3 = fmaf(-2.0f, __uint_as_float(r[cl + 3]), nxv) + nyv.w;
+                    w |= (p0 < thr ? (1u << j) : 0u) | (p1 < thr ? (2u << j) : 0u) | (p2 < thr ? (4u << j) : 0u) | (p3 < thr ? (8u << j) : 0u);
+                    if (last) {
+                        pdv[cl + 0] = p0;
+                        pdv[cl + 1] = p1;
+                        pdv[cl + 2] = p2;
+                        pdv[cl + 3] = p3;
+                    }
+                }
+                pass[ch] = w;
+            }
             if (seg == 0) {
 #pragma unroll
                 for (uint32_t ch = 0; ch < CBN / 32; ++ch) {
-                    uint32_t word = 0;
-#pragma unroll
-                    for (uint32_t j = 0; j < 32; ++j) {
-                        const uint32_t cl = ch * 32 + j;
-                        const float pd = fmaf(-2.0f, __uint_as_float(r[cl]), nxv) + ny[cl];
-                        if (cl < cols_valid && pd < thr) {
-                            word |= 1u << j;
-                            if (static_cast<size_t>(prev) == col0 + cl) prev_first = true;
-                        }
-                    }
-                    cnt += __popc(word);
-                    alive[ch] = word;
+                    const uint32_t lo = ch * 32;
+                    const uint32_t valid = (cols_valid >= lo + 32) ? 0xFFFFFFFFu : (cols_valid > lo ? ((1u << (cols_valid - lo)) - 1u) : 0u);
+                    alive[ch] = pass[ch] & valid;
+                    cnt += __popc(alive[ch]);
                 }
+                if (static_cast<size_t>(prev) >= col0 && static_cast<size_t>(prev) < col0 + cols_valid) {
+                    const uint32_t pl = static_cast<uint32_t>(prev - col0);
+                    if ((alive[pl >> 5] >> (pl & 31)) & 1u) prev_first = true;
+                }
+            } else if (!last) {
+#pragma unroll
+                for (uint32_t ch = 0; ch < CBN / 32; ++ch) alive[ch] &= pass[ch];
             } else {
-#pragma unroll
+                // Last checkpoint: the pairs still alive compete.  thr == best here (ratio[d] == 1).
+#pragma unroll 1
                 for (uint32_t ch = 0; ch < CBN / 32; ++ch) {
-                    uint32_t word = alive[ch];
-                    if (word == 0u) continue;
-#pragma unroll
-                    for (uint32_t j = 0; j < 32; ++j) {
-                        if (word & (1u << j)) {
-                            const uint32_t cl = ch * 32 + j;
-                            const float pd = fmaf(-2.0f, __uint_as_float(r[cl]), nxv) + ny[cl];
-                            if (last && pd < t2) {
-                                // runner-ups by the chain's own (slightly truncated) distances; the fp32
-                                // refinement afterwards decides among them and the chain's winner
-                                if (pd < t1) {
-                                    t2 = t1;
-                                    i2 = i1;
-                                    t1 = pd;
-                                    i1 = static_cast<uint32_t>(col0 + cl);
-                                } else {
-                                    t2 = pd;
-                                    i2 = static_cast<uint32_t>(col0 + cl);
-                                }
-                            }
-                            if (!(pd < thr)) {
-                                word &= ~(1u << j);
-                            } else if (last && pd < cb) {  // thr == best here (ratio[d] == 1)
-                                cb = pd;
-                                cbi = static_cast<uint32_t>(col0 + cl);
+                    uint32_t w = alive[ch];
+                    while (w) {
+                        const uint32_t j = __ffs(w) - 1;
+                        w &= w - 1;
+                        const uint32_t cl = ch * 32 + j;
+                        const float pd = pdv[cl];
+                        const uint32_t gc = static_cast<uint32_t>(col0 + cl);
+                        if (pd < t2) {
+                            // runner-ups by the chain's own (slightly truncated) distances; the fp32
+                            // refinement afterwards decides among them and the chain's winner
+                            if (pd < t1) {
+                                t2 = t1;
+                                i2 = i1;
+                                t1 = pd;
+                                i1 = gc;
+                            } else {
+                                t2 = pd;
+                                i2 = gc;
                             }
                         }
+                        if (pd < thr && pd < cb) {
+                            cb = pd;
+                            cbi = gc;
+                        }
                     }
-                    alive[ch] = word;
+                    alive[ch] &= pass[ch];
                 }
             }
         })
         if (ok && cur_rt != ~size_t{0}) {
             close_chunk();
             close_row();
+        }
+        if (p.dbg && blockIdx.x == 0 && threadIdx.x == 192) {
+            p.dbg[0] = dbg_wait;
+            p.dbg[1] = dbg_ld;
+            p.dbg[2] = dbg_other;
+            p.dbg[3] = unit;
         }
     }
 #undef CHAIN_FOR_EACH_UNIT
@@ -1039,6 +1133,14 @@ void launch_chain(const float* x, const float* y, size_t n, size_t k, size_t d, 
     p.not_pruned = not_pruned;
     p.top2 = top2_scratch;
     p.error = error_flag(device);
+    p.dbg = nullptr;
+    static long long* dbg_dev = nullptr;
+    const bool want_dbg = std::getenv("SKM_CHAIN_DEBUG") != nullptr;
+    if (want_dbg) {
+        if (!dbg_dev) SKM_CUDA(cudaMalloc(&dbg_dev, 16 * sizeof(long long)));
+        SKM_CUDA(cudaMemsetAsync(dbg_dev, 0, 16 * sizeof(long long), stream));
+        p.dbg = dbg_dev;
+    }
     SKM_CUDA(cudaFuncSetAttribute(chain_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(C_SMEM_BYTES)));
     const size_t row_tiles = (n + BM - 1) / BM;
     const int grid = static_cast<int>(std::min<size_t>(row_tiles, static_cast<size_t>(sm_count(device))));
@@ -1048,6 +1150,15 @@ void launch_chain(const float* x, const float* y, size_t n, size_t k, size_t d, 
     refine_chain_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, d, top2_scratch, knn, dist);
     note_kernel_launch();
     SKM_CUDA(cudaGetLastError());
+    if (want_dbg) {
+        long long h[16];
+        SKM_CUDA(cudaMemcpyAsync(h, dbg_dev, sizeof(h), cudaMemcpyDeviceToHost, stream));
+        SKM_CUDA(cudaStreamSynchronize(stream));
+        std::fprintf(stderr,
+                     "[chain dbg] epi: wait_ready %lld ld %lld other %lld units %lld | mma: wait_loaded %lld wait_conv %lld | split: wait_full %lld total %lld kblocks %lld | "
+                     "prod: wait_empty %lld\n",
+                     h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7], h[8], h[9]);
+    }
 }
 
 // Reads (and clears) the error code left by the last kernels on this device.  Synchronises `stream`.
