@@ -123,6 +123,9 @@ skm_status skm_get_assignments(skm_handle* h, uint32_t* out, uint64_t n);
 skm_status skm_get_distances(skm_handle* h, float* out, uint64_t n);
 /* horizontal_centroids after training: rotated-space centroids, n_clusters x d. */
 skm_status skm_get_rotated_centroids(skm_handle* h, float* out);
+/* Which kernels the last pruned assignment pass used: 0 none yet, 1 candidate lists (+ dense SIMT chain for
+ * flagged points), 3 tensor-core chain. */
+int skm_last_prune_path(const skm_handle* h);
 /* Objective of the last iteration accumulated in float64 (the reference sums float32). */
 double skm_last_objective_f64(const skm_handle* h);
 

@@ -86,6 +86,7 @@ SIGNATURES = {
     "skm_get_distances": (C.c_int, [C.c_void_p, f32p, C.c_uint64]),
     "skm_get_rotated_centroids": (C.c_int, [C.c_void_p, f32p]),
     "skm_last_objective_f64": (C.c_double, [C.c_void_p]),
+    "skm_last_prune_path": (C.c_int, [C.c_void_p]),
     "skm_set_trace": (C.c_int, [C.c_void_p, C.c_int]),
     "skm_trace_count": (C.c_uint64, [C.c_void_p]),
     "skm_trace_get": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint32), C.c_void_p, C.c_void_p, C.c_void_p,

@@ -142,6 +142,7 @@ class Engine {
     float sampling_fraction() const { return cfg_.sampling_fraction; }
     size_t n_mesoclusters_value() const { return n_meso_; }
     double last_objective_f64() const { return last_cost_f64_; }
+    int last_prune_path() const { return prune_bufs_.last_path; }
     const std::vector<skm_iter_stats>& stats(int phase) const;
     int device() const { return device_; }
     // Per-iteration snapshots for step-wise parity checks (what RunIteration leaves behind).

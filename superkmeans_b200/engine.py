@@ -132,6 +132,10 @@ class Engine:
         return int(lib.skm_n_mesoclusters(self._h))
 
     @property
+    def last_prune_path(self) -> int:
+        return int(lib.skm_last_prune_path(self._h))
+
+    @property
     def last_objective_f64(self) -> float:
         return float(lib.skm_last_objective_f64(self._h))
 

@@ -117,16 +117,18 @@ def _trace(ref, n, d, k, iters, seed, hier=False, centers=None, **kw):
 def test_pruned_step_matches_reference_teacher_forced(eng, ref, n, d, k, split_mode):
     """Every pruned iteration of a reference run, replayed from the reference's own inputs, with the
     points routed through the candidate-list kernel, the dense-chain kernel, or split between them."""
-    if split_mode == 3 and d % 4 != 0:
-        pytest.skip("the tensor-core chain needs d % 4 == 0")
+    if split_mode == 3 and (d % 4 != 0 or not eng.tensor_cores_enabled()):
+        pytest.skip("the tensor-core chain needs d % 4 == 0 and the tensor-core kernels switched on")
     eng.set_prune_split(split_mode)
     try:
-        _pruned_step_check(eng, ref, n, d, k)
+        # the tensor-memory accumulator truncates: partial distances sit ~1e-5 (relative to the dot product)
+        # high, which moves a few more pairs across the thresholds than fp32 rounding does
+        _pruned_step_check(eng, ref, n, d, k, count_tol=5e-3 if split_mode in (0, 3) else 1e-3)
     finally:
         eng.set_prune_split(0)
 
 
-def _pruned_step_check(eng, ref, n, d, k):
+def _pruned_step_check(eng, ref, n, d, k, count_tol=1e-3):
     x, km, _ = _trace(ref, n, d, k, 5, 17)
     m = km.rotation_matrix()
     xr = eng.rotate(m, x)
@@ -147,7 +149,7 @@ def _pruned_step_check(eng, ref, n, d, k):
         assert np.abs(dist[same] - rdist[same]).max() <= 2e-5 * max(1.0, float(rdist.max()))
         # not-pruned counters: integer, but each counts threshold tests on rounded partial distances
         tot, rtot = float(npc.sum()), float(rnp.sum())
-        assert abs(tot - rtot) <= 1e-3 * rtot + 10, (tot, rtot)
+        assert abs(tot - rtot) <= count_tol * rtot + 10, (tot, rtot)
         nd, _ = eng.tune_partial_d(tot, n, k, pd, eng.dimension_split(d)[1])
         assert nd == cur.partial_d_next
         checked += 1

@@ -127,7 +127,7 @@ def test_train_errors_match_reference_classes(ref):
         e.assign_training_points(x, x[:10])
 
 
-@pytest.mark.parametrize("n,d,k,seed", [(40000, 128, 400, 10), (30000, 256, 1024, 11)])
+@pytest.mark.parametrize("n,d,k,seed", [(40000, 128, 400, 10), (60000, 256, 512, 11)])
 def test_hierarchical_train_matches_reference(ref, n, d, k, seed):
     import superkmeans_b200 as skm
 
