@@ -186,6 +186,28 @@ skm_status skm_op_update_centroids(int device, const float* x, const uint32_t* a
 /* PDXLayout::PDXify<false> (include/superkmeans/pdx/layout.h:155-232). */
 skm_status skm_op_pdxify(int device, const float* in, uint64_t n, uint64_t d, float* out);
 
+/* Exact nearest-centroid assignment that allocates nothing.  No counterpart in the reference (which
+ * allocates freely on the host); the result is that of skm_op_find_nearest.
+ *
+ * For callers that cannot call cudaMalloc: code running inside a process whose own pool took the GPU's
+ * memory at start-up, and latency-critical loops that cannot afford the device-wide synchronisation an
+ * allocation or a free implies.  x_dev [n][d], y_dev [k][d], out_knn_dev [n] and out_dist_dev [n] are DEVICE
+ * memory of `device` (-1 = the current device) supplied by the caller; cuda_stream is a cudaStream_t (NULL =
+ * the default stream).  The call returns after the outputs are written (it synchronises that stream).
+ *
+ * The intermediate data (norms, candidate pairs, a status word) live in one fixed array in the library's
+ * device image, about 3.3 MiB, which every GPU that loads the library holds until the process exits.  Hence:
+ *   - n <= SKM_NOALLOC_MAX_ROWS and k <= SKM_NOALLOC_MAX_CENTROIDS, else SKM_INVALID_ARGUMENT (split a
+ *     larger batch of rows into several calls); d is not limited;
+ *   - every call uses the same array: calls whose kernels can overlap on one GPU (two streams, two
+ *     threads) race with each other and must be serialised by the caller;
+ *   - the first call on a device looks the array's address up; make that call before any stream
+ *     capture starts. */
+#define SKM_NOALLOC_MAX_ROWS 262144
+#define SKM_NOALLOC_MAX_CENTROIDS 65536
+skm_status skm_op_find_nearest_noalloc(int device, const float* x_dev, const float* y_dev, uint64_t n, uint64_t k, uint64_t d, uint32_t* out_knn_dev, float* out_dist_dev,
+                                       void* cuda_stream);
+
 /* ---- host-side decisions of the path (no GPU needed) ---------------------------------------- */
 
 /* PDXLayout::GetDimensionSplit (layout.h:115-140). */

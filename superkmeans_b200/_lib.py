@@ -102,6 +102,7 @@ SIGNATURES = {
     "skm_op_rotate": (C.c_int, [C.c_int, f32p, f32p, C.c_uint64, C.c_uint64, f32p]),
     "skm_op_unrotate": (C.c_int, [C.c_int, f32p, f32p, C.c_uint64, C.c_uint64, f32p]),
     "skm_op_find_nearest": (C.c_int, [C.c_int, f32p, f32p, C.c_uint64, C.c_uint64, C.c_uint64, u32p, f32p]),
+    "skm_op_find_nearest_noalloc": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "skm_op_find_nearest_pruned": (C.c_int, [C.c_int, f32p, f32p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_float, C.c_uint32, u32p, f32p, u64p]),
     "skm_op_update_centroids": (C.c_int, [C.c_int, f32p, u32p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, f32p, u32p, C.POINTER(C.c_double)]),
     "skm_op_pdxify": (C.c_int, [C.c_int, f32p, C.c_uint64, C.c_uint64, f32p]),

@@ -6,6 +6,7 @@
 #include <string>
 
 #include "engine.h"
+#include "noalloc.h"
 #include "kernels_tc.cuh"
 
 using skmb::Engine;
@@ -238,6 +239,13 @@ skm_status skm_op_update_centroids(int device, const float* x, const uint32_t* a
 skm_status skm_op_pdxify(int device, const float* in, uint64_t n, uint64_t d, float* out) {
     g_create_error.clear();
     return guarded(g_op_error, [&] { Engine::op_pdxify(device, in, n, d, out); });
+}
+
+// ---- allocation-free operator (noalloc.cu) -----------------------------------------------------
+skm_status skm_op_find_nearest_noalloc(int device, const float* x_dev, const float* y_dev, uint64_t n, uint64_t k, uint64_t d, uint32_t* out_knn_dev, float* out_dist_dev,
+                                       void* cuda_stream) {
+    g_create_error.clear();
+    return guarded(g_op_error, [&] { skmb::noalloc::find_nearest(device, x_dev, y_dev, n, k, d, out_knn_dev, out_dist_dev, static_cast<cudaStream_t>(cuda_stream)); });
 }
 
 // ---- host-side decisions ---------------------------------------------------------------------

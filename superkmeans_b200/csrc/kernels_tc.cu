@@ -1088,6 +1088,27 @@ void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size
     SKM_CUDA(cudaGetLastError());
 }
 
+void launch_assign_full_flagged(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist,
+                                uint2* top2_scratch, int* error_word, cudaStream_t stream) {
+    if (n == 0 || k == 0) return;
+    const CUtensorMap tx = make_tmap(x, d, n, d, BM);
+    const CUtensorMap ty = make_tmap(y, d, k, d, BN);
+    Params p{};
+    p.n = n;
+    p.k = k;
+    p.kdim = static_cast<uint32_t>(d);
+    p.norms_x = norms_x;
+    p.norms_y = norms_y;
+    p.out_knn = out_knn;
+    p.out_dist = out_dist;
+    p.out_top2 = top2_scratch;
+    p.error = error_word;
+    launch<MODE_ARGMIN>(tx, ty, p, stream);
+    refine_top2_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, d, norms_x, norms_y, top2_scratch, out_knn, out_dist);
+    note_kernel_launch();
+    SKM_CUDA(cudaGetLastError());
+}
+
 void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, float* out, size_t ldo, size_t n, size_t n_out, size_t k_dim, cudaStream_t stream) {
     if (n == 0 || n_out == 0) return;
     int device = 0;

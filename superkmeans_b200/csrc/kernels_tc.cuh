@@ -20,6 +20,10 @@ bool eligible(const float* x, size_t ldx, const float* y, size_t ldy);
 // fp32 refinement).
 void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist,
                         uint2* top2_scratch, cudaStream_t stream);
+// Same two kernels, but the word that a kernel sets when one of its bounded waits runs out is supplied by
+// the caller (device memory, zero on entry) instead of coming from this file's lazily allocated per-device word.
+void launch_assign_full_flagged(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist,
+                                uint2* top2_scratch, int* error_word, cudaStream_t stream);
 void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, float* out, size_t ldo, size_t n, size_t n_out, size_t k_dim, cudaStream_t stream);
 
 // Pruned assignment for all n points as a dense ADSampling chain on the tensor cores.  chain_norms_x /

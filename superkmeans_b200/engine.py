@@ -238,6 +238,16 @@ def find_nearest(x: np.ndarray, y: np.ndarray, device: int = -1):
     return knn, dist
 
 
+def find_nearest_noalloc(x_dev_ptr: int, y_dev_ptr: int, n: int, k: int, d: int, out_knn_dev_ptr: int, out_dist_dev_ptr: int, device: int = -1, stream: int = 0) -> None:
+    """Exact assignment on DEVICE buffers given as raw addresses, with no allocation made on the way.
+
+    For callers whose device memory belongs to someone else's pool, or who cannot afford the device-wide
+    stall of an allocation.  x [n][d] and y [k][d] are fp32, the outputs uint32 [n] and fp32 [n].  Limited to
+    n <= 262144 and k <= 65536 per call; calls share one scratch area on the GPU and must not overlap.
+    """
+    check(lib.skm_op_find_nearest_noalloc(device, x_dev_ptr, y_dev_ptr, n, k, d, out_knn_dev_ptr, out_dist_dev_ptr, stream or None))
+
+
 def find_nearest_pruned(x: np.ndarray, y: np.ndarray, prev_assign: np.ndarray, partial_d: int, epsilon0: float = 1.5, device: int = -1):
     x, y = _f32(x), _f32(y)
     knn = np.ascontiguousarray(prev_assign, dtype=np.uint32).copy()
