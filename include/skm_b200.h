@@ -151,10 +151,13 @@ skm_status skm_reset_phase_times(skm_handle* h);
  * No counterpart in the reference (it delegates to whatever BLAS is linked). */
 void skm_set_tensor_cores(int enabled);
 int skm_get_tensor_cores(void);
-/* How a pruned assignment pass divides its points between its two kernels: 0 (default) by the survival
- * rate of the first ADSampling test on a sample of centroids, 1 all through the candidate-list kernel,
- * 2 all through the dense-chain kernel.  The results do not depend on the choice (up to fp32 rounding);
- * it exists for profiling and for testing each kernel on its own.  No counterpart in the reference. */
+/* Which kernels a pruned assignment pass uses: 0 (default) chosen from the survival rate of the first
+ * ADSampling test on a sample of centroids (tensor-core dense chain when many pairs survive, else tensor-core
+ * first test + candidate-list walk, with the few points of high survival on the dense SIMT chain); 1 SIMT
+ * candidate lists for all points; 2 dense SIMT chain for all; 3 tensor-core dense chain for all; 4 tensor-core
+ * first test + list walk for all; 5 as 4 with a quarter of the list capacity, so that overflowing lists take
+ * their fallback.  The results do not depend on the choice (up to fp32 rounding); it exists for profiling and
+ * for testing each kernel on its own.  No counterpart in the reference. */
 void skm_set_prune_split(int mode);
 int skm_get_prune_split(void);
 /* Kernels launched by this library in the calling process so far. */

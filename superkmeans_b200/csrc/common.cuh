@@ -111,6 +111,37 @@ void launch_pruned_prepare(const PrunedParams& p, PruneSplitWorkspace& ws, cudaS
 // Runs the dense chain for the n_hard points listed in ws.hard_idx.
 void launch_assign_pruned_dense(const PrunedParams& p, PruneSplitWorkspace& ws, size_t n_hard, cudaStream_t stream);
 
+// Pruned assignment with candidate lists made by the tensor-core first test (kernels_tc.cu) and walked by
+// walk_lists_kernel (kernels_walk.cu), for the row tiles [tile0, tile0 + n_tiles) of 128 points.
+struct WalkParams {
+    const float* x;
+    const float* y_pdx;
+    const float* y_aux;
+    const float* ratios;
+    const uint2* lists;          // n_tiles * 4 groups of cap_group entries
+    const uint32_t* list_offs;   // n_tiles * 4 * (n_chunks + 1)
+    uint32_t cap_group;
+    size_t n, k, d;
+    uint32_t partial_d, vertical_d, horizontal_d;
+    size_t tile0, n_tiles;
+    const float* best_in;        // exact distance to the previous centroid
+    const uint32_t* skip;        // may be null
+    uint32_t* knn;
+    float* dist;
+    uint32_t* not_pruned;
+    uint32_t* redo;              // set to 1 for points whose group list overflowed
+    uint32_t* redo_count;
+    unsigned long long* step_hist = nullptr;   // optional profiling aid: pairs alive at every step, 32 slots
+};
+void launch_walk_lists(const WalkParams& w, int device, cudaStream_t stream);
+// hard_idx / *n_hard_dev from an arbitrary flag array (same buffers as launch_pruned_prepare fills)
+void launch_compact_flags(const uint32_t* flags, size_t n, PruneSplitWorkspace& ws, cudaStream_t stream);
+
+void launch_gather_listed(const float* x, const float* best, const uint32_t* knn, const uint32_t* idx, size_t n_listed, size_t d, float* x_out, float* best_out,
+                          uint32_t* knn_out, cudaStream_t stream);
+void launch_scatter_listed(const uint32_t* idx, size_t n_listed, const uint32_t* knn_in, const float* dist_in, const uint32_t* np_in, uint32_t* knn, float* dist,
+                           uint32_t* not_pruned, cudaStream_t stream);
+
 int pruned_grid_size(int device);
 size_t pruned_scratch_elems(int grid);
 void launch_assign_pruned(const PrunedParams& p, int grid, cudaStream_t stream);

@@ -344,6 +344,30 @@ __global__ void fill_iota_kernel(uint32_t* idx, uint32_t* flags, size_t n, uint3
 void set_prune_split_mode(int mode) { g_prune_split_mode = mode; }
 int prune_split_mode() { return g_prune_split_mode; }
 
+namespace {
+
+// The points listed in ws.hard_idx through the dense chain: on the tensor cores over a gathered copy of their
+// rows when `on_tensor_cores`, else with the SIMT kernel in place.
+void run_listed_dense(const PrunedParams& p, PruneSplitWorkspace& ws, PrunePassBuffers& b, size_t n_listed, bool on_tensor_cores, cudaStream_t stream) {
+    if (n_listed == 0) return;
+    if (!on_tensor_cores) {
+        launch_assign_pruned_dense(p, ws, n_listed, stream);
+        return;
+    }
+    const uint32_t n_ck = prune_chain_checkpoints(p.partial_d, p.vertical_d, p.horizontal_d);
+    float* xl = b.listed_x.ensure(n_listed * p.d);
+    float* bestl = b.listed_best.ensure(n_listed);
+    uint32_t* knnl = b.listed_knn.ensure(n_listed);
+    launch_gather_listed(p.x, ws.best, p.knn, ws.hard_idx, n_listed, p.d, xl, bestl, knnl, stream);
+    launch_chain_norms(xl, n_listed, p.d, p.partial_d, p.vertical_d, p.horizontal_d, false, b.listed_norms.ensure(n_listed * n_ck), stream);
+    launch_chain_norms(p.y, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, true, ws.chain_norms_y, stream);
+    tc::launch_chain(xl, p.y, n_listed, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, b.listed_norms.get(), ws.chain_norms_y, p.ratios, bestl, knnl,
+                     b.listed_dist.ensure(n_listed), b.listed_np.ensure(n_listed), b.listed_top2.ensure(n_listed), stream);
+    launch_scatter_listed(ws.hard_idx, n_listed, knnl, b.listed_dist.get(), b.listed_np.get(), p.knn, p.dist, p.not_pruned, stream);
+}
+
+} // namespace
+
 void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, int device, cudaStream_t stream) {
     if (p.n == 0) return;
     if (b.grid == 0) b.grid = pruned_grid_size(device);
@@ -363,7 +387,7 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
     const int n_sample = static_cast<int>(std::min<size_t>(p.k, 128));
     const bool tc_ok = tc::eligible(p.x, p.d, p.y, p.d);
     size_t n_hard = 0;
-    bool use_chain = false;
+    bool use_chain = false, use_tc_lists = false;
     if (g_prune_split_mode == 0) {
         unsigned long long* host = b.counters_host.ensure(2);
         host[0] = 0;
@@ -375,12 +399,17 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
         // Candidate lists cost one gathered block per surviving pair and step; the tensor-core chain costs a
         // full product whatever survives.  Past roughly 0.8 % of surviving pairs the chain is cheaper.
         const double survival = static_cast<double>(host[0]) / (static_cast<double>(p.n) * n_sample);
-        use_chain = tc_ok && survival > 0.008;
+        // The chain costs a full product whatever survives; lists cost a partial product plus one gathered
+        // block per surviving pair and step, and their capacity is an eighth of all pairs.
+        use_chain = tc_ok && (survival > 0.08 || n_hard * 4 > p.n);
+        use_tc_lists = tc_ok && !use_chain;
     } else if (g_prune_split_mode == 3) {
         if (!tc_ok) throw std::invalid_argument("the tensor-core chain needs 16-byte aligned rows (d % 4 == 0)");
         use_chain = true;
     } else {
         const bool dense = g_prune_split_mode == 2;
+        use_tc_lists = g_prune_split_mode == 4 || g_prune_split_mode == 5;
+        if (use_tc_lists && !tc_ok) throw std::invalid_argument("the tensor-core first test needs 16-byte aligned rows (d % 4 == 0)");
         fill_iota_kernel<<<static_cast<unsigned>((p.n + 255) / 256), 256, 0, stream>>>(ws.hard_idx, ws.flags, p.n, dense ? 1u : 0u);
         note_kernel_launch();
         SKM_CUDA(cudaGetLastError());
@@ -395,10 +424,69 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
                          p.not_pruned, b.top2.ensure(p.n), stream);
         return;
     }
-    b.last_path = 1;
-    b.last_n_hard = n_hard;
     p.best_in = ws.best;
     p.skip = ws.flags;
+    if (use_tc_lists) {
+        b.last_path = 4;
+        b.last_n_hard = n_hard;
+        uint32_t* redo = b.redo.ensure(p.n + 1);
+        uint32_t* redo_count = redo + p.n;
+        SKM_CUDA(cudaMemsetAsync(redo, 0, sizeof(uint32_t) * (p.n + 1), stream));
+        if (n_hard < p.n) {
+            const size_t n_chunks = (p.k + kChunk - 1) / kChunk;
+            // per group of 32 points: room for an eighth of its pairs (mode 5: a thirty-second, so that lists overflow)
+            const uint32_t cap_group = static_cast<uint32_t>(std::max<size_t>(256, g_prune_split_mode == 5 ? p.k : p.k * 4));
+            const size_t tile_bytes = 4 * static_cast<size_t>(cap_group) * sizeof(uint2);
+            const size_t n_tiles = (p.n + kTileM - 1) / kTileM;
+            const size_t budget = static_cast<size_t>(6) << 30;
+            const size_t per_batch = std::min(n_tiles, std::max<size_t>(148, budget / tile_bytes));
+            uint2* lists = b.tc_lists.ensure(per_batch * 4 * cap_group);
+            uint32_t* offs = b.tc_list_offs.ensure(per_batch * 4 * (n_chunks + 1));
+            for (size_t t0 = 0; t0 < n_tiles; t0 += per_batch) {
+                const size_t nt = std::min(per_batch, n_tiles - t0);
+                tc::launch_first_test(p.x, p.y, p.n, p.k, p.d, p.partial_d, p.norms_x, p.norms_y, ws.best, ws.flags, ratio_first, t0, nt, lists, offs, cap_group, stream);
+                WalkParams w{};
+                w.x = p.x;
+                w.y_pdx = p.y_pdx;
+                w.y_aux = p.y_aux;
+                w.ratios = p.ratios;
+                w.lists = lists;
+                w.list_offs = offs;
+                w.cap_group = cap_group;
+                w.n = p.n;
+                w.k = p.k;
+                w.d = p.d;
+                w.partial_d = p.partial_d;
+                w.vertical_d = p.vertical_d;
+                w.horizontal_d = p.horizontal_d;
+                w.tile0 = t0;
+                w.n_tiles = nt;
+                w.best_in = ws.best;
+                w.skip = ws.flags;
+                w.knn = p.knn;
+                w.dist = p.dist;
+                w.not_pruned = p.not_pruned;
+                w.redo = redo;
+                w.redo_count = redo_count;
+                launch_walk_lists(w, device, stream);
+            }
+        }
+        run_listed_dense(p, ws, b, n_hard, true, stream);
+        // points of groups whose list overflowed
+        unsigned long long* host = b.counters_host.ensure(2);
+        host[0] = 0;
+        SKM_CUDA(cudaMemcpyAsync(&host[0], redo_count, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
+        SKM_CUDA(cudaStreamSynchronize(stream));
+        const size_t n_redo = static_cast<size_t>(host[0] & 0xFFFFFFFFull);
+        b.last_n_redo = n_redo;
+        if (n_redo != 0) {
+            launch_compact_flags(redo, p.n, ws, stream);
+            run_listed_dense(p, ws, b, n_redo, true, stream);
+        }
+        return;
+    }
+    b.last_path = 1;
+    b.last_n_hard = n_hard;
     if (n_hard < p.n) {
         p.scratch = b.lists.ensure(pruned_scratch_elems(b.grid));
         launch_assign_pruned(p, b.grid, stream);

@@ -107,15 +107,21 @@ struct PrunePassBuffers {
     DeviceBuffer<float> best, sample, sample_norms, chain_norms_y;
     DeviceBuffer<float> chain_norms_x;
     DeviceBuffer<uint32_t> flags, positions, hard_idx, n_hard_dev;
+    DeviceBuffer<uint2> tc_lists, listed_top2;
+    DeviceBuffer<uint32_t> tc_list_offs, redo, listed_knn, listed_np;
+    DeviceBuffer<float> listed_x, listed_best, listed_dist, listed_norms;
     DeviceBuffer<unsigned long long> alive_total;
     PinnedBuffer<unsigned long long> counters_host;
-    int last_path = 0;   // 1 lists (+ dense for flagged points), 3 tensor-core chain
+    int last_path = 0;   // 1 lists (+ dense for flagged points), 3 tensor-core chain, 4 tensor-core first test + list walk
     int grid = 0;
     size_t last_n_hard = 0;
+    size_t last_n_redo = 0;   // points whose candidate list overflowed (path 4)
 };
-// mode: 0 = automatic (tensor-core chain for every point when the sampled survival rate is high, else
-// candidate lists with the flagged points on the dense SIMT chain), 1 = candidate lists for every point,
-// 2 = dense SIMT chain for every point, 3 = tensor-core chain for every point.
+// mode: 0 = automatic (tensor-core chain for every point when the sampled survival rate is high, else the
+// tensor-core first test with list walk, flagged points on the dense SIMT chain; SIMT candidate lists when rows
+// are not 16-byte aligned), 1 = SIMT candidate lists for every point, 2 = dense SIMT chain for every point,
+// 3 = tensor-core chain for every point, 4 = tensor-core first test + list walk for every point, 5 = as 4 with
+// the list capacity cut to a quarter so that the overflow route runs.
 void set_prune_split_mode(int mode);
 int prune_split_mode();
 void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, int device, cudaStream_t stream);

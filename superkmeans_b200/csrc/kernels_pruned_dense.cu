@@ -339,6 +339,61 @@ void launch_pruned_prepare(const PrunedParams& p, PruneSplitWorkspace& ws, cudaS
     SKM_LAUNCH_CHECK();
 }
 
+// Rows listed in idx gathered into a compact matrix together with their threshold and previous assignment,
+// and the results of a pass over the compact rows scattered back.
+__global__ void __launch_bounds__(256) gather_listed_kernel(const float* __restrict__ x, const float* __restrict__ best, const uint32_t* __restrict__ knn,
+                                                            const uint32_t* __restrict__ idx, size_t n_listed, size_t d, float* __restrict__ x_out,
+                                                            float* __restrict__ best_out, uint32_t* __restrict__ knn_out) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t i = static_cast<size_t>(blockIdx.x) * 8 + warp;
+    if (i >= n_listed) return;
+    const size_t row = idx[i];
+    const float* src = x + row * d;
+    float* dst = x_out + i * d;
+    if (d % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(x_out)) & 15) == 0) {
+        for (size_t j = static_cast<size_t>(lane) * 4; j < d; j += 128) *reinterpret_cast<float4*>(dst + j) = __ldg(reinterpret_cast<const float4*>(src + j));
+    } else {
+        for (size_t j = lane; j < d; j += 32) dst[j] = src[j];
+    }
+    if (lane == 0) {
+        best_out[i] = best[row];
+        knn_out[i] = knn[row];
+    }
+}
+
+__global__ void scatter_listed_kernel(const uint32_t* __restrict__ idx, size_t n_listed, const uint32_t* __restrict__ knn_in, const float* __restrict__ dist_in,
+                                      const uint32_t* __restrict__ np_in, uint32_t* __restrict__ knn, float* __restrict__ dist, uint32_t* __restrict__ not_pruned) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n_listed) return;
+    const size_t row = idx[i];
+    knn[row] = knn_in[i];
+    dist[row] = dist_in[i];
+    not_pruned[row] = np_in[i];
+}
+
+void launch_gather_listed(const float* x, const float* best, const uint32_t* knn, const uint32_t* idx, size_t n_listed, size_t d, float* x_out, float* best_out,
+                          uint32_t* knn_out, cudaStream_t stream) {
+    if (n_listed == 0) return;
+    gather_listed_kernel<<<static_cast<unsigned>((n_listed + 7) / 8), 256, 0, stream>>>(x, best, knn, idx, n_listed, d, x_out, best_out, knn_out);
+    SKM_LAUNCH_CHECK();
+}
+
+void launch_scatter_listed(const uint32_t* idx, size_t n_listed, const uint32_t* knn_in, const float* dist_in, const uint32_t* np_in, uint32_t* knn, float* dist,
+                           uint32_t* not_pruned, cudaStream_t stream) {
+    if (n_listed == 0) return;
+    scatter_listed_kernel<<<static_cast<unsigned>((n_listed + 255) / 256), 256, 0, stream>>>(idx, n_listed, knn_in, dist_in, np_in, knn, dist, not_pruned);
+    SKM_LAUNCH_CHECK();
+}
+
+void launch_compact_flags(const uint32_t* flags, size_t n, PruneSplitWorkspace& ws, cudaStream_t stream) {
+    if (n == 0) return;
+    copy_u32_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(flags, ws.positions, n);
+    SKM_LAUNCH_CHECK();
+    exclusive_scan_u32(ws.positions, n, ws.positions + n, stream);
+    compact_flags_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(flags, ws.positions, n, ws.hard_idx, ws.n_hard_dev);
+    SKM_LAUNCH_CHECK();
+}
+
 void launch_chain_norms(const float* m, size_t rows, size_t d, uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d, bool transposed, float* out,
                         cudaStream_t stream) {
     if (rows == 0) return;

@@ -42,7 +42,9 @@ constexpr uint32_t STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;  // 49152
 constexpr uint32_t OFF_A_HI = 0, OFF_A_LO = A_TILE_BYTES, OFF_B_HI = 2 * A_TILE_BYTES, OFF_B_LO = 2 * A_TILE_BYTES + B_TILE_BYTES;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t SMEM_CTRL_BYTES = 9216;
-constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + 1024;  // + alignment slack
+constexpr uint32_t STAGE_ENTRIES = 256;   // per epilogue warp, first-test epilogue
+constexpr uint32_t SMEM_STAGE_BYTES = 4 * STAGE_ENTRIES * 8;
+constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + SMEM_STAGE_BYTES + 1024;  // + alignment slack
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
 
 // kind::tf32, fp32 accumulate, K-major A and B, N = 256, M = 128
@@ -186,9 +188,19 @@ struct Params {
     float* out;
     size_t ldo;
     int* error;
+    // first-test epilogue (MODE_PRUNE): rows [tile0 * 128, (tile0 + n_tiles) * 128) are processed; norms_x / norms_y
+    // hold the norms over the first kdim dimensions
+    size_t tile0;
+    size_t n_tiles;        // 0 = all row tiles (other modes)
+    const float* best_in;  // n: exact distance to the previous centroid
+    const uint32_t* skip;  // n or null: 1 = row handled elsewhere
+    float ratio_first;     // ratios[kdim]
+    uint2* lists;          // per 32-row group: cap_group entries {column << 5 | row in group, partial distance}
+    uint32_t* list_offs;   // per group: (n_chunks + 1) entry counts at the start of every 1024-centroid chunk
+    uint32_t cap_group;
 };
 
-enum { MODE_ARGMIN = 0, MODE_STORE = 1 };
+enum { MODE_ARGMIN = 0, MODE_STORE = 1, MODE_PRUNE = 2 };
 
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y, const Params p) {
@@ -219,7 +231,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
     tc_fence_after();
     const uint32_t tmem_base = ctrl->tmem_base;
 
-    const size_t n_row_tiles = (p.n + BM - 1) / BM;
+    const size_t rt_begin = (MODE == MODE_PRUNE) ? p.tile0 : 0;
+    const size_t n_row_tiles = (MODE == MODE_PRUNE) ? p.tile0 + p.n_tiles : (p.n + BM - 1) / BM;
     const uint32_t n_col_tiles = static_cast<uint32_t>((p.k + BN - 1) / BN);
     const uint32_t nkb = (p.kdim + BK - 1) / BK;
 
@@ -228,7 +241,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
         if (lane == 0) {
             uint32_t kbt = 0;
             bool ok = true;
-            for (size_t rt = blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {
+            for (size_t rt = rt_begin + blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {
                 for (uint32_t nt = 0; nt < n_col_tiles && ok; ++nt) {
                     for (uint32_t kb = 0; kb < nkb; ++kb, ++kbt) {
                         const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
@@ -249,7 +262,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
         if (lane == 0) {
             uint32_t kbt = 0, t = 0;
             bool ok = true;
-            for (size_t rt = blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {
+            for (size_t rt = rt_begin + blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {
                 for (uint32_t nt = 0; nt < n_col_tiles && ok; ++nt, ++t) {
                     const uint32_t b = t & 1u, tph = (t >> 1) & 1u;
                     if (!mbar_wait(&ctrl->tmem_empty[b], tph ^ 1u, p.error, 2)) {
@@ -287,7 +300,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
         const int cid = threadIdx.x - 64;
         uint32_t kbt = 0;
         bool ok = true;
-        for (size_t rt = blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {
+        for (size_t rt = rt_begin + blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {
             for (uint32_t nt = 0; nt < n_col_tiles && ok; ++nt) {
                 for (uint32_t kb = 0; kb < nkb; ++kb, ++kbt) {
                     const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
@@ -325,7 +338,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
         const uint32_t row_in_tile = lane_base + lane;
         uint32_t t = 0;
         bool ok = true;
-        for (size_t rt = blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {
+        for (size_t rt = rt_begin + blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {
             const size_t row = rt * BM + row_in_tile;
             const bool row_valid = row < p.n;
             // Best and runner-up of the tensor-core distances.  They are only candidates: the accumulator
@@ -333,12 +346,24 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
             // its distance are settled afterwards in fp32 by refine_top2_kernel.
             float nx = 0.f, d1 = FLT_MAX, d2 = FLT_MAX;
             uint32_t i1 = 0, i2 = 0xFFFFFFFFu;
-            if (MODE == MODE_ARGMIN && row_valid) nx = p.norms_x[row];
+            if ((MODE == MODE_ARGMIN || MODE == MODE_PRUNE) && row_valid) nx = p.norms_x[row];
+            // first-test epilogue: this warp's 32 rows share one candidate list; `filled` is warp-uniform
+            float thr = -FLT_MAX;
+            uint32_t filled = 0;
+            uint2* my_list = nullptr;
+            uint32_t* my_offs = nullptr;
+            if (MODE == MODE_PRUNE) {
+                const size_t group = (rt - rt_begin) * 4 + (warp & 3);
+                my_list = p.lists + group * p.cap_group;
+                my_offs = p.list_offs + group * ((p.k + 1023) / 1024 + 1);
+                if (row_valid && !(p.skip && p.skip[row])) thr = p.best_in[row] * p.ratio_first;
+            }
             for (uint32_t nt = 0; nt < n_col_tiles && ok; ++nt, ++t) {
                 const uint32_t b = t & 1u, tph = (t >> 1) & 1u;
                 const size_t col0 = static_cast<size_t>(nt) * BN;
                 float* ny = ctrl->ny[warp & 3][b];
-                if (MODE == MODE_ARGMIN) {
+                if (MODE == MODE_PRUNE && (nt & 3u) == 0 && lane == 0) my_offs[nt >> 2] = filled;
+                if (MODE == MODE_ARGMIN || MODE == MODE_PRUNE) {
                     // each warp keeps its own copy, so no cross-warp barrier is needed
                     for (int j = lane; j < BN; j += 32) ny[j] = (col0 + j < p.k) ? __ldg(p.norms_y + col0 + j) : 0.f;
                     __syncwarp();
@@ -373,6 +398,73 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                                 }
                             }
                         }
+                    } else if (MODE == MODE_PRUNE) {
+                        // test of the first checkpoint for 32 centroids, then a warp scan places every row's
+                        // survivors behind those of the lower lanes
+                        uint32_t mask = 0;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float pd = fmaf(-2.0f, __uint_as_float(r[j]), nx) + ny[ch * 32 + j];
+                            r[j] = __float_as_uint(pd);
+                            mask |= (pd < thr && col0 + ch * 32 + j < p.k) ? (1u << j) : 0u;
+                        }
+                        const uint32_t cnt = __popc(mask);
+                        uint32_t incl = cnt;
+#pragma unroll
+                        for (int off = 1; off < 32; off <<= 1) {
+                            const uint32_t v = __shfl_up_sync(0xffffffffu, incl, off);
+                            if (lane >= off) incl += v;
+                        }
+                        const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+                        if (total != 0) {
+                            const uint32_t colbits = static_cast<uint32_t>(col0 + ch * 32) << 5;
+                            if (total <= STAGE_ENTRIES) {
+                                // survivors are packed in shared memory first (predicated stores, no divergence) and
+                                // leave for global memory as contiguous runs
+                                uint2* stg = reinterpret_cast<uint2*>(smem + STAGES * STAGE_BYTES + SMEM_CTRL_BYTES) + (warp & 3) * STAGE_ENTRIES;
+                                uint32_t pos = incl - cnt;
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) {
+                                    const uint32_t bit = (mask >> j) & 1u;
+                                    if (bit) stg[pos] = make_uint2((colbits + (static_cast<uint32_t>(j) << 5)) | lane, r[j]);
+                                    pos += bit;
+                                }
+                                __syncwarp();
+                                for (uint32_t i = lane; i < total; i += 32)
+                                    if (filled + i < p.cap_group) my_list[filled + i] = stg[i];
+                                __syncwarp();
+                            } else {
+                                // dense case (more than a quarter of the 32 x 32 block passes): eight columns at a time,
+                                // which always fit in the staging area
+                                uint2* stg = reinterpret_cast<uint2*>(smem + STAGES * STAGE_BYTES + SMEM_CTRL_BYTES) + (warp & 3) * STAGE_ENTRIES;
+                                uint32_t done = 0;
+#pragma unroll
+                                for (int sb = 0; sb < 4; ++sb) {
+                                    const uint32_t sub = (mask >> (8 * sb)) & 0xFFu;
+                                    const uint32_t c8 = __popc(sub);
+                                    uint32_t in8 = c8;
+#pragma unroll
+                                    for (int off = 1; off < 32; off <<= 1) {
+                                        const uint32_t v = __shfl_up_sync(0xffffffffu, in8, off);
+                                        if (lane >= off) in8 += v;
+                                    }
+                                    const uint32_t tot8 = __shfl_sync(0xffffffffu, in8, 31);
+                                    uint32_t pos = in8 - c8;
+#pragma unroll
+                                    for (int j = 8 * sb; j < 8 * sb + 8; ++j) {
+                                        const uint32_t bit = (mask >> j) & 1u;
+                                        if (bit) stg[pos] = make_uint2((colbits + (static_cast<uint32_t>(j) << 5)) | lane, r[j]);
+                                        pos += bit;
+                                    }
+                                    __syncwarp();
+                                    for (uint32_t i = lane; i < tot8; i += 32)
+                                        if (filled + done + i < p.cap_group) my_list[filled + done + i] = stg[i];
+                                    __syncwarp();
+                                    done += tot8;
+                                }
+                            }
+                            filled += total;
+                        }
                     } else if (row_valid) {
                         float* orow = p.out + row * p.ldo + col0 + ch * 32;
                         const size_t left = (col0 + ch * 32 < p.k) ? (p.k - (col0 + ch * 32)) : 0;
@@ -392,6 +484,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                 mbar_arrive(&ctrl->tmem_empty[b]);
             }
             if (MODE == MODE_ARGMIN && ok && row_valid) p.out_top2[row] = make_uint2(i1, i2);
+            if (MODE == MODE_PRUNE && ok && lane == 0) my_offs[(n_col_tiles + 3) / 4] = filled;
         }
     }
 
@@ -1105,6 +1198,35 @@ void launch_assign_full_flagged(const float* x, const float* y, size_t n, size_t
     p.error = error_word;
     launch<MODE_ARGMIN>(tx, ty, p, stream);
     refine_top2_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, d, norms_x, norms_y, top2_scratch, out_knn, out_dist);
+    note_kernel_launch();
+    SKM_CUDA(cudaGetLastError());
+}
+
+void launch_first_test(const float* x, const float* y, size_t n, size_t k, size_t d, uint32_t partial_d, const float* norms_x, const float* norms_y, const float* best_in,
+                       const uint32_t* skip, float ratio_first, size_t tile0, size_t n_tiles, uint2* lists, uint32_t* list_offs, uint32_t cap_group, cudaStream_t stream) {
+    if (n_tiles == 0 || k == 0) return;
+    int device = 0;
+    SKM_CUDA(cudaGetDevice(&device));
+    const CUtensorMap tx = make_tmap(x, partial_d, n, d, BM);
+    const CUtensorMap ty = make_tmap(y, partial_d, k, d, BN);
+    Params p{};
+    p.n = n;
+    p.k = k;
+    p.kdim = partial_d;
+    p.norms_x = norms_x;
+    p.norms_y = norms_y;
+    p.error = error_flag(device);
+    p.tile0 = tile0;
+    p.n_tiles = n_tiles;
+    p.best_in = best_in;
+    p.skip = skip;
+    p.ratio_first = ratio_first;
+    p.lists = lists;
+    p.list_offs = list_offs;
+    p.cap_group = cap_group;
+    SKM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<MODE_PRUNE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES)));
+    const int grid = static_cast<int>(std::min<size_t>(n_tiles, static_cast<size_t>(sm_count(device))));
+    gemm_tc_kernel<MODE_PRUNE><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, ty, p);
     note_kernel_launch();
     SKM_CUDA(cudaGetLastError());
 }

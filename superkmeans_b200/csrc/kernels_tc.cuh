@@ -26,6 +26,14 @@ void launch_assign_full_flagged(const float* x, const float* y, size_t n, size_t
                                 uint2* top2_scratch, int* error_word, cudaStream_t stream);
 void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, float* out, size_t ldo, size_t n, size_t n_out, size_t k_dim, cudaStream_t stream);
 
+// First ADSampling test on the tensor cores for the row tiles [tile0, tile0 + n_tiles) of 128 points: partial
+// distances over the first partial_d dimensions of every (point, centroid) pair, tested against
+// best_in * ratio_first; pairs that pass go to one list per group of 32 rows ({centroid << 5 | row in group,
+// partial distance}, at most cap_group entries, in centroid order), and list_offs receives, per group, the
+// number of entries before every 1024-centroid chunk and the total (which exceeds cap_group on overflow).
+void launch_first_test(const float* x, const float* y, size_t n, size_t k, size_t d, uint32_t partial_d, const float* norms_x, const float* norms_y, const float* best_in,
+                       const uint32_t* skip, float ratio_first, size_t tile0, size_t n_tiles, uint2* lists, uint32_t* list_offs, uint32_t cap_group, cudaStream_t stream);
+
 // Pruned assignment for all n points as a dense ADSampling chain on the tensor cores.  chain_norms_x /
 // chain_norms_y hold, per row, the cumulative squared norm after each of the chain's checkpoints
 // (launch_chain_norms; point norms row-major, centroid norms checkpoint-major); best_in the exact distance to the previous centroid; knn the previous

@@ -206,7 +206,7 @@ def tensor_cores_enabled() -> bool:
 
 
 def set_prune_split(mode: int) -> None:
-    """0 = split points between the two pruned kernels automatically, 1 = candidate lists only, 2 = dense only."""
+    """0 = automatic, 1 = SIMT candidate lists, 2 = dense SIMT chain, 3 = tensor-core chain, 4 = tensor-core first test + list walk, 5 = as 4 with small lists (see skm_set_prune_split)."""
     lib.skm_set_prune_split(int(mode))
 
 

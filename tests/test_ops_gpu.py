@@ -112,18 +112,19 @@ def _trace(ref, n, d, k, iters, seed, hier=False, centers=None, **kw):
     return x, km, cent
 
 
-@pytest.mark.parametrize("split_mode", [0, 1, 2, 3], ids=["auto", "lists_only", "dense_simt_only", "tensor_core_chain"])
+@pytest.mark.parametrize("split_mode", [0, 1, 2, 3, 4, 5],
+                         ids=["auto", "lists_only", "dense_simt_only", "tensor_core_chain", "tensor_core_lists", "tensor_core_lists_overflowing"])
 @pytest.mark.parametrize("n,d,k", [(20000, 256, 512), (12000, 768, 1500), (6000, 130, 1030), (9000, 1024, 2100)])
 def test_pruned_step_matches_reference_teacher_forced(eng, ref, n, d, k, split_mode):
     """Every pruned iteration of a reference run, replayed from the reference's own inputs, with the
     points routed through the candidate-list kernel, the dense-chain kernel, or split between them."""
-    if split_mode == 3 and (d % 4 != 0 or not eng.tensor_cores_enabled()):
-        pytest.skip("the tensor-core chain needs d % 4 == 0 and the tensor-core kernels switched on")
+    if split_mode >= 3 and (d % 4 != 0 or not eng.tensor_cores_enabled()):
+        pytest.skip("the tensor-core kernels need d % 4 == 0 and to be switched on")
     eng.set_prune_split(split_mode)
     try:
         # the tensor-memory accumulator truncates: partial distances sit ~1e-5 (relative to the dot product)
         # high, which moves a few more pairs across the thresholds than fp32 rounding does
-        _pruned_step_check(eng, ref, n, d, k, count_tol=5e-3 if split_mode in (0, 3) else 1e-3)
+        _pruned_step_check(eng, ref, n, d, k, count_tol=5e-3 if split_mode in (0, 3, 4, 5) else 1e-3)
     finally:
         eng.set_prune_split(0)
 
