@@ -124,8 +124,13 @@ skm_status skm_get_distances(skm_handle* h, float* out, uint64_t n);
 /* horizontal_centroids after training: rotated-space centroids, n_clusters x d. */
 skm_status skm_get_rotated_centroids(skm_handle* h, float* out);
 /* Which kernels the last pruned assignment pass used: 0 none yet, 1 candidate lists (+ dense SIMT chain for
- * flagged points), 3 tensor-core chain. */
+ * flagged points), 3 tensor-core chain, 4 tensor-core first test + list walk (+ tensor-core chain for flagged
+ * points). */
 int skm_last_prune_path(const skm_handle* h);
+/* Work done by the pruned passes of this handle so far: out3[0] rows sent through a dense chain, out3[1]
+ * (pair, 64-dimension block) steps of the candidate-list walk (each reads 256 bytes of a centroid and of a
+ * point), out3[2] rows whose candidate list overflowed and were redone densely.  For roofline accounting. */
+skm_status skm_get_prune_counters(const skm_handle* h, uint64_t* out3);
 /* Objective of the last iteration accumulated in float64 (the reference sums float32). */
 double skm_last_objective_f64(const skm_handle* h);
 
@@ -143,7 +148,8 @@ skm_status skm_trace_get(const skm_handle* h, uint64_t idx, uint64_t* n_samples,
  * since creation or the last reset.  Phases follow the reference profiler's sections
  * (include/superkmeans/profiler.h, SKM_PROFILE_SCOPE names): 0 rotator, 1 norms_calc,
  * 2 search/1st_blas (exact assignment), 3 search (pruned assignment), 4 update_centroids,
- * 5 consolidate, 6 shift, 7 whole Train call. */
+ * 5 consolidate, 6 shift, 7 whole Train call; parts of phase 3: 8 first ADSampling test on the tensor cores,
+ * 9 candidate-list walk, 10 dense chain (the points, or all points, that are cheaper without lists). */
 skm_status skm_get_phase_time(const skm_handle* h, int phase, double* ms, uint64_t* calls);
 skm_status skm_reset_phase_times(skm_handle* h);
 /* Process-wide choice between the tcgen05 tensor-core kernels (1, default) and the fp32 SIMT kernels

@@ -131,6 +131,13 @@ int skm_is_trained(const skm_handle* h) { return (h && h->engine) ? (h->engine->
 float skm_sampling_fraction(const skm_handle* h) { return (h && h->engine) ? h->engine->sampling_fraction() : 0.f; }
 uint64_t skm_n_mesoclusters(const skm_handle* h) { return (h && h->engine) ? h->engine->n_mesoclusters_value() : 0; }
 int skm_last_prune_path(const skm_handle* h) { return (h && h->engine) ? h->engine->last_prune_path() : 0; }
+
+skm_status skm_get_prune_counters(const skm_handle* h, uint64_t* out3) {
+    SKM_NEED(h);
+    if (!out3) return SKM_INVALID_ARGUMENT;
+    h->engine->prune_counters(out3);
+    return SKM_OK;
+}
 double skm_last_objective_f64(const skm_handle* h) { return (h && h->engine) ? h->engine->last_objective_f64() : 0.0; }
 
 skm_status skm_get_iteration_stats(const skm_handle* h, int phase, skm_iter_stats* out, uint64_t cap, uint64_t* count) {

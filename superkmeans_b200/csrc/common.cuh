@@ -97,6 +97,7 @@ struct PruneSplitWorkspace {
     unsigned long long* alive_total = nullptr;  // 1: sampled pairs passing the first test
     int n_sample = 128;
     float ratio_first = 1.0f;       // ratios[partial_d], host copy
+    uint32_t flag_mult = 16;        // a point is flagged when survivors * flag_mult >= n_sample
 };
 size_t prune_split_positions_elems(size_t n);
 uint32_t prune_chain_checkpoints(uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d);
@@ -131,7 +132,7 @@ struct WalkParams {
     uint32_t* not_pruned;
     uint32_t* redo;              // set to 1 for points whose group list overflowed
     uint32_t* redo_count;
-    unsigned long long* step_hist = nullptr;   // optional profiling aid: pairs alive at every step, 32 slots
+    unsigned long long* pair_steps;            // += pairs advanced by one 64-dimension block
 };
 void launch_walk_lists(const WalkParams& w, int device, cudaStream_t stream);
 // hard_idx / *n_hard_dev from an arbitrary flag array (same buffers as launch_pruned_prepare fills)

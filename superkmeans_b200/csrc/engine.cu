@@ -1,6 +1,8 @@
 // Host orchestration: see engine.h.  Every step cites the reference code it reproduces
 // (paths relative to the SuperKMeans repository, include/superkmeans/...).
 #include "engine.h"
+
+#include <cstdlib>
 #include "kernels_tc.cuh"
 
 #include <algorithm>
@@ -368,7 +370,17 @@ void run_listed_dense(const PrunedParams& p, PruneSplitWorkspace& ws, PrunePassB
 
 } // namespace
 
-void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, int device, cudaStream_t stream) {
+void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, int device, cudaStream_t stream, PhaseTimers* timers) {
+    struct Sub {
+        PhaseTimers* t;
+        cudaStream_t s;
+        Sub(PhaseTimers* t_, int phase, cudaStream_t s_) : t(t_), s(s_) {
+            if (t) t->begin(phase, s);
+        }
+        ~Sub() {
+            if (t) t->end(s);
+        }
+    };
     if (p.n == 0) return;
     if (b.grid == 0) b.grid = pruned_grid_size(device);
     const uint32_t n_ck = prune_chain_checkpoints(p.partial_d, p.vertical_d, p.horizontal_d);
@@ -383,6 +395,7 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
     ws.n_hard_dev = b.n_hard_dev.ensure(1);
     ws.ratio_first = ratio_first;
     ws.alive_total = b.alive_total.ensure(1);
+    if (const char* e = std::getenv("SKM_HARD_MULT")) ws.flag_mult = static_cast<uint32_t>(std::atoi(e));
     launch_pruned_prepare(p, ws, stream);
     const int n_sample = static_cast<int>(std::min<size_t>(p.k, 128));
     const bool tc_ok = tc::eligible(p.x, p.d, p.y, p.d);
@@ -418,6 +431,8 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
     if (use_chain) {
         b.last_path = 3;
         b.last_n_hard = p.n;
+        b.total_dense_rows += p.n;
+        Sub sub(timers, PH_PRUNE_DENSE, stream);
         launch_chain_norms(p.x, p.n, p.d, p.partial_d, p.vertical_d, p.horizontal_d, false, b.chain_norms_x.ensure(p.n * n_ck), stream);
         launch_chain_norms(p.y, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, true, ws.chain_norms_y, stream);
         tc::launch_chain(p.x, p.y, p.n, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, b.chain_norms_x.get(), ws.chain_norms_y, p.ratios, ws.best, p.knn, p.dist,
@@ -432,6 +447,8 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
         uint32_t* redo = b.redo.ensure(p.n + 1);
         uint32_t* redo_count = redo + p.n;
         SKM_CUDA(cudaMemsetAsync(redo, 0, sizeof(uint32_t) * (p.n + 1), stream));
+        unsigned long long* pair_steps = b.pair_steps_dev.ensure(1);
+        SKM_CUDA(cudaMemsetAsync(pair_steps, 0, sizeof(unsigned long long), stream));
         if (n_hard < p.n) {
             const size_t n_chunks = (p.k + kChunk - 1) / kChunk;
             // per group of 32 points: room for an eighth of its pairs (mode 5: a thirty-second, so that lists overflow)
@@ -444,7 +461,10 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
             uint32_t* offs = b.tc_list_offs.ensure(per_batch * 4 * (n_chunks + 1));
             for (size_t t0 = 0; t0 < n_tiles; t0 += per_batch) {
                 const size_t nt = std::min(per_batch, n_tiles - t0);
-                tc::launch_first_test(p.x, p.y, p.n, p.k, p.d, p.partial_d, p.norms_x, p.norms_y, ws.best, ws.flags, ratio_first, t0, nt, lists, offs, cap_group, stream);
+                {
+                    Sub sub(timers, PH_PRUNE_FIRST_TEST, stream);
+                    tc::launch_first_test(p.x, p.y, p.n, p.k, p.d, p.partial_d, p.norms_x, p.norms_y, ws.best, ws.flags, ratio_first, t0, nt, lists, offs, cap_group, stream);
+                }
                 WalkParams w{};
                 w.x = p.x;
                 w.y_pdx = p.y_pdx;
@@ -468,18 +488,29 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
                 w.not_pruned = p.not_pruned;
                 w.redo = redo;
                 w.redo_count = redo_count;
+                w.pair_steps = pair_steps;
+                Sub sub(timers, PH_PRUNE_WALK, stream);
                 launch_walk_lists(w, device, stream);
             }
         }
-        run_listed_dense(p, ws, b, n_hard, true, stream);
+        {
+            Sub sub(timers, PH_PRUNE_DENSE, stream);
+            run_listed_dense(p, ws, b, n_hard, true, stream);
+        }
         // points of groups whose list overflowed
         unsigned long long* host = b.counters_host.ensure(2);
         host[0] = 0;
+        host[1] = 0;
         SKM_CUDA(cudaMemcpyAsync(&host[0], redo_count, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
+        SKM_CUDA(cudaMemcpyAsync(&host[1], pair_steps, sizeof(unsigned long long), cudaMemcpyDeviceToHost, stream));
         SKM_CUDA(cudaStreamSynchronize(stream));
         const size_t n_redo = static_cast<size_t>(host[0] & 0xFFFFFFFFull);
         b.last_n_redo = n_redo;
+        b.total_pair_steps += host[1];
+        b.total_dense_rows += n_hard + n_redo;
+        b.total_redo_rows += n_redo;
         if (n_redo != 0) {
+            Sub sub(timers, PH_PRUNE_DENSE, stream);
             launch_compact_flags(redo, p.n, ws, stream);
             run_listed_dense(p, ws, b, n_redo, true, stream);
         }
@@ -512,7 +543,7 @@ void Engine::run_pruned_pass(const float* x, size_t n, size_t k_cur, const float
     p.partial_d = partial_d_;
     p.vertical_d = vertical_d_;
     p.horizontal_d = horizontal_d_;
-    run_pruned_pass_on(p, prune_bufs_, ratios_host_[partial_d_], device_, stream_);
+    run_pruned_pass_on(p, prune_bufs_, ratios_host_[partial_d_], device_, stream_, &timers_);
 }
 
 // -------------------------------------------------------------------------------------------------

@@ -77,7 +77,8 @@ class PinnedBuffer {
 // Accumulating per-phase device timers (CUDA events on the engine's stream); names follow the
 // sections of the reference's profiler (profiler.h): rotator, norms_calc, search/1st_blas, search,
 // update_centroids, consolidate, shift.
-enum Phase { PH_ROTATE = 0, PH_NORMS, PH_ASSIGN_FULL, PH_ASSIGN_PRUNED, PH_UPDATE, PH_CONSOLIDATE, PH_SHIFT, PH_TRAIN_TOTAL, PH_COUNT };
+// The last three are parts of the pruned assignment: first ADSampling test on the tensor cores, candidate-list walk, dense chain.
+enum Phase { PH_ROTATE = 0, PH_NORMS, PH_ASSIGN_FULL, PH_ASSIGN_PRUNED, PH_UPDATE, PH_CONSOLIDATE, PH_SHIFT, PH_TRAIN_TOTAL, PH_PRUNE_FIRST_TEST, PH_PRUNE_WALK, PH_PRUNE_DENSE, PH_COUNT };
 
 class PhaseTimers {
   public:
@@ -116,6 +117,10 @@ struct PrunePassBuffers {
     int grid = 0;
     size_t last_n_hard = 0;
     size_t last_n_redo = 0;   // points whose candidate list overflowed (path 4)
+    // running totals since the buffers were created: rows sent through a dense chain, (pair, 64-dimension block)
+    // steps of the list walk, rows whose list overflowed
+    unsigned long long total_dense_rows = 0, total_pair_steps = 0, total_redo_rows = 0;
+    DeviceBuffer<unsigned long long> pair_steps_dev;
 };
 // mode: 0 = automatic (tensor-core chain for every point when the sampled survival rate is high, else the
 // tensor-core first test with list walk, flagged points on the dense SIMT chain; SIMT candidate lists when rows
@@ -124,7 +129,7 @@ struct PrunePassBuffers {
 // the list capacity cut to a quarter so that the overflow route runs.
 void set_prune_split_mode(int mode);
 int prune_split_mode();
-void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, int device, cudaStream_t stream);
+void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, int device, cudaStream_t stream, PhaseTimers* timers = nullptr);
 
 class Engine {
   public:
@@ -149,6 +154,11 @@ class Engine {
     size_t n_mesoclusters_value() const { return n_meso_; }
     double last_objective_f64() const { return last_cost_f64_; }
     int last_prune_path() const { return prune_bufs_.last_path; }
+    void prune_counters(uint64_t out[3]) const {
+        out[0] = prune_bufs_.total_dense_rows;
+        out[1] = prune_bufs_.total_pair_steps;
+        out[2] = prune_bufs_.total_redo_rows;
+    }
     const std::vector<skm_iter_stats>& stats(int phase) const;
     int device() const { return device_; }
     // Per-iteration snapshots for step-wise parity checks (what RunIteration leaves behind).

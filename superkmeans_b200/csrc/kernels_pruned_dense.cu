@@ -70,7 +70,7 @@ __global__ void gather_sample_kernel(const float* __restrict__ y, size_t k, size
 // counted per point.
 __global__ void __launch_bounds__(256, 2) classify_kernel(
     const float* __restrict__ x, const float* __restrict__ sample, const float* __restrict__ sample_norms, const float* __restrict__ norms_x, const float* __restrict__ best,
-    size_t n, size_t d, uint32_t partial_d, int n_sample, float ratio_first, uint32_t* __restrict__ flags, unsigned long long* __restrict__ alive_total
+    size_t n, size_t d, uint32_t partial_d, int n_sample, float ratio_first, uint32_t flag_mult, uint32_t* __restrict__ flags, unsigned long long* __restrict__ alive_total
 ) {
     __shared__ GemmSmem smem;
     __shared__ uint32_t cnt[kTileM];
@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(256, 2) classify_kernel(
         if (c_alive) atomicAdd(&cnt[r], c_alive);
     }
     __syncthreads();
-    if (static_cast<int>(threadIdx.x) < m_valid) flags[row0 + threadIdx.x] = (cnt[threadIdx.x] * 16u >= static_cast<uint32_t>(n_sample)) ? 1u : 0u;
+    if (static_cast<int>(threadIdx.x) < m_valid) flags[row0 + threadIdx.x] = (cnt[threadIdx.x] * flag_mult >= static_cast<uint32_t>(n_sample)) ? 1u : 0u;
     // total number of sampled pairs that pass the first test (estimates the pass's survival rate)
     if (threadIdx.x < 32) {
         uint32_t s = 0;
@@ -330,7 +330,7 @@ void launch_pruned_prepare(const PrunedParams& p, PruneSplitWorkspace& ws, cudaS
     const float ratio_first = ws.ratio_first;
     SKM_CUDA(cudaMemsetAsync(ws.alive_total, 0, sizeof(unsigned long long), stream));
     classify_kernel<<<static_cast<unsigned>((p.n + kTileM - 1) / kTileM), 256, 0, stream>>>(p.x, ws.sample, ws.sample_norms, p.norms_x, ws.best, p.n, p.d, p.partial_d, n_sample,
-                                                                                             ratio_first, ws.flags, ws.alive_total);
+                                                                                             ratio_first, ws.flag_mult, ws.flags, ws.alive_total);
     SKM_LAUNCH_CHECK();
     copy_u32_kernel<<<static_cast<unsigned>((p.n + 255) / 256), 256, 0, stream>>>(ws.flags, ws.positions, p.n);
     SKM_LAUNCH_CHECK();

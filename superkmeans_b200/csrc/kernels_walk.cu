@@ -11,15 +11,16 @@
 //     lowered) and counts the survivors per point (the not-pruned counter);
 //   * holds the pair with the point's previous centroid back until that count is known and drops it
 //     when it is the only survivor;
-//   * advances all surviving pairs together, 64 horizontal dimensions at a time (eight lanes per pair,
-//     128 contiguous bytes of the PDX block per lane group), re-testing after every block and compacting
-//     the list in shared memory, so lanes never idle behind a pair that died early;
+//   * keeps the surviving pairs of a batch in shared memory sorted by point and gives every group of eight
+//     lanes a contiguous run of them; a group advances its run 64 horizontal dimensions at a time (128
+//     contiguous bytes of the PDX block per load, the point's slice held in registers while the point does
+//     not change), re-tests after every block and compacts the run in place, so no lane idles behind a pair
+//     that died early and no block-wide barrier is needed between blocks; the runs are evened out once,
+//     after the first two blocks;
 //   * adds the vertical dimensions [d', vertical_d), takes the per-point minimum, lowers `best`.
 // `best` is constant inside a chunk, so pairs are independent and any processing order gives the same
 // result.
 #include <cfloat>
-#include <cstdio>
-#include <cstdlib>
 
 #include "common.cuh"
 #include "device_utils.cuh"
@@ -29,34 +30,30 @@ namespace skmb {
 namespace {
 
 constexpr int kWalkThreads = 256;
-constexpr int kWalkBatch = 2048;                  // pairs advanced together
+constexpr int kWalkGroups = kWalkThreads / 8;     // lane groups of eight, one pair at a time each
+constexpr int kWalkPerThread = 8;                 // listed pairs a thread loads per batch
+constexpr int kWalkBatch = kWalkThreads * kWalkPerThread;
 constexpr int kWalkListCap = kWalkBatch + kTileM; // + the held-back pairs with the previous centroid
+constexpr int kRebalanceAfter = 2;                // blocks after which the runs are evened out once
 
 struct WalkShared {
-    uint2 list[2][kWalkListCap];   // {local centroid << 7 | row in tile, partial distance}
+    uint2 list[2][kWalkListCap];   // {local centroid << 7 | row in tile, partial distance}, sorted by row
     float best[kTileM];
     float thr[kTileM];
     float prev_pd[kTileM];
     uint32_t bestidx[kTileM];
     uint32_t prev[kTileM];
-    uint32_t cnt[kTileM];
+    uint32_t cnt[kTileM];          // survivors of the first test in this chunk
     uint32_t npc[kTileM];
     uint32_t prev_flag[kTileM];
     uint32_t active[kTileM];
+    uint32_t hist[kTileM];         // survivors per row in this batch, then their first position
+    uint32_t cursor[kTileM];
+    uint32_t warp_tot[4];
+    uint32_t gcount[kWalkGroups];
     unsigned long long key[kTileM];
-    uint32_t count[2];
+    uint32_t m;
 };
-
-// Appends `ent` for the lanes with keep != 0 (one lane per pair calls with keep set); one shared-memory atomic per warp.
-__device__ __forceinline__ void warp_append(uint2* list, uint32_t* counter, bool keep, uint2 ent) {
-    const uint32_t m = __ballot_sync(0xffffffffu, keep);
-    if (m == 0) return;
-    const int lane = threadIdx.x & 31;
-    uint32_t base = 0;
-    if (lane == __ffs(m) - 1) base = atomicAdd(counter, __popc(m));
-    base = __shfl_sync(0xffffffffu, base, __ffs(m) - 1);
-    if (keep) list[base + __popc(m & ((1u << lane) - 1u))] = ent;
-}
 
 __device__ __forceinline__ float sqdiff8(const float4 a0, const float4 a1, const float4 b0, const float4 b1) {
     float s0, s1, t;
@@ -71,14 +68,66 @@ __device__ __forceinline__ float sqdiff8(const float4 a0, const float4 a1, const
     return s0 + s1;
 }
 
+__device__ __forceinline__ float group_sum(float s, uint32_t gmask) {
+    s += __shfl_xor_sync(gmask, s, 4);
+    s += __shfl_xor_sync(gmask, s, 2);
+    s += __shfl_xor_sync(gmask, s, 1);
+    return s;
+}
+
+// One 64-dimension block for the run [beg, beg + cnt) of `list`, compacted in place; returns the new length.
+// All eight lanes of the group execute this together.  The point's slice of the block stays in registers
+// while consecutive pairs belong to the same point (the list is sorted by point).
+__device__ __forceinline__ uint32_t walk_block(uint2* list, uint32_t beg, uint32_t cnt, const float* __restrict__ blk, const float* __restrict__ xblk, size_t d,
+                                               const float* best, float ratio, int gl, uint32_t gmask) {
+    uint32_t j = 0, xrow = 0xFFFFFFFFu;
+    float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f), x1 = x0;
+    for (uint32_t i = 0; i < cnt; i += 2) {
+        const bool vb = i + 1 < cnt;
+        const uint2 ea = list[beg + i];
+        const uint2 eb = list[beg + (vb ? i + 1 : i)];
+        const uint32_t ra = ea.x & 127u, rb = eb.x & 127u;
+        const float* ca = blk + static_cast<size_t>(ea.x >> 7) * kHBlock;
+        const float* cb = blk + static_cast<size_t>(eb.x >> 7) * kHBlock;
+        const float4 ca0 = __ldg(reinterpret_cast<const float4*>(ca)), ca1 = __ldg(reinterpret_cast<const float4*>(ca + 4));
+        const float4 cb0 = __ldg(reinterpret_cast<const float4*>(cb)), cb1 = __ldg(reinterpret_cast<const float4*>(cb + 4));
+        if (ra != xrow) {
+            const float* q = xblk + static_cast<size_t>(ra) * d;
+            x0 = __ldg(reinterpret_cast<const float4*>(q));
+            x1 = __ldg(reinterpret_cast<const float4*>(q + 4));
+            xrow = ra;
+        }
+        const float sa = group_sum(sqdiff8(x0, x1, ca0, ca1), gmask);
+        if (rb != xrow) {
+            const float* q = xblk + static_cast<size_t>(rb) * d;
+            x0 = __ldg(reinterpret_cast<const float4*>(q));
+            x1 = __ldg(reinterpret_cast<const float4*>(q + 4));
+            xrow = rb;
+        }
+        const float sb = group_sum(sqdiff8(x0, x1, cb0, cb1), gmask);
+        const float pda = __uint_as_float(ea.y) + sa;
+        const float pdb = __uint_as_float(eb.y) + sb;
+        const bool ka = pda < best[ra] * ratio;
+        const bool kb = vb && pdb < best[rb] * ratio;
+        if (gl == 0) {
+            if (ka) list[beg + j] = make_uint2(ea.x, __float_as_uint(pda));
+            if (kb) list[beg + j + (ka ? 1u : 0u)] = make_uint2(eb.x, __float_as_uint(pdb));
+        }
+        j += (ka ? 1u : 0u) + (kb ? 1u : 0u);
+    }
+    __syncwarp(gmask);
+    return j;
+}
+
 __global__ void __launch_bounds__(kWalkThreads, 3) walk_lists_kernel(const WalkParams w) {
     __shared__ WalkShared sh;
-    const int tid = threadIdx.x, lane = tid & 31;
-    const int g = tid >> 3, gl = tid & 7;            // 32 lane groups of 8
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = tid >> 3, gl = tid & 7;
     const uint32_t gmask = 0xFFu << (lane & 24);
     const size_t n_chunks = (w.k + kChunk - 1) / kChunk;
     const size_t n_h = w.horizontal_d / kHBlock;
     const float ratio_first = __ldg(w.ratios + w.partial_d);
+    unsigned long long steps_done = 0;
 
     for (size_t tile = blockIdx.x; tile < w.n_tiles; tile += gridDim.x) {
         const size_t row0 = (w.tile0 + tile) * kTileM;
@@ -109,8 +158,6 @@ __global__ void __launch_bounds__(kWalkThreads, 3) walk_lists_kernel(const WalkP
                 sh.prev_flag[tid] = 0;
                 sh.key[tid] = ~0ull;
             }
-            if (tid == 0) sh.count[0] = 0;
-            __syncthreads();
 
             // The chunk's pairs of the four row groups, taken as one sequence of `total` positions.
             uint32_t gbeg[4], glen[4];
@@ -124,18 +171,26 @@ __global__ void __launch_bounds__(kWalkThreads, 3) walk_lists_kernel(const WalkP
                 total += glen[q];
             }
             const uint2* base_list = w.lists + tile * 4 * static_cast<size_t>(w.cap_group);
+            const float* __restrict__ blk_chunk = w.y_pdx + chunk * kChunk * w.d + static_cast<size_t>(w.vertical_d) * cs;
 
             uint32_t b0 = 0;
             do {
                 const uint32_t b1 = min(b0 + static_cast<uint32_t>(kWalkBatch), total);
                 const bool last_batch = b1 == total;
-                // ---- load, re-test against the current threshold, count, hold the previous centroid's pair back
-                for (uint32_t e0 = b0; e0 < b1; e0 += kWalkThreads) {
-                    const uint32_t e = e0 + tid;
-                    bool keep = false;
-                    uint2 ent = make_uint2(0, 0);
+                if (tid < kTileM) {
+                    sh.hist[tid] = 0;
+                    sh.cursor[tid] = 0;
+                }
+                __syncthreads();
+                // ---- load, re-test against the current threshold, count; the previous centroid's pair is held back
+                uint2 mine[kWalkPerThread];
+                uint32_t keep = 0;
+#pragma unroll
+                for (int u = 0; u < kWalkPerThread; ++u) {
+                    const uint32_t e = b0 + u * kWalkThreads + tid;
+                    mine[u] = make_uint2(0, 0);
                     if (e < b1) {
-                        uint32_t q = 0, off = e - 0u;
+                        uint32_t q = 0, off = e;
                         if (off >= glen[0]) {
                             off -= glen[0];
                             q = 1;
@@ -159,103 +214,134 @@ __global__ void __launch_bounds__(kWalkThreads, 3) walk_lists_kernel(const WalkP
                                 sh.prev_pd[r] = pd;
                                 sh.prev_flag[r] = 1u;
                             } else {
-                                keep = true;
-                                ent = make_uint2(((col - static_cast<uint32_t>(c0)) << 7) | r, raw.y);
+                                keep |= 1u << u;
+                                mine[u] = make_uint2(((col - static_cast<uint32_t>(c0)) << 7) | r, raw.y);
+                                atomicAdd(&sh.hist[r], 1u);
                             }
                         }
                     }
-                    warp_append(sh.list[0], &sh.count[0], keep, ent);
                 }
                 __syncthreads();
-                if (last_batch) {
-                    // the survivor counts of the chunk are final now
-                    bool keep = false;
-                    uint2 ent = make_uint2(0, 0);
-                    if (tid < kTileM && sh.prev_flag[tid] && sh.cnt[tid] != 1u) {
-                        keep = true;
-                        ent = make_uint2(((sh.prev[tid] - static_cast<uint32_t>(c0)) << 7) | tid, __float_as_uint(sh.prev_pd[tid]));
-                    }
-                    if (tid < kTileM) warp_append(sh.list[0], &sh.count[0], keep, ent);
-                    __syncthreads();
+                // the held-back pairs join the last batch, once the survivor counts of the chunk are final
+                bool add_prev = false;
+                if (last_batch && tid < kTileM && sh.prev_flag[tid] && sh.cnt[tid] != 1u) {
+                    add_prev = true;
+                    sh.hist[tid] += 1u;   // only this thread touches its row's counter here
                 }
-
-                // ---- horizontal blocks, all pairs of the batch in step
-                int cur = 0;
-                uint32_t m = sh.count[0];
-                const float* __restrict__ blk_chunk = w.y_pdx + chunk * kChunk * w.d + static_cast<size_t>(w.vertical_d) * cs;
-                if (w.step_hist && tid == 0) atomicAdd(&w.step_hist[30], static_cast<unsigned long long>(b1 - b0));
-                for (size_t hb = 0; hb < n_h && m != 0; ++hb) {
-                    if (w.step_hist && tid == 0) atomicAdd(&w.step_hist[hb < 29 ? hb : 29], static_cast<unsigned long long>(m));
-                    if (tid == 0) sh.count[cur ^ 1] = 0;
-                    __syncthreads();
-                    const float ratio = __ldg(w.ratios + w.partial_d + (hb + 1) * kHBlock);
-                    const float* __restrict__ blk = blk_chunk + hb * cs * kHBlock + gl * 8;
-                    const size_t xoff = w.vertical_d + hb * kHBlock + gl * 8;
-                    const uint32_t m_pad = (m + 63u) & ~63u;
-                    for (uint32_t e = g; e < m_pad; e += 64) {
-                        // two pairs per lane group and round, loads of both issued before any arithmetic
-                        const uint32_t ea = e, eb = e + 32;
-                        const bool va = ea < m, vb = eb < m;
-                        const uint2 enta = sh.list[cur][va ? ea : 0];
-                        const uint2 entb = sh.list[cur][vb ? eb : 0];
-                        const uint32_t ra = enta.x & 127u, rb = entb.x & 127u;
-                        const float* ca = blk + static_cast<size_t>(enta.x >> 7) * kHBlock;
-                        const float* cb = blk + static_cast<size_t>(entb.x >> 7) * kHBlock;
-                        const float* qa = w.x + (row0 + ra) * w.d + xoff;
-                        const float* qb = w.x + (row0 + rb) * w.d + xoff;
-                        const float4 ca0 = __ldg(reinterpret_cast<const float4*>(ca)), ca1 = __ldg(reinterpret_cast<const float4*>(ca + 4));
-                        const float4 cb0 = __ldg(reinterpret_cast<const float4*>(cb)), cb1 = __ldg(reinterpret_cast<const float4*>(cb + 4));
-                        const float4 qa0 = __ldg(reinterpret_cast<const float4*>(qa)), qa1 = __ldg(reinterpret_cast<const float4*>(qa + 4));
-                        const float4 qb0 = __ldg(reinterpret_cast<const float4*>(qb)), qb1 = __ldg(reinterpret_cast<const float4*>(qb + 4));
-                        float sa = sqdiff8(qa0, qa1, ca0, ca1);
-                        float sb = sqdiff8(qb0, qb1, cb0, cb1);
-                        sa += __shfl_xor_sync(0xffffffffu, sa, 4);
-                        sb += __shfl_xor_sync(0xffffffffu, sb, 4);
-                        sa += __shfl_xor_sync(0xffffffffu, sa, 2);
-                        sb += __shfl_xor_sync(0xffffffffu, sb, 2);
-                        sa += __shfl_xor_sync(0xffffffffu, sa, 1);
-                        sb += __shfl_xor_sync(0xffffffffu, sb, 1);
-                        const float pda = __uint_as_float(enta.y) + sa;
-                        const float pdb = __uint_as_float(entb.y) + sb;
-                        const bool ka = va && gl == 0 && pda < sh.best[ra] * ratio;
-                        const bool kb = vb && gl == 0 && pdb < sh.best[rb] * ratio;
-                        warp_append(sh.list[cur ^ 1], &sh.count[cur ^ 1], ka, make_uint2(enta.x, __float_as_uint(pda)));
-                        warp_append(sh.list[cur ^ 1], &sh.count[cur ^ 1], kb, make_uint2(entb.x, __float_as_uint(pdb)));
+                // ---- exclusive scan of the per-row counts: pairs are stored sorted by row
+                if (tid < kTileM) {
+                    const uint32_t v = sh.hist[tid];
+                    uint32_t incl = v;
+#pragma unroll
+                    for (int off = 1; off < 32; off <<= 1) {
+                        const uint32_t t = __shfl_up_sync(0xffffffffu, incl, off);
+                        if (lane >= off) incl += t;
                     }
+                    if (lane == 31) sh.warp_tot[warp] = incl;
+                    sh.cursor[tid] = incl - v;   // exclusive inside the warp for now
+                }
+                __syncthreads();
+                if (tid < kTileM) {
+                    uint32_t base = 0;
+                    for (int q = 0; q < warp; ++q) base += sh.warp_tot[q];
+                    const uint32_t start = base + sh.cursor[tid];
+                    sh.hist[tid] = start;
+                    sh.cursor[tid] = 0;
+                }
+                __syncthreads();
+                if (tid == 0) sh.m = sh.warp_tot[0] + sh.warp_tot[1] + sh.warp_tot[2] + sh.warp_tot[3];
+#pragma unroll
+                for (int u = 0; u < kWalkPerThread; ++u) {
+                    if ((keep >> u) & 1u) {
+                        const uint32_t r = mine[u].x & 127u;
+                        sh.list[0][sh.hist[r] + atomicAdd(&sh.cursor[r], 1u)] = mine[u];
+                    }
+                }
+                __syncthreads();
+                if (add_prev) {
+                    sh.list[0][sh.hist[tid] + sh.cursor[tid]] =
+                        make_uint2(((sh.prev[tid] - static_cast<uint32_t>(c0)) << 7) | tid, __float_as_uint(sh.prev_pd[tid]));
+                }
+                __syncthreads();
+
+                // ---- horizontal blocks: every lane group owns a contiguous run of the sorted list
+                int cur = 0;
+                uint32_t m = sh.m;
+                uint32_t run = (m + kWalkGroups - 1) / kWalkGroups;
+                uint32_t beg = min(static_cast<uint32_t>(g) * run, m);
+                uint32_t len = min(run, m - beg);
+                size_t hb = 0;
+                for (; hb < n_h && hb < static_cast<size_t>(kRebalanceAfter); ++hb) {
+                    steps_done += (gl == 0) ? len : 0u;
+                    len = walk_block(sh.list[cur], beg, len, blk_chunk + hb * cs * kHBlock + gl * 8, w.x + row0 * w.d + w.vertical_d + hb * kHBlock + gl * 8, w.d, sh.best,
+                                     __ldg(w.ratios + w.partial_d + (hb + 1) * kHBlock), gl, gmask);
+                }
+                if (hb < n_h) {
+                    // even the runs out once: early blocks remove most of what will ever be removed
+                    if (gl == 0) sh.gcount[g] = len;
+                    __syncthreads();
+                    uint32_t off = 0, tot = 0;
+                    for (int q = 0; q < kWalkGroups; ++q) {
+                        const uint32_t c = sh.gcount[q];
+                        off += (q < g) ? c : 0u;
+                        tot += c;
+                    }
+                    for (uint32_t i = gl; i < len; i += 8) sh.list[cur ^ 1][off + i] = sh.list[cur][beg + i];
                     __syncthreads();
                     cur ^= 1;
-                    m = sh.count[cur];
+                    m = tot;
+                    run = (m + kWalkGroups - 1) / kWalkGroups;
+                    beg = min(static_cast<uint32_t>(g) * run, m);
+                    len = min(run, m - beg);
+                    for (; hb < n_h; ++hb) {
+                        steps_done += (gl == 0) ? len : 0u;
+                        len = walk_block(sh.list[cur], beg, len, blk_chunk + hb * cs * kHBlock + gl * 8, w.x + row0 * w.d + w.vertical_d + hb * kHBlock + gl * 8, w.d,
+                                         sh.best, __ldg(w.ratios + w.partial_d + (hb + 1) * kHBlock), gl, gmask);
+                    }
                 }
 
                 // ---- vertical dimensions [d', vertical_d) and the minimum of the chunk
-                if (w.step_hist && tid == 0) atomicAdd(&w.step_hist[31], static_cast<unsigned long long>(m));
-                if (m != 0) {
-                    const uint32_t len = w.vertical_d - w.partial_d;
-                    for (uint32_t e = g; e < m; e += 32) {
-                        const uint2 ent = sh.list[cur][e];
+                {
+                    const uint32_t vlen = w.vertical_d - w.partial_d;
+                    for (uint32_t i = 0; i < len; ++i) {
+                        const uint2 ent = sh.list[cur][beg + i];
                         const uint32_t r = ent.x & 127u;
                         const size_t c = c0 + (ent.x >> 7);
                         float pd = __uint_as_float(ent.y);
-                        if (len != 0) {
+                        if (vlen != 0) {
                             const float* __restrict__ cp = w.y_aux + c * w.vertical_d + w.partial_d;
                             const float* __restrict__ qp = w.x + (row0 + r) * w.d + w.partial_d;
+                            // scalar head up to a 16-byte boundary (both rows start at a multiple of four floats, so
+                            // they share it), float4 body, scalar rest
+                            const uint32_t head = min(vlen, (4u - (w.partial_d & 3u)) & 3u);
+                            const uint32_t n4 = (vlen - head) >> 2;
+                            const uint32_t rest0 = head + (n4 << 2);
                             float s = 0.f;
-                            for (uint32_t j = gl; j < len; j += 8) {
-                                const float t = __ldg(qp + j) - __ldg(cp + j);
+                            if (static_cast<uint32_t>(gl) < head) {
+                                const float t = __ldg(qp + gl) - __ldg(cp + gl);
+                                s = t * t;
+                            }
+                            if (rest0 + gl < vlen) {
+                                const float t = __ldg(qp + rest0 + gl) - __ldg(cp + rest0 + gl);
                                 s = fmaf(t, t, s);
                             }
-                            s += __shfl_xor_sync(gmask, s, 4);
-                            s += __shfl_xor_sync(gmask, s, 2);
-                            s += __shfl_xor_sync(gmask, s, 1);
-                            pd += s;
+                            const float4* q4 = reinterpret_cast<const float4*>(qp + head);
+                            const float4* c4 = reinterpret_cast<const float4*>(cp + head);
+                            for (uint32_t jj = gl; jj < n4; jj += 8) {
+                                const float4 a = __ldg(q4 + jj), b = __ldg(c4 + jj);
+                                float t;
+                                t = a.x - b.x; s = fmaf(t, t, s);
+                                t = a.y - b.y; s = fmaf(t, t, s);
+                                t = a.z - b.z; s = fmaf(t, t, s);
+                                t = a.w - b.w; s = fmaf(t, t, s);
+                            }
+                            pd += group_sum(s, gmask);
                         }
                         if (gl == 0 && pd < sh.best[r]) {
                             atomicMin(&sh.key[r], (static_cast<unsigned long long>(float_to_ordered(pd)) << 32) | static_cast<unsigned long long>(c));
                         }
                     }
                 }
-                __syncthreads();
-                if (tid == 0) sh.count[0] = 0;
                 __syncthreads();
                 b0 = b1;
             } while (b0 < total);
@@ -278,6 +364,7 @@ __global__ void __launch_bounds__(kWalkThreads, 3) walk_lists_kernel(const WalkP
         }
         __syncthreads();
     }
+    if (gl == 0 && steps_done) atomicAdd(w.pair_steps, steps_done);
 }
 
 } // namespace
@@ -287,25 +374,8 @@ void launch_walk_lists(const WalkParams& w, int device, cudaStream_t stream) {
     int sms = 0;
     SKM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
     const unsigned grid = static_cast<unsigned>(std::min<size_t>(w.n_tiles, static_cast<size_t>(sms) * 3));
-    static unsigned long long* hist_dev = nullptr;
-    const bool want_hist = std::getenv("SKM_WALK_DEBUG") != nullptr;
-    WalkParams wp = w;
-    wp.step_hist = nullptr;
-    if (want_hist) {
-        if (!hist_dev) SKM_CUDA(cudaMalloc(&hist_dev, 32 * sizeof(unsigned long long)));
-        SKM_CUDA(cudaMemsetAsync(hist_dev, 0, 32 * sizeof(unsigned long long), stream));
-        wp.step_hist = hist_dev;
-    }
-    walk_lists_kernel<<<grid, kWalkThreads, 0, stream>>>(wp);
+    walk_lists_kernel<<<grid, kWalkThreads, 0, stream>>>(w);
     SKM_LAUNCH_CHECK();
-    if (want_hist) {
-        unsigned long long h[32];
-        SKM_CUDA(cudaMemcpyAsync(h, hist_dev, sizeof(h), cudaMemcpyDeviceToHost, stream));
-        SKM_CUDA(cudaStreamSynchronize(stream));
-        std::fprintf(stderr, "[walk dbg] listed %llu | alive entering block:", h[30]);
-        for (int i = 0; i < 16; ++i) std::fprintf(stderr, " %llu", h[i]);
-        std::fprintf(stderr, " | entering tail %llu\n", h[31]);
-    }
 }
 
 } // namespace skmb

@@ -135,6 +135,12 @@ class Engine:
     def last_prune_path(self) -> int:
         return int(lib.skm_last_prune_path(self._h))
 
+    def prune_counters(self) -> dict:
+        """Work of the pruned passes so far: rows through a dense chain, pair-steps of the list walk, overflowed rows."""
+        out = (C.c_uint64 * 3)()
+        check(lib.skm_get_prune_counters(self._h, out), self._h)
+        return {"dense_rows": int(out[0]), "walk_pair_steps": int(out[1]), "overflow_rows": int(out[2])}
+
     @property
     def last_objective_f64(self) -> float:
         return float(lib.skm_last_objective_f64(self._h))
@@ -157,7 +163,7 @@ class Engine:
             out.append(dict(n_samples=ns.value, n_clusters=nc.value, partial_d_next=pd.value, centroids=cen, assign=asg, dist=dst, sizes_pre=s0, sizes_post=s1))
         return out
 
-    PHASES = ("rotator", "norms_calc", "search/1st_blas", "search", "update_centroids", "consolidate", "shift", "train")
+    PHASES = ("rotator", "norms_calc", "search/1st_blas", "search", "update_centroids", "consolidate", "shift", "train", "search/first_test", "search/walk", "search/dense")
 
     def phase_times(self) -> dict:
         """{phase name: (device milliseconds, calls)} accumulated since creation / reset."""
