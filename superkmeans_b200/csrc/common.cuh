@@ -58,7 +58,8 @@ void launch_transpose_square(const float* in, float* out, size_t n, cudaStream_t
 // 1024-centroid batch, strict < across batches, clamped at 0 when stored.
 // top2_scratch (n entries, may be null) enables the tensor-core path: tcgen05 pass for the two best
 // candidates per row, then an fp32 refinement; without it the fp32 SIMT kernel runs.
-void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist, uint2* top2_scratch, cudaStream_t stream);
+// y_split (2 * k * d floats, optional): scratch in which the tensor-core path keeps the centroids split into tf32 parts.
+void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist, uint2* top2_scratch, cudaStream_t stream, float* y_split = nullptr);
 
 struct PrunedParams {
     const float* x;             // n x d rotated points

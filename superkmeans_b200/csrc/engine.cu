@@ -459,11 +459,13 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
             const size_t per_batch = std::min(n_tiles, std::max<size_t>(148, budget / tile_bytes));
             uint2* lists = b.tc_lists.ensure(per_batch * 4 * cap_group);
             uint32_t* offs = b.tc_list_offs.ensure(per_batch * 4 * (n_chunks + 1));
+            float* y_split = b.y_split.ensure(2 * p.k * p.d);
+            tc::launch_presplit(p.y, p.k, p.d, y_split, stream);
             for (size_t t0 = 0; t0 < n_tiles; t0 += per_batch) {
                 const size_t nt = std::min(per_batch, n_tiles - t0);
                 {
                     Sub sub(timers, PH_PRUNE_FIRST_TEST, stream);
-                    tc::launch_first_test(p.x, p.y, p.n, p.k, p.d, p.partial_d, p.norms_x, p.norms_y, ws.best, ws.flags, ratio_first, t0, nt, lists, offs, cap_group, stream);
+                    tc::launch_first_test(p.x, p.y, p.n, p.k, p.d, p.partial_d, p.norms_x, p.norms_y, ws.best, ws.flags, ratio_first, t0, nt, lists, offs, cap_group, stream, y_split);
                 }
                 WalkParams w{};
                 w.x = p.x;
@@ -579,7 +581,7 @@ void Engine::run_iteration(bool gemm_only, const IterationInput& in, size_t iter
     if (gemm_only) {
         launch_row_sqnorms(c_prev_.get(), k_cur, d_, d_, centroid_norms_.get(), stream_);
         PhaseScope ps(*this, PH_ASSIGN_FULL);
-        launch_assign_full(in.x, c_prev_.get(), n, k_cur, d_, norms, centroid_norms_.get(), assignments_.get(), distances_.get(), top2_.ensure(n), stream_);
+        launch_assign_full(in.x, c_prev_.get(), n, k_cur, d_, norms, centroid_norms_.get(), assignments_.get(), distances_.get(), top2_.ensure(n), stream_, y_split_.ensure(2 * k_cur * d_));
     } else {
         launch_row_sqnorms(c_prev_.get(), k_cur, d_, partial_d_, centroid_norms_.get(), stream_);
         PhaseScope ps(*this, PH_ASSIGN_PRUNED);
@@ -1012,7 +1014,7 @@ void Engine::assign(const float* vectors, const float* centroids, size_t n, size
     if (on_device) {
         DeviceBuffer<float> xn, dist;
         launch_row_sqnorms(vectors, n, d_, d_, xn.ensure(n), stream_);
-        launch_assign_full(vectors, c_dev, n, n_centroids, d_, xn.get(), cn.get(), out, dist.ensure(n), top2_.ensure(n), stream_);
+        launch_assign_full(vectors, c_dev, n, n_centroids, d_, xn.get(), cn.get(), out, dist.ensure(n), top2_.ensure(n), stream_, y_split_.ensure(2 * n_centroids * d_));
         sync();
         check_tc_error(stream_);
         return;
@@ -1038,7 +1040,7 @@ void Engine::assign(const float* vectors, const float* centroids, size_t n, size
         SKM_CUDA(cudaEventRecord(copied[b], copy_stream_));
         SKM_CUDA(cudaStreamWaitEvent(stream_, copied[b], 0));
         launch_row_sqnorms(xb[b].get(), cnt, d_, d_, xn[b].get(), stream_);
-        launch_assign_full(xb[b].get(), c_dev, cnt, n_centroids, d_, xn[b].get(), cn.get(), knn[b].get(), dist[b].get(), top2_.ensure(rows), stream_);
+        launch_assign_full(xb[b].get(), c_dev, cnt, n_centroids, d_, xn[b].get(), cn.get(), knn[b].get(), dist[b].get(), top2_.ensure(rows), stream_, y_split_.ensure(2 * n_centroids * d_));
         SKM_CUDA(cudaMemcpyAsync(out + r0, knn[b].get(), sizeof(uint32_t) * cnt, cudaMemcpyDeviceToHost, stream_));
         SKM_CUDA(cudaEventRecord(consumed[b], stream_));
     }
@@ -1221,7 +1223,8 @@ void Engine::op_find_nearest(int device, const float* x, const float* y, size_t 
     launch_row_sqnorms(xd.get(), n, d, d, nx.ensure(n), ctx.stream);
     launch_row_sqnorms(yd.get(), k, d, d, ny.ensure(k), ctx.stream);
     DeviceBuffer<uint2> top2;
-    launch_assign_full(xd.get(), yd.get(), n, k, d, nx.get(), ny.get(), knn.ensure(n), dist.ensure(n), top2.ensure(n), ctx.stream);
+    DeviceBuffer<float> ysplit;
+    launch_assign_full(xd.get(), yd.get(), n, k, d, nx.get(), ny.get(), knn.ensure(n), dist.ensure(n), top2.ensure(n), ctx.stream, ysplit.ensure(2 * k * d));
     ctx.download(out_knn, knn.get(), n);
     ctx.download(out_dist, dist.get(), n);
     ctx.sync();

@@ -110,7 +110,7 @@ struct PrunePassBuffers {
     DeviceBuffer<uint32_t> flags, positions, hard_idx, n_hard_dev;
     DeviceBuffer<uint2> tc_lists, listed_top2;
     DeviceBuffer<uint32_t> tc_list_offs, redo, listed_knn, listed_np;
-    DeviceBuffer<float> listed_x, listed_best, listed_dist, listed_norms;
+    DeviceBuffer<float> listed_x, listed_best, listed_dist, listed_norms, y_split;
     DeviceBuffer<unsigned long long> alive_total;
     PinnedBuffer<unsigned long long> counters_host;
     int last_path = 0;   // 1 lists (+ dense for flagged points), 3 tensor-core chain, 4 tensor-core first test + list walk
@@ -256,6 +256,7 @@ class Engine {
     PrunePassBuffers prune_bufs_;
     std::vector<float> ratios_host_;
     DeviceBuffer<uint2> top2_;           // candidate pairs of the tensor-core exact assignment
+    DeviceBuffer<float> y_split_;        // centroids split into tf32 hi / lo parts for the tensor-core kernels
     DeviceBuffer<SplitOpDev> split_ops_dev_;
     DeviceBuffer<double> scalars_dev_;   // [0] wcss, [1] not-pruned total (as double), [2] shift
     DeviceBuffer<unsigned long long> np_total_dev_;

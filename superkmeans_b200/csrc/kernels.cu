@@ -207,10 +207,10 @@ __global__ void __launch_bounds__(256, 2) assign_full_kernel(
     }
 }
 
-void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist, uint2* top2_scratch, cudaStream_t stream) {
+void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist, uint2* top2_scratch, cudaStream_t stream, float* y_split) {
     if (n == 0) return;
     if (top2_scratch && tc::eligible(x, d, y, d)) {
-        tc::launch_assign_full(x, y, n, k, d, norms_x, norms_y, out_knn, out_dist, top2_scratch, stream);
+        tc::launch_assign_full(x, y, n, k, d, norms_x, norms_y, out_knn, out_dist, top2_scratch, stream, y_split);
         return;
     }
     const unsigned grid = static_cast<unsigned>((n + kTileM - 1) / kTileM);

@@ -198,12 +198,16 @@ struct Params {
     uint2* lists;          // per 32-row group: cap_group entries {column << 5 | row in group, partial distance}
     uint32_t* list_offs;   // per group: (n_chunks + 1) entry counts at the start of every 1024-centroid chunk
     uint32_t cap_group;
+    // Y arrives already split: tmap_y covers the hi parts, tmap_ylo the lo parts, and the splitter warps
+    // only treat X
+    bool y_presplit;
 };
 
 enum { MODE_ARGMIN = 0, MODE_STORE = 1, MODE_PRUNE = 2 };
 
 template <int MODE>
-__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y, const Params p) {
+__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y,
+                                                                 const __grid_constant__ CUtensorMap tmap_ylo, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -249,10 +253,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                             ok = false;
                             break;
                         }
-                        mbar_arrive_expect_tx(&ctrl->full[s], A_TILE_BYTES + B_TILE_BYTES);
+                        mbar_arrive_expect_tx(&ctrl->full[s], A_TILE_BYTES + (p.y_presplit ? 2 * B_TILE_BYTES : B_TILE_BYTES));
                         const uint32_t st = smem_base + s * STAGE_BYTES;
                         tma_load_2d(st + OFF_A_HI, &tmap_x, &ctrl->full[s], static_cast<int>(kb * BK), static_cast<int>(rt * BM));
                         tma_load_2d(st + OFF_B_HI, &tmap_y, &ctrl->full[s], static_cast<int>(kb * BK), static_cast<int>(nt * BN));
+                        if (p.y_presplit) tma_load_2d(st + OFF_B_LO, &tmap_ylo, &ctrl->full[s], static_cast<int>(kb * BK), static_cast<int>(nt * BN));
                     }
                 }
             }
@@ -320,12 +325,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                         a_hi[cid + 128 * i] = hi;
                         a_lo[cid + 128 * i] = lo;
                     }
+                    if (!p.y_presplit) {
 #pragma unroll
-                    for (int i = 0; i < static_cast<int>(B_TILE_BYTES / 16 / 128); ++i) {
-                        float4 hi, lo;
-                        split4(b_hi[cid + 128 * i], hi, lo);
-                        b_hi[cid + 128 * i] = hi;
-                        b_lo[cid + 128 * i] = lo;
+                        for (int i = 0; i < static_cast<int>(B_TILE_BYTES / 16 / 128); ++i) {
+                            float4 hi, lo;
+                            split4(b_hi[cid + 128 * i], hi, lo);
+                            b_hi[cid + 128 * i] = hi;
+                            b_lo[cid + 128 * i] = lo;
+                        }
                     }
                     fence_proxy_async();
                     mbar_arrive(&ctrl->conv[s]);
@@ -1079,6 +1086,16 @@ __global__ void __launch_bounds__(256) refine_top2_kernel(
     }
 }
 
+// hi = tf32(v), lo = tf32(v - hi) for every element (the split the splitter warps would do in shared memory)
+__global__ void __launch_bounds__(256) split_tf32_kernel(const float4* __restrict__ in, float4* __restrict__ hi, float4* __restrict__ lo, size_t n4) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    float4 h, l;
+    split4(__ldg(in + i), h, l);
+    hi[i] = h;
+    lo[i] = l;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
@@ -1115,6 +1132,16 @@ CUtensorMap make_tmap(const float* base, size_t extent, size_t rows, size_t ld, 
     return m;
 }
 
+// Splits y (rows x ld, 16-byte aligned, ld % 4 == 0) into y_split[0 .. rows*ld) = hi and y_split[rows*ld ..) = lo.
+void presplit(const float* y, size_t rows, size_t ld, float* y_split, cudaStream_t stream) {
+    const size_t n4 = rows * ld / 4;
+    if (n4 == 0) return;
+    split_tf32_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, stream>>>(reinterpret_cast<const float4*>(y), reinterpret_cast<float4*>(y_split),
+                                                                                   reinterpret_cast<float4*>(y_split + rows * ld), n4);
+    note_kernel_launch();
+    SKM_CUDA(cudaGetLastError());
+}
+
 int* error_flag(int device) {
     static std::mutex mu;
     static int* flags[64] = {nullptr};
@@ -1133,13 +1160,13 @@ int sm_count(int device) {
 }
 
 template <int MODE>
-void launch(const CUtensorMap& tx, const CUtensorMap& ty, const Params& p, cudaStream_t stream) {
+void launch(const CUtensorMap& tx, const CUtensorMap& ty, const CUtensorMap& tylo, const Params& p, cudaStream_t stream) {
     SKM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES)));
     int device = 0;
     SKM_CUDA(cudaGetDevice(&device));
     const size_t row_tiles = (p.n + BM - 1) / BM;
     const int grid = static_cast<int>(std::min<size_t>(row_tiles, static_cast<size_t>(sm_count(device))));
-    gemm_tc_kernel<MODE><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, ty, p);
+    gemm_tc_kernel<MODE><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, ty, tylo, p);
     note_kernel_launch();
     SKM_CUDA(cudaGetLastError());
 }
@@ -1147,6 +1174,8 @@ void launch(const CUtensorMap& tx, const CUtensorMap& ty, const Params& p, cudaS
 bool g_enabled = true;
 
 } // namespace
+
+void launch_presplit(const float* y, size_t rows, size_t ld, float* y_split, cudaStream_t stream) { presplit(y, rows, ld, y_split, stream); }
 
 void set_enabled(bool on) { g_enabled = on; }
 bool enabled() { return g_enabled; }
@@ -1159,13 +1188,16 @@ bool eligible(const float* x, size_t ldx, const float* y, size_t ldy) {
 }
 
 void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist,
-                        uint2* top2_scratch, cudaStream_t stream) {
+                        uint2* top2_scratch, cudaStream_t stream, float* y_split) {
     if (n == 0 || k == 0) return;
     int device = 0;
     SKM_CUDA(cudaGetDevice(&device));
+    if (y_split) presplit(y, k, d, y_split, stream);
     const CUtensorMap tx = make_tmap(x, d, n, d, BM);
-    const CUtensorMap ty = make_tmap(y, d, k, d, BN);
+    const CUtensorMap ty = make_tmap(y_split ? y_split : y, d, k, d, BN);
+    const CUtensorMap tylo = y_split ? make_tmap(y_split + k * d, d, k, d, BN) : ty;
     Params p{};
+    p.y_presplit = y_split != nullptr;
     p.n = n;
     p.k = k;
     p.kdim = static_cast<uint32_t>(d);
@@ -1175,7 +1207,7 @@ void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size
     p.out_dist = out_dist;
     p.out_top2 = top2_scratch;
     p.error = error_flag(device);
-    launch<MODE_ARGMIN>(tx, ty, p, stream);
+    launch<MODE_ARGMIN>(tx, ty, tylo, p, stream);
     refine_top2_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, d, norms_x, norms_y, top2_scratch, out_knn, out_dist);
     note_kernel_launch();
     SKM_CUDA(cudaGetLastError());
@@ -1196,20 +1228,23 @@ void launch_assign_full_flagged(const float* x, const float* y, size_t n, size_t
     p.out_dist = out_dist;
     p.out_top2 = top2_scratch;
     p.error = error_word;
-    launch<MODE_ARGMIN>(tx, ty, p, stream);
+    launch<MODE_ARGMIN>(tx, ty, ty, p, stream);
     refine_top2_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, d, norms_x, norms_y, top2_scratch, out_knn, out_dist);
     note_kernel_launch();
     SKM_CUDA(cudaGetLastError());
 }
 
 void launch_first_test(const float* x, const float* y, size_t n, size_t k, size_t d, uint32_t partial_d, const float* norms_x, const float* norms_y, const float* best_in,
-                       const uint32_t* skip, float ratio_first, size_t tile0, size_t n_tiles, uint2* lists, uint32_t* list_offs, uint32_t cap_group, cudaStream_t stream) {
+                       const uint32_t* skip, float ratio_first, size_t tile0, size_t n_tiles, uint2* lists, uint32_t* list_offs, uint32_t cap_group, cudaStream_t stream,
+                       const float* y_split) {
     if (n_tiles == 0 || k == 0) return;
     int device = 0;
     SKM_CUDA(cudaGetDevice(&device));
     const CUtensorMap tx = make_tmap(x, partial_d, n, d, BM);
-    const CUtensorMap ty = make_tmap(y, partial_d, k, d, BN);
+    const CUtensorMap ty = make_tmap(y_split ? y_split : y, partial_d, k, d, BN);
+    const CUtensorMap tylo = y_split ? make_tmap(y_split + k * d, partial_d, k, d, BN) : ty;
     Params p{};
+    p.y_presplit = y_split != nullptr;
     p.n = n;
     p.k = k;
     p.kdim = partial_d;
@@ -1226,7 +1261,7 @@ void launch_first_test(const float* x, const float* y, size_t n, size_t k, size_
     p.cap_group = cap_group;
     SKM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<MODE_PRUNE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES)));
     const int grid = static_cast<int>(std::min<size_t>(n_tiles, static_cast<size_t>(sm_count(device))));
-    gemm_tc_kernel<MODE_PRUNE><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, ty, p);
+    gemm_tc_kernel<MODE_PRUNE><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, ty, tylo, p);
     note_kernel_launch();
     SKM_CUDA(cudaGetLastError());
 }
@@ -1244,7 +1279,7 @@ void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, floa
     p.out = out;
     p.ldo = ldo;
     p.error = error_flag(device);
-    launch<MODE_STORE>(tx, ty, p, stream);
+    launch<MODE_STORE>(tx, ty, ty, p, stream);
 }
 
 void launch_chain(const float* x, const float* y, size_t n, size_t k, size_t d, uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d, const float* chain_norms_x,

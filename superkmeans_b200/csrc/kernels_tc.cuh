@@ -18,8 +18,12 @@ bool eligible(const float* x, size_t ldx, const float* y, size_t ldy);
 
 // top2_scratch: n entries of device scratch (candidate pairs handed from the tensor-core pass to the
 // fp32 refinement).
+// y_split (2 * k * d floats of scratch, optional): the centroids are split into their tf32 hi and lo parts once, in
+// global memory, instead of in shared memory for every tile that uses them.
 void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist,
-                        uint2* top2_scratch, cudaStream_t stream);
+                        uint2* top2_scratch, cudaStream_t stream, float* y_split = nullptr);
+// y_split[0 .. rows*ld) = tf32(y), y_split[rows*ld .. 2*rows*ld) = tf32(y - tf32(y))
+void launch_presplit(const float* y, size_t rows, size_t ld, float* y_split, cudaStream_t stream);
 // Same two kernels, but the word that a kernel sets when one of its bounded waits runs out is supplied by
 // the caller (device memory, zero on entry) instead of coming from this file's lazily allocated per-device word.
 void launch_assign_full_flagged(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist,
@@ -32,7 +36,8 @@ void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, floa
 // partial distance}, at most cap_group entries, in centroid order), and list_offs receives, per group, the
 // number of entries before every 1024-centroid chunk and the total (which exceeds cap_group on overflow).
 void launch_first_test(const float* x, const float* y, size_t n, size_t k, size_t d, uint32_t partial_d, const float* norms_x, const float* norms_y, const float* best_in,
-                       const uint32_t* skip, float ratio_first, size_t tile0, size_t n_tiles, uint2* lists, uint32_t* list_offs, uint32_t cap_group, cudaStream_t stream);
+                       const uint32_t* skip, float ratio_first, size_t tile0, size_t n_tiles, uint2* lists, uint32_t* list_offs, uint32_t cap_group, cudaStream_t stream,
+                       const float* y_split = nullptr);   // y already split by launch_presplit, optional
 
 // Pruned assignment for all n points as a dense ADSampling chain on the tensor cores.  chain_norms_x /
 // chain_norms_y hold, per row, the cumulative squared norm after each of the chain's checkpoints
