@@ -364,7 +364,7 @@ void run_listed_dense(const PrunedParams& p, PruneSplitWorkspace& ws, PrunePassB
     launch_chain_norms(xl, n_listed, p.d, p.partial_d, p.vertical_d, p.horizontal_d, false, b.listed_norms.ensure(n_listed * n_ck), stream);
     launch_chain_norms(p.y, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, true, ws.chain_norms_y, stream);
     tc::launch_chain(xl, p.y, n_listed, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, b.listed_norms.get(), ws.chain_norms_y, p.ratios, bestl, knnl,
-                     b.listed_dist.ensure(n_listed), b.listed_np.ensure(n_listed), b.listed_top2.ensure(n_listed), stream);
+                     b.listed_dist.ensure(n_listed), b.listed_np.ensure(n_listed), b.listed_top2.ensure(n_listed), b.y_split.ensure(2 * p.k * p.d), stream);
     launch_scatter_listed(ws.hard_idx, n_listed, knnl, b.listed_dist.get(), b.listed_np.get(), p.knn, p.dist, p.not_pruned, stream);
 }
 
@@ -436,7 +436,7 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
         launch_chain_norms(p.x, p.n, p.d, p.partial_d, p.vertical_d, p.horizontal_d, false, b.chain_norms_x.ensure(p.n * n_ck), stream);
         launch_chain_norms(p.y, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, true, ws.chain_norms_y, stream);
         tc::launch_chain(p.x, p.y, p.n, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, b.chain_norms_x.get(), ws.chain_norms_y, p.ratios, ws.best, p.knn, p.dist,
-                         p.not_pruned, b.top2.ensure(p.n), stream);
+                         p.not_pruned, b.top2.ensure(p.n), b.y_split.ensure(2 * p.k * p.d), stream);
         return;
     }
     p.best_in = ws.best;

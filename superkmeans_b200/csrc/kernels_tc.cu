@@ -24,6 +24,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <mutex>
+#include <stdexcept>
 
 #include "common.cuh"
 #include "kernels_tc.cuh"
@@ -509,11 +510,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
 // dimensions (pdx/pdxearch.h:118-217); `best` is fixed inside the chunk and lowered at its end
 // (:290-324).  Here the partial distances come from accumulators that keep growing along that same
 // order of dimensions: the MMA warp walks the reduction dimension segment by segment and publishes
-// the accumulator after each one; the epilogue thread of a row reads it (without clearing it), turns
-// it into ||x||^2 + ||c||^2 - 2 x.c over the dimensions seen so far with precomputed cumulative norms,
-// and updates a bit mask of surviving centroids.  Two 256-centroid tiles are in flight on the two
-// accumulators, so the tensor pipe works on one while the other is being tested.  Every quantity a
-// row needs (survivor mask, survivor count, chunk minimum) is private to its thread.
+// the accumulator after each one; the epilogue thread of a row reads it (without clearing it), 32
+// columns at a time, turns it into ||x||^2 + ||c||^2 - 2 x.c over the dimensions seen so far with
+// precomputed cumulative norms, and updates a bit mask of surviving centroids.  Every quantity a row
+// needs (survivor masks, survivor count, chunk minimum) is private to its thread.
 // =================================================================================================
 struct ChainParams {
     size_t n, k;
@@ -528,7 +528,6 @@ struct ChainParams {
     uint32_t* not_pruned;
     uint2* top2;                    // out: the two smallest final distances seen by the chain, per point
     int* error;
-    long long* dbg;                 // optional cycle counters of CTA 0 (profiling aid), 16 slots
 };
 
 struct SegInfo {
@@ -565,70 +564,77 @@ __device__ __forceinline__ SegInfo chain_segment(const ChainParams& p, uint32_t 
 }
 
 struct ChainMaps {
-    CUtensorMap x[3];
-    CUtensorMap y[3];
+    CUtensorMap x[3];     // points, visible extent d' / vertical_d / d
+    CUtensorMap yhi[3];   // tf32 hi parts of the centroids, same extents
+    CUtensorMap ylo[3];   // tf32 lo parts
 };
 
-// Chain kernel geometry: 128 x 128 tiles (one x128 tensor-memory load brings a row's whole tile into
-// registers), six stages of {X hi, X lo, Y hi, Y lo}.
-constexpr int CBN = 128;
-constexpr int CSTAGES = 6;
-constexpr uint32_t C_TILE_BYTES = 128 * BK * 4;            // 8192 for X and for Y
-constexpr uint32_t CSTAGE_BYTES = 4 * C_TILE_BYTES;        // 32768
-constexpr uint32_t C_OFF_A_HI = 0, C_OFF_A_LO = C_TILE_BYTES, C_OFF_B_HI = 2 * C_TILE_BYTES, C_OFF_B_LO = 3 * C_TILE_BYTES;
-constexpr uint32_t C_SMEM_BYTES = CSTAGES * CSTAGE_BYTES + SMEM_CTRL_BYTES + 1024;
-constexpr uint32_t C_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((CBN >> 3) << 17) | ((BM >> 4) << 24);
-
+// Chain kernel geometry: units of 128 points x 256 centroids, the stage layout of the GEMM kernel (X raw ->
+// hi/lo by the splitter warps, Y hi and lo straight from global memory), two accumulators of 256 columns.
+// The two accumulators belong to two neighbouring centroid units that advance through the segments in
+// turn, so the tensor pipe works on one unit while the rows' threads test the other.
 struct ChainCtrl {
-    uint64_t full[CSTAGES];
-    uint64_t conv[CSTAGES];
-    uint64_t empty[CSTAGES];
-    uint64_t acc_ready;    // MMA -> epilogue: the accumulator holds the chain up to this segment
-    uint64_t acc_loaded;   // epilogue -> MMA: every row has copied it to registers
+    uint64_t full[STAGES];
+    uint64_t conv[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t acc_ready[2];    // MMA -> epilogue: accumulator a holds the chain up to the current segment
+    uint64_t acc_loaded[2];   // epilogue -> MMA: every row has read it
     uint32_t tmem_base;
     uint32_t pad;
-    alignas(16) float ny[4][CBN];  // per epilogue warp: centroid norms of the current checkpoint (read as float4)
+    alignas(16) float ny[4][BN];   // per epilogue warp: centroid norms of the unit at the current checkpoint
     float seg_ratio[64];           // ratios[dimensions seen after segment s]
 };
 static_assert(sizeof(ChainCtrl) <= SMEM_CTRL_BYTES, "control block too large");
+constexpr uint32_t C_SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + 1024;
+constexpr uint32_t CHAIN_MAX_SEGMENTS = 64;
 
-__device__ __forceinline__ void umma_tf32_n128(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(C_IDESC), "r"(accumulate)
-        : "memory");
-}
+// Order of work shared by all roles: row tile, chunk of 1024 centroids, pair of 256-centroid units, segment,
+// unit of the pair.  `a` (0 / 1) is the unit's accumulator.
+#define CHAIN_FOR_EACH_UNIT_SEGMENT(...)                                                                  \
+    for (size_t rt = blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {                               \
+        for (uint32_t chunk = 0; chunk < n_chunks && ok; ++chunk) {                                       \
+            const size_t c0 = static_cast<size_t>(chunk) * kChunk;                                        \
+            const uint32_t cs = static_cast<uint32_t>(min(static_cast<size_t>(kChunk), p.k - c0));        \
+            const uint32_t n_units = (cs + BN - 1) / BN;                                                  \
+            for (uint32_t pair = 0; pair * 2 < n_units && ok; ++pair) {                                   \
+                for (uint32_t seg = 0; seg < p.n_seg && ok; ++seg) {                                      \
+                    const SegInfo si = chain_segment(p, seg);                                             \
+                    for (uint32_t a = 0; a < 2 && ok; ++a) {                                              \
+                        const uint32_t unit = pair * 2 + a;                                               \
+                        if (unit >= n_units) break;                                                       \
+                        __VA_ARGS__                                                                       \
+                    }                                                                                     \
+                }                                                                                         \
+            }                                                                                             \
+        }                                                                                                 \
+    }
 
-// Work units, walked identically by all roles: row tile -> chunk of 1024 centroids -> 128-centroid tile
-// -> segment of the chain.  The MMA warp issues a segment only after the epilogue has copied the
-// previous unit's accumulator to registers: tensor-memory loads queue behind MMAs already issued, so
-// letting the next unit's MMAs go first would stall every load for the length of a segment.
 __global__ void __launch_bounds__(NUM_THREADS, 1) chain_tc_kernel(const __grid_constant__ ChainMaps maps, const ChainParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
     uint8_t* smem = smem_raw + pad;
     const uint32_t smem_base = raw_addr + pad;
-    ChainCtrl* ctrl = reinterpret_cast<ChainCtrl*>(smem + CSTAGES * CSTAGE_BYTES);
+    ChainCtrl* ctrl = reinterpret_cast<ChainCtrl*>(smem + STAGES * STAGE_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < CSTAGES; ++s) {
+        for (int s = 0; s < STAGES; ++s) {
             mbar_init(&ctrl->full[s], 1);
             mbar_init(&ctrl->conv[s], 128);
             mbar_init(&ctrl->empty[s], 1);
         }
-        mbar_init(&ctrl->acc_ready, 1);
-        mbar_init(&ctrl->acc_loaded, 128);
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&ctrl->acc_ready[a], 1);
+            mbar_init(&ctrl->acc_loaded[a], 128);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
     }
-    if (threadIdx.x >= 64 && threadIdx.x < 64 + 64 && threadIdx.x - 64 < p.n_seg) {
+    if (threadIdx.x >= 64 && threadIdx.x < 64 + CHAIN_MAX_SEGMENTS && threadIdx.x - 64 < p.n_seg) {
         ctrl->seg_ratio[threadIdx.x - 64] = __ldg(p.ratios + chain_segment(p, threadIdx.x - 64).dims_after);
     }
-    if (warp == 1) tmem_alloc(&ctrl->tmem_base, 128);
+    if (warp == 1) tmem_alloc(&ctrl->tmem_base, TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -637,111 +643,87 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) chain_tc_kernel(const __grid_c
     const size_t n_row_tiles = (p.n + BM - 1) / BM;
     const uint32_t n_chunks = static_cast<uint32_t>((p.k + kChunk - 1) / kChunk);
 
-#define CHAIN_FOR_EACH_UNIT(...)                                                                         \
-    for (size_t rt = blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {                              \
-        for (uint32_t chunk = 0; chunk < n_chunks && ok; ++chunk) {                                      \
-            const size_t c0 = static_cast<size_t>(chunk) * kChunk;                                       \
-            const uint32_t cs = static_cast<uint32_t>(min(static_cast<size_t>(kChunk), p.k - c0));       \
-            const uint32_t n_tiles = (cs + CBN - 1) / CBN;                                               \
-            for (uint32_t tile = 0; tile < n_tiles && ok; ++tile) {                                      \
-                for (uint32_t seg = 0; seg < p.n_seg && ok; ++seg) {                                     \
-                    const SegInfo si = chain_segment(p, seg);                                            \
-                    __VA_ARGS__                                                                          \
-                }                                                                                        \
-            }                                                                                            \
-        }                                                                                                \
-    }
-
     if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
             uint32_t kbt = 0;
             bool ok = true;
-            long long p_wait_empty = 0;
-            CHAIN_FOR_EACH_UNIT({
+            CHAIN_FOR_EACH_UNIT_SEGMENT({
                 const CUtensorMap* mx = &maps.x[si.map];
-                const CUtensorMap* my = &maps.y[si.map];
+                const CUtensorMap* mh = &maps.yhi[si.map];
+                const CUtensorMap* ml = &maps.ylo[si.map];
+                const int yrow = static_cast<int>(c0 + static_cast<size_t>(unit) * BN);
                 for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
-                    const uint32_t s = kbt % CSTAGES, ph = (kbt / CSTAGES) & 1u;
-                    const long long tp0 = clock64();
+                    const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
                     if (!mbar_wait(&ctrl->empty[s], ph ^ 1u, p.error, 11)) {
                         ok = false;
                         break;
                     }
-                    p_wait_empty += clock64() - tp0;
-                    mbar_arrive_expect_tx(&ctrl->full[s], 2 * C_TILE_BYTES);
-                    const uint32_t st = smem_base + s * CSTAGE_BYTES;
+                    mbar_arrive_expect_tx(&ctrl->full[s], A_TILE_BYTES + 2 * B_TILE_BYTES);
+                    const uint32_t st = smem_base + s * STAGE_BYTES;
                     const int xc = static_cast<int>(si.x_begin + kb * BK);
-                    tma_load_2d(st + C_OFF_A_HI, mx, &ctrl->full[s], xc, static_cast<int>(rt * BM));
-                    tma_load_2d(st + C_OFF_B_HI, my, &ctrl->full[s], xc, static_cast<int>(c0 + tile * CBN));
+                    tma_load_2d(st + OFF_A_HI, mx, &ctrl->full[s], xc, static_cast<int>(rt * BM));
+                    tma_load_2d(st + OFF_B_HI, mh, &ctrl->full[s], xc, yrow);
+                    tma_load_2d(st + OFF_B_LO, ml, &ctrl->full[s], xc, yrow);
                 }
             })
-            if (p.dbg && blockIdx.x == 0) p.dbg[9] = p_wait_empty;
         }
     } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            uint32_t kbt = 0, unit = 0;
+            uint32_t kbt = 0;
+            uint32_t uses[2] = {0, 0};
             bool ok = true;
-            long long m_wait_loaded = 0, m_wait_conv = 0;
-            CHAIN_FOR_EACH_UNIT({
-                const long long tm0 = clock64();
-                if (unit > 0 && !mbar_wait(&ctrl->acc_loaded, (unit - 1) & 1u, p.error, 12)) {
+            CHAIN_FOR_EACH_UNIT_SEGMENT({
+                // the rows must have read this accumulator's previous checkpoint before it grows (or restarts)
+                if (uses[a] > 0 && !mbar_wait(&ctrl->acc_loaded[a], (uses[a] - 1) & 1u, p.error, 12)) {
                     ok = false;
                     break;
                 }
-                m_wait_loaded += clock64() - tm0;
                 tc_fence_after();
+                const uint32_t acc = tmem_base + a * BN;
                 for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
-                    const uint32_t s = kbt % CSTAGES, ph = (kbt / CSTAGES) & 1u;
-                    const long long tm1 = clock64();
+                    const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
                     if (!mbar_wait(&ctrl->conv[s], ph, p.error, 13)) {
                         ok = false;
                         break;
                     }
-                    m_wait_conv += clock64() - tm1;
                     tc_fence_after();
-                    const uint32_t st = smem_base + s * CSTAGE_BYTES;
+                    const uint32_t st = smem_base + s * STAGE_BYTES;
 #pragma unroll
                     for (uint32_t kk = 0; kk < BK / 8; ++kk) {
-                        const uint64_t a_hi = make_desc(st + C_OFF_A_HI + kk * 32);
-                        const uint64_t a_lo = make_desc(st + C_OFF_A_LO + kk * 32);
-                        const uint64_t b_hi = make_desc(st + C_OFF_B_HI + kk * 32);
-                        const uint64_t b_lo = make_desc(st + C_OFF_B_LO + kk * 32);
-                        umma_tf32_n128(tmem_base, a_hi, b_hi, (seg | kb | kk) != 0 ? 1u : 0u);
-                        umma_tf32_n128(tmem_base, a_hi, b_lo, 1u);
-                        umma_tf32_n128(tmem_base, a_lo, b_hi, 1u);
+                        const uint64_t a_hi = make_desc(st + OFF_A_HI + kk * 32);
+                        const uint64_t a_lo = make_desc(st + OFF_A_LO + kk * 32);
+                        const uint64_t b_hi = make_desc(st + OFF_B_HI + kk * 32);
+                        const uint64_t b_lo = make_desc(st + OFF_B_LO + kk * 32);
+                        umma_tf32(acc, a_hi, b_hi, (seg | kb | kk) != 0 ? 1u : 0u);
+                        umma_tf32(acc, a_hi, b_lo, 1u);
+                        umma_tf32(acc, a_lo, b_hi, 1u);
                     }
                     umma_commit(&ctrl->empty[s]);
                 }
-                if (ok) umma_commit(&ctrl->acc_ready);
-                ++unit;
+                if (ok) umma_commit(&ctrl->acc_ready[a]);
+                ++uses[a];
             })
-            if (p.dbg && blockIdx.x == 0) {
-                p.dbg[4] = m_wait_loaded;
-                p.dbg[5] = m_wait_conv;
-            }
         }
     } else if (warp < 6) {
+        // ---------------------------------------------------------------- hi / lo splitter of the X tile
         const int cid = threadIdx.x - 64;
         uint32_t kbt = 0;
         bool ok = true;
-        long long s_wait_full = 0, s_total0 = clock64();
-        CHAIN_FOR_EACH_UNIT({
+        CHAIN_FOR_EACH_UNIT_SEGMENT({
             for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
-                const uint32_t s = kbt % CSTAGES, ph = (kbt / CSTAGES) & 1u;
-                const long long ts0 = clock64();
+                const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
                 if (!mbar_wait(&ctrl->full[s], ph, p.error, 14)) {
                     ok = false;
                     break;
                 }
-                s_wait_full += clock64() - ts0;
-                uint8_t* st = smem + s * CSTAGE_BYTES;
-                float4* a_hi = reinterpret_cast<float4*>(st + C_OFF_A_HI);
-                float4* a_lo = reinterpret_cast<float4*>(st + C_OFF_A_LO);
-                float4* b_hi = reinterpret_cast<float4*>(st + C_OFF_B_HI);
-                float4* b_lo = reinterpret_cast<float4*>(st + C_OFF_B_LO);
+                uint8_t* st = smem + s * STAGE_BYTES;
+                float4* a_hi = reinterpret_cast<float4*>(st + OFF_A_HI);
+                float4* a_lo = reinterpret_cast<float4*>(st + OFF_A_LO);
                 const bool mask = (kb == 0) && (si.mask_below > si.x_begin);
 #pragma unroll
-                for (int i = 0; i < static_cast<int>(C_TILE_BYTES / 16 / 128); ++i) {
+                for (int i = 0; i < static_cast<int>(A_TILE_BYTES / 16 / 128); ++i) {
                     const int q = cid + 128 * i;
                     float4 v = a_hi[q];
                     if (mask) {
@@ -757,25 +739,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) chain_tc_kernel(const __grid_c
                     split4(v, hi, lo);
                     a_hi[q] = hi;
                     a_lo[q] = lo;
-                    split4(b_hi[q], hi, lo);
-                    b_hi[q] = hi;
-                    b_lo[q] = lo;
                 }
                 fence_proxy_async();
                 mbar_arrive(&ctrl->conv[s]);
             }
         })
-        if (p.dbg && blockIdx.x == 0 && cid == 0) {
-            p.dbg[6] = s_wait_full;
-            p.dbg[7] = clock64() - s_total0;
-            p.dbg[8] = kbt;
-        }
     } else {
+        // ---------------------------------------------------------------- rows: tests at every checkpoint
         const uint32_t lane_base = 32u * (warp & 3);
         const uint32_t row_in_tile = lane_base + lane;
-        uint32_t unit = 0;
+        uint32_t uses[2] = {0, 0};
         bool ok = true;
-        // per-row state (private to this thread)
         size_t cur_rt = ~size_t{0};
         uint32_t cur_chunk = 0xFFFFFFFFu;
         size_t row = 0;
@@ -783,19 +757,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) chain_tc_kernel(const __grid_c
         float best = -1.f, cb = FLT_MAX, t1 = FLT_MAX, t2 = FLT_MAX;
         uint32_t bestidx = 0, prev = 0xFFFFFFFFu, npc = 0, cnt = 0, cbi = 0, i1 = 0xFFFFFFFFu, i2 = 0xFFFFFFFFu;
         bool prev_first = false;
-        uint32_t alive[CBN / 32] = {0, 0, 0, 0};
-        float* ny = ctrl->ny[warp & 3];
-        long long dbg_wait = 0, dbg_ld = 0, dbg_other = 0, dbg_prev = clock64();
-        float nx_row[64];          // cumulative norms of this thread's row, one per checkpoint
-        float ny_next[CBN / 32];   // centroid norms of the next unit, fetched one unit ahead
-        bool ny_next_valid = false;
-        // centroid norms of unit (rt, chunk, tile, seg) for this lane: columns lane, lane+32, ...
-        auto fetch_ny = [&](uint32_t chunk_, uint32_t tile_, uint32_t seg_, float (&dst)[CBN / 32]) {
-            const size_t col0_ = static_cast<size_t>(chunk_) * kChunk + static_cast<size_t>(tile_) * CBN;
-            const float* __restrict__ src = p.chain_norms_y + static_cast<size_t>(seg_) * p.k + col0_;
+        // survivor masks of the two units in flight (kept apart so that both stay in registers)
+        uint32_t alive0[BN / 32], alive1[BN / 32];
 #pragma unroll
-            for (uint32_t q = 0; q < CBN / 32; ++q) dst[q] = (col0_ + q * 32 + lane < p.k) ? __ldg(src + q * 32 + lane) : 0.f;
-        };
+        for (int q = 0; q < BN / 32; ++q) alive0[q] = alive1[q] = 0;
+        float* ny = ctrl->ny[warp & 3];
         auto close_chunk = [&]() {
             npc += cnt;
             // pdxearch.h:140-143: the previous centroid as the only survivor leaves the candidate untouched
@@ -816,7 +782,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) chain_tc_kernel(const __grid_c
                 p.top2[row] = make_uint2(i1, i2);
             }
         };
-        CHAIN_FOR_EACH_UNIT({
+        CHAIN_FOR_EACH_UNIT_SEGMENT({
             if (rt != cur_rt) {
                 if (cur_rt != ~size_t{0}) {
                     close_chunk();
@@ -836,149 +802,121 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) chain_tc_kernel(const __grid_c
                 cbi = 0;
                 t1 = t2 = FLT_MAX;
                 i1 = i2 = 0xFFFFFFFFu;
-                for (uint32_t q = 0; q < p.n_seg; ++q) nx_row[q] = row_valid ? __ldg(p.chain_norms_x + row * p.n_seg + q) : 0.f;
             } else if (chunk != cur_chunk) {
                 close_chunk();
                 cur_chunk = chunk;
             }
-            const size_t col0 = c0 + static_cast<size_t>(tile) * CBN;
-            const uint32_t cols_valid = static_cast<uint32_t>(min(static_cast<size_t>(CBN), p.k - col0));
+            const size_t col0 = c0 + static_cast<size_t>(unit) * BN;
+            const uint32_t cols_valid = static_cast<uint32_t>(min(static_cast<size_t>(BN), p.k - col0));
             const float thr = best * ctrl->seg_ratio[seg];
-            const float nxv = nx_row[seg];
-            const bool last = (seg + 1 == p.n_seg);
+            const float nxv = row_valid ? __ldg(p.chain_norms_x + row * p.n_seg + seg) : 0.f;
+            const bool first = seg == 0, last = (seg + 1 == p.n_seg);
+            // this warp's copy of the unit's centroid norms at this checkpoint
             {
-                // this warp's copy of the tile's centroid norms at this checkpoint
-                float cur[CBN / 32];
-                if (ny_next_valid) {
+                const float* __restrict__ src = p.chain_norms_y + static_cast<size_t>(seg) * p.k + col0;
+                float cur[BN / 32];
 #pragma unroll
-                    for (uint32_t q = 0; q < CBN / 32; ++q) cur[q] = ny_next[q];
-                } else {
-                    fetch_ny(chunk, tile, seg, cur);
-                }
+                for (uint32_t q = 0; q < BN / 32; ++q) cur[q] = (q * 32 + lane < cols_valid) ? __ldg(src + q * 32 + lane) : 0.f;
                 __syncwarp();
 #pragma unroll
-                for (uint32_t q = 0; q < CBN / 32; ++q) ny[q * 32 + lane] = cur[q];
+                for (uint32_t q = 0; q < BN / 32; ++q) ny[q * 32 + lane] = cur[q];
                 __syncwarp();
-                // next unit: next segment of this tile, else the first segment of the next tile / chunk; a new
-                // row tile starts with a plain fetch
-                uint32_t nseg = seg + 1, ntile = tile, nchunk = chunk;
-                ny_next_valid = true;
-                if (nseg == p.n_seg) {
-                    nseg = 0;
-                    if (++ntile == n_tiles) {
-                        ntile = 0;
-                        if (++nchunk == n_chunks) ny_next_valid = false;
-                    }
-                }
-                if (ny_next_valid) fetch_ny(nchunk, ntile, nseg, ny_next);
             }
-            const long long tq0 = clock64();
-            if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->acc_ready, unit & 1u, p.error, 15))) {
+            if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->acc_ready[a], uses[a] & 1u, p.error, 15))) {
                 ok = false;
                 break;
             }
-            const long long tq1 = clock64();
+            ++uses[a];
             tc_fence_after();
-            uint32_t r[CBN];
-            tmem_ld128(tmem_base + (lane_base << 16), r);
-            tc_fence_before();
-            mbar_arrive(&ctrl->acc_loaded);
-            const long long tq2 = clock64();
-            dbg_wait += tq1 - tq0;
-            dbg_ld += tq2 - tq1;
-            dbg_other += tq0 - dbg_prev;
-            dbg_prev = tq2;
-            ++unit;
-            // Branch-free pass over the 128 columns: bit j of pass[ch] = (partial distance < threshold).
-            // (A per-column branch would be taken by some lane almost always and its unrolled body does not
-            // fit the instruction cache; this form is ~5 instructions per column.)
-            uint32_t pass[CBN / 32];
-            float pdv[CBN];
+            const uint32_t taddr = tmem_base + (lane_base << 16) + a * BN;
+            uint32_t alive[BN / 32];
 #pragma unroll
-            for (uint32_t ch = 0; ch < CBN / 32; ++ch) {
+            for (int q = 0; q < BN / 32; ++q) alive[q] = a ? alive1[q] : alive0[q];
+#pragma unroll
+            for (uint32_t ch = 0; ch < BN / 32; ++ch) {
+                uint32_t r[32];
+                tmem_ld32(taddr + ch * 32, r);
+                if (ch == BN / 32 - 1) {
+                    // everything of this checkpoint is in registers: the accumulator may grow again
+                    tc_fence_before();
+                    mbar_arrive(&ctrl->acc_loaded[a]);
+                }
+                // bit j of w = (partial distance of column ch * 32 + j < threshold), branch-free
                 uint32_t w = 0;
 #pragma unroll
                 for (uint32_t j = 0; j < 32; j += 4) {
-                    const uint32_t cl = ch * 32 + j;
-                    const float4 nyv = *reinterpret_cast<const float4*>(ny + cl);
-                    const float p0 = fmaf(-2.0f, __uint_as_float(r[cl + 0]), nxv) + nyv.x;
-                    const float p1 = fmaf(-2.0f, __uint_as_float(r[cl + 1]), nxv) + nyv.y;
-                    const float p2 = fmaf(-2.0f, __uint_as_float(r[cl + 2]), nxv) + nyv.z;
-                    const float p3 = fmaf(-2.0f, __uint_as_float(r[cl + 3]), nxv) + nyv.w;
+                    const float4 nyv = *reinterpret_cast<const float4*>(ny + ch * 32 + j);
+                    const float p0 = fmaf(-2.0f, __uint_as_float(r[j + 0]), nxv) + nyv.x;
+                    const float p1 = fmaf(-2.0f, __uint_as_float(r[j + 1]), nxv) + nyv.y;
+                    const float p2 = fmaf(-2.0f, __uint_as_float(r[j + 2]), nxv) + nyv.z;
+                    const float p3 = fmaf(-2.0f, __uint_as_float(r[j + 3]), nxv) + nyv.w;
                     w |= (p0 < thr ? (1u << j) : 0u) | (p1 < thr ? (2u << j) : 0u) | (p2 < thr ? (4u << j) : 0u) | (p3 < thr ? (8u << j) : 0u);
-                    if (last) {
-                        pdv[cl + 0] = p0;
-                        pdv[cl + 1] = p1;
-                        pdv[cl + 2] = p2;
-                        pdv[cl + 3] = p3;
-                    }
+                    r[j + 0] = __float_as_uint(p0);
+                    r[j + 1] = __float_as_uint(p1);
+                    r[j + 2] = __float_as_uint(p2);
+                    r[j + 3] = __float_as_uint(p3);
                 }
-                pass[ch] = w;
-            }
-            if (seg == 0) {
-#pragma unroll
-                for (uint32_t ch = 0; ch < CBN / 32; ++ch) {
+                if (first) {
                     const uint32_t lo = ch * 32;
                     const uint32_t valid = (cols_valid >= lo + 32) ? 0xFFFFFFFFu : (cols_valid > lo ? ((1u << (cols_valid - lo)) - 1u) : 0u);
-                    alive[ch] = pass[ch] & valid;
-                    cnt += __popc(alive[ch]);
+                    const uint32_t al = w & valid;
+                    alive[ch] = al;
+                    cnt += __popc(al);
+                    if (static_cast<size_t>(prev) >= col0 + lo && static_cast<size_t>(prev) < col0 + lo + 32) {
+                        if ((al >> (static_cast<uint32_t>(prev - col0) & 31u)) & 1u) prev_first = true;
+                    }
                 }
-                if (static_cast<size_t>(prev) >= col0 && static_cast<size_t>(prev) < col0 + cols_valid) {
-                    const uint32_t pl = static_cast<uint32_t>(prev - col0);
-                    if ((alive[pl >> 5] >> (pl & 31)) & 1u) prev_first = true;
-                }
-            } else if (!last) {
+                if (!first && !last) alive[ch] &= w;
+                if (last) {
+                    // Last checkpoint: the pairs still alive compete.  thr == best here (ratio[d] == 1).  With a
+                    // single segment (first and last at once) alive[] has just been set above.
+                    uint32_t m = alive[ch];
+                    if (m) {
+                        float pdv[32];
 #pragma unroll
-                for (uint32_t ch = 0; ch < CBN / 32; ++ch) alive[ch] &= pass[ch];
-            } else {
-                // Last checkpoint: the pairs still alive compete.  thr == best here (ratio[d] == 1).
-#pragma unroll 1
-                for (uint32_t ch = 0; ch < CBN / 32; ++ch) {
-                    uint32_t w = alive[ch];
-                    while (w) {
-                        const uint32_t j = __ffs(w) - 1;
-                        w &= w - 1;
-                        const uint32_t cl = ch * 32 + j;
-                        const float pd = pdv[cl];
-                        const uint32_t gc = static_cast<uint32_t>(col0 + cl);
-                        if (pd < t2) {
-                            // runner-ups by the chain's own (slightly truncated) distances; the fp32
-                            // refinement afterwards decides among them and the chain's winner
-                            if (pd < t1) {
-                                t2 = t1;
-                                i2 = i1;
-                                t1 = pd;
-                                i1 = gc;
-                            } else {
-                                t2 = pd;
-                                i2 = gc;
+                        for (int j = 0; j < 32; ++j) pdv[j] = __uint_as_float(r[j]);
+                        while (m) {
+                            const uint32_t j = __ffs(m) - 1;
+                            m &= m - 1;
+                            const float pd = pdv[j];
+                            const uint32_t gc = static_cast<uint32_t>(col0 + ch * 32 + j);
+                            if (pd < t2) {
+                                // runner-ups by the chain's own (slightly truncated) distances; the fp32
+                                // refinement afterwards decides among them and the chain's winner
+                                if (pd < t1) {
+                                    t2 = t1;
+                                    i2 = i1;
+                                    t1 = pd;
+                                    i1 = gc;
+                                } else {
+                                    t2 = pd;
+                                    i2 = gc;
+                                }
+                            }
+                            if (pd < thr && pd < cb) {
+                                cb = pd;
+                                cbi = gc;
                             }
                         }
-                        if (pd < thr && pd < cb) {
-                            cb = pd;
-                            cbi = gc;
-                        }
                     }
-                    alive[ch] &= pass[ch];
                 }
+            }
+#pragma unroll
+            for (int q = 0; q < BN / 32; ++q) {
+                if (a) alive1[q] = alive[q];
+                else alive0[q] = alive[q];
             }
         })
         if (ok && cur_rt != ~size_t{0}) {
             close_chunk();
             close_row();
         }
-        if (p.dbg && blockIdx.x == 0 && threadIdx.x == 192) {
-            p.dbg[0] = dbg_wait;
-            p.dbg[1] = dbg_ld;
-            p.dbg[2] = dbg_other;
-            p.dbg[3] = unit;
-        }
     }
-#undef CHAIN_FOR_EACH_UNIT
+#undef CHAIN_FOR_EACH_UNIT_SEGMENT
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, 128);
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 // After the chain: the exact squared distance (direct differences, fp32) of a point to the chain's
@@ -1284,15 +1222,17 @@ void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, floa
 
 void launch_chain(const float* x, const float* y, size_t n, size_t k, size_t d, uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d, const float* chain_norms_x,
                   const float* chain_norms_y, const float* ratios, const float* best_in, uint32_t* knn, float* dist, uint32_t* not_pruned, uint2* top2_scratch,
-                  cudaStream_t stream) {
+                  float* y_split, cudaStream_t stream) {
     if (n == 0 || k == 0) return;
     int device = 0;
     SKM_CUDA(cudaGetDevice(&device));
+    presplit(y, k, d, y_split, stream);
     ChainMaps maps;
     const size_t extents[3] = {partial_d, vertical_d, d};
     for (int i = 0; i < 3; ++i) {
         maps.x[i] = make_tmap(x, extents[i], n, d, BM);
-        maps.y[i] = make_tmap(y, extents[i], k, d, CBN);
+        maps.yhi[i] = make_tmap(y_split, extents[i], k, d, BN);
+        maps.ylo[i] = make_tmap(y_split + k * d, extents[i], k, d, BN);
     }
     ChainParams p{};
     p.n = n;
@@ -1302,6 +1242,7 @@ void launch_chain(const float* x, const float* y, size_t n, size_t k, size_t d, 
     p.vertical_d = vertical_d;
     p.horizontal_d = horizontal_d;
     p.n_seg = 1u + horizontal_d / 64u + (partial_d < vertical_d ? 1u : 0u);
+    if (p.n_seg > CHAIN_MAX_SEGMENTS) throw std::invalid_argument("dimensionality too large for the tensor-core chain");
     p.chain_norms_x = chain_norms_x;
     p.chain_norms_y = chain_norms_y;
     p.ratios = ratios;
@@ -1311,14 +1252,6 @@ void launch_chain(const float* x, const float* y, size_t n, size_t k, size_t d, 
     p.not_pruned = not_pruned;
     p.top2 = top2_scratch;
     p.error = error_flag(device);
-    p.dbg = nullptr;
-    static long long* dbg_dev = nullptr;
-    const bool want_dbg = std::getenv("SKM_CHAIN_DEBUG") != nullptr;
-    if (want_dbg) {
-        if (!dbg_dev) SKM_CUDA(cudaMalloc(&dbg_dev, 16 * sizeof(long long)));
-        SKM_CUDA(cudaMemsetAsync(dbg_dev, 0, 16 * sizeof(long long), stream));
-        p.dbg = dbg_dev;
-    }
     SKM_CUDA(cudaFuncSetAttribute(chain_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(C_SMEM_BYTES)));
     const size_t row_tiles = (n + BM - 1) / BM;
     const int grid = static_cast<int>(std::min<size_t>(row_tiles, static_cast<size_t>(sm_count(device))));
@@ -1328,15 +1261,6 @@ void launch_chain(const float* x, const float* y, size_t n, size_t k, size_t d, 
     refine_chain_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, d, top2_scratch, knn, dist);
     note_kernel_launch();
     SKM_CUDA(cudaGetLastError());
-    if (want_dbg) {
-        long long h[16];
-        SKM_CUDA(cudaMemcpyAsync(h, dbg_dev, sizeof(h), cudaMemcpyDeviceToHost, stream));
-        SKM_CUDA(cudaStreamSynchronize(stream));
-        std::fprintf(stderr,
-                     "[chain dbg] epi: wait_ready %lld ld %lld other %lld units %lld | mma: wait_loaded %lld wait_conv %lld | split: wait_full %lld total %lld kblocks %lld | "
-                     "prod: wait_empty %lld\n",
-                     h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7], h[8], h[9]);
-    }
 }
 
 // Reads (and clears) the error code left by the last kernels on this device.  Synchronises `stream`.

@@ -46,7 +46,7 @@ void launch_first_test(const float* x, const float* y, size_t n, size_t k, size_
 // fp32 among the chain's winner and its two runner-ups (top2_scratch: n entries).
 void launch_chain(const float* x, const float* y, size_t n, size_t k, size_t d, uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d, const float* chain_norms_x,
                   const float* chain_norms_y, const float* ratios, const float* best_in, uint32_t* knn, float* dist, uint32_t* not_pruned, uint2* top2_scratch,
-                  cudaStream_t stream);
+                  float* y_split, cudaStream_t stream);   // y_split: 2 * k * d floats of scratch for the tf32 parts of the centroids
 
 // Error code (0 = none) recorded by a kernel whose bounded wait expired; clears it.  Synchronises.
 int fetch_error(cudaStream_t stream);
