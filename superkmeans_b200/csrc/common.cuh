@@ -120,8 +120,8 @@ struct WalkParams {
     const float* y_pdx;
     const float* y_aux;
     const float* ratios;
-    const uint2* lists;          // n_tiles * 4 groups of cap_group entries
-    const uint32_t* list_offs;   // n_tiles * 4 * (n_chunks + 1)
+    const uint2* lists;          // n_tiles * 8 lists of cap_group entries (see tc::launch_first_test)
+    const uint32_t* list_offs;   // n_tiles * 8 * (n_chunks + 1)
     uint32_t cap_group;
     size_t n, k, d;
     uint32_t partial_d, vertical_d, horizontal_d;

@@ -395,7 +395,8 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
     ws.n_hard_dev = b.n_hard_dev.ensure(1);
     ws.ratio_first = ratio_first;
     ws.alive_total = b.alive_total.ensure(1);
-    if (const char* e = std::getenv("SKM_HARD_MULT")) ws.flag_mult = static_cast<uint32_t>(std::atoi(e));
+    // with the tensor-core chain available, points from 6 of 128 sampled survivors up are cheaper there
+    if (tc::eligible(p.x, p.d, p.y, p.d) && (g_prune_split_mode == 0)) ws.flag_mult = 22;
     launch_pruned_prepare(p, ws, stream);
     const int n_sample = static_cast<int>(std::min<size_t>(p.k, 128));
     const bool tc_ok = tc::eligible(p.x, p.d, p.y, p.d);
@@ -414,7 +415,7 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
         const double survival = static_cast<double>(host[0]) / (static_cast<double>(p.n) * n_sample);
         // The chain costs a full product whatever survives; lists cost a partial product plus one gathered
         // block per surviving pair and step, and their capacity is an eighth of all pairs.
-        use_chain = tc_ok && (survival > 0.08 || n_hard * 4 > p.n);
+        use_chain = tc_ok && (survival > 0.08 || n_hard * 2 > p.n);
         use_tc_lists = tc_ok && !use_chain;
     } else if (g_prune_split_mode == 3) {
         if (!tc_ok) throw std::invalid_argument("the tensor-core chain needs 16-byte aligned rows (d % 4 == 0)");
@@ -451,14 +452,15 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
         SKM_CUDA(cudaMemsetAsync(pair_steps, 0, sizeof(unsigned long long), stream));
         if (n_hard < p.n) {
             const size_t n_chunks = (p.k + kChunk - 1) / kChunk;
-            // per group of 32 points: room for an eighth of its pairs (mode 5: a thirty-second, so that lists overflow)
-            const uint32_t cap_group = static_cast<uint32_t>(std::max<size_t>(256, g_prune_split_mode == 5 ? p.k : p.k * 4));
-            const size_t tile_bytes = 4 * static_cast<size_t>(cap_group) * sizeof(uint2);
+            // eight lists per tile of 128 points, each with room for an eighth of its pairs (32 points x half the
+            // centroids); mode 5: a thirty-second, so that lists overflow
+            const uint32_t cap_group = static_cast<uint32_t>(std::max<size_t>(128, g_prune_split_mode == 5 ? p.k / 2 : p.k * 2));
+            const size_t tile_bytes = 8 * static_cast<size_t>(cap_group) * sizeof(uint2);
             const size_t n_tiles = (p.n + kTileM - 1) / kTileM;
             const size_t budget = static_cast<size_t>(6) << 30;
             const size_t per_batch = std::min(n_tiles, std::max<size_t>(148, budget / tile_bytes));
-            uint2* lists = b.tc_lists.ensure(per_batch * 4 * cap_group);
-            uint32_t* offs = b.tc_list_offs.ensure(per_batch * 4 * (n_chunks + 1));
+            uint2* lists = b.tc_lists.ensure(per_batch * 8 * cap_group);
+            uint32_t* offs = b.tc_list_offs.ensure(per_batch * 8 * (n_chunks + 1));
             float* y_split = b.y_split.ensure(2 * p.k * p.d);
             tc::launch_presplit(p.y, p.k, p.d, y_split, stream);
             for (size_t t0 = 0; t0 < n_tiles; t0 += per_batch) {

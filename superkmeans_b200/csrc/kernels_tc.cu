@@ -36,7 +36,7 @@ constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 16;
 constexpr int STAGES = 4;
-constexpr int NUM_THREADS = 320;
+constexpr int NUM_THREADS = 448;   // warps 10-13 work only in the first-test epilogue and in no other mode
 constexpr uint32_t A_TILE_BYTES = BM * BK * 4;   // 8192
 constexpr uint32_t B_TILE_BYTES = BN * BK * 4;   // 16384
 constexpr uint32_t STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;  // 49152
@@ -44,7 +44,7 @@ constexpr uint32_t OFF_A_HI = 0, OFF_A_LO = A_TILE_BYTES, OFF_B_HI = 2 * A_TILE_
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t SMEM_CTRL_BYTES = 9216;
 constexpr uint32_t STAGE_ENTRIES = 256;   // per epilogue warp, first-test epilogue
-constexpr uint32_t SMEM_STAGE_BYTES = 4 * STAGE_ENTRIES * 8;
+constexpr uint32_t SMEM_STAGE_BYTES = 8 * STAGE_ENTRIES * 8;
 constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + SMEM_STAGE_BYTES + 1024;  // + alignment slack
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
 
@@ -155,6 +155,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// The same load without the wait, and the wait as a separate step that names the destination registers, so that
+// a second load can be in flight while the values of the first are being used.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])::"memory");
+}
+
 __device__ __forceinline__ void tmem_ld128(uint32_t taddr, uint32_t (&r)[128]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x128.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63, %64, %65, %66, %67, %68, %69, %70, %71, %72, %73, %74, %75, %76, %77, %78, %79, %80, %81, %82, %83, %84, %85, %86, %87, %88, %89, %90, %91, %92, %93, %94, %95, %96, %97, %98, %99, %100, %101, %102, %103, %104, %105, %106, %107, %108, %109, %110, %111, %112, %113, %114, %115, %116, %117, %118, %119, %120, %121, %122, %123, %124, %125, %126, %127}, [%128];"
@@ -196,9 +209,11 @@ struct Params {
     const float* best_in;  // n: exact distance to the previous centroid
     const uint32_t* skip;  // n or null: 1 = row handled elsewhere
     float ratio_first;     // ratios[kdim]
-    uint2* lists;          // per 32-row group: cap_group entries {column << 5 | row in group, partial distance}
-    uint32_t* list_offs;   // per group: (n_chunks + 1) entry counts at the start of every 1024-centroid chunk
-    uint32_t cap_group;
+    // eight lists per row tile: list (h * 4 + q) holds the pairs of rows 32q..32q+31 with the centroids of columns
+    // 128h..128h+127 of every 256-column tile; entries {centroid << 5 | row in the 32-row group, partial distance}
+    uint2* lists;
+    uint32_t* list_offs;   // per list: (n_chunks + 1) entry counts at the start of every 1024-centroid chunk
+    uint32_t cap_group;    // capacity of one list
     // Y arrives already split: tmap_y covers the hi parts, tmap_ylo the lo parts, and the splitter warps
     // only treat X
     bool y_presplit;
@@ -225,7 +240,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&ctrl->tmem_full[b], 1);
-            mbar_init(&ctrl->tmem_empty[b], 128);
+            mbar_init(&ctrl->tmem_empty[b], MODE == MODE_PRUNE ? 256 : 128);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
@@ -340,8 +355,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                 }
             }
         }
-    } else {
+    } else if (warp < 10 || MODE == MODE_PRUNE) {
         // ---------------------------------------------------------------- epilogue
+        // First-test mode: eight warps, two per quarter of the tile's rows; warps 6-9 take columns 0-127 of
+        // every 256-column tile, warps 10-13 columns 128-255, each with a candidate list of its own.
+        const uint32_t half = (MODE == MODE_PRUNE) ? static_cast<uint32_t>(warp - 6) >> 2 : 0u;
         const uint32_t lane_base = 32u * (warp & 3);    // tensor-memory lanes this warp may read
         const uint32_t row_in_tile = lane_base + lane;
         uint32_t t = 0;
@@ -361,7 +379,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
             uint2* my_list = nullptr;
             uint32_t* my_offs = nullptr;
             if (MODE == MODE_PRUNE) {
-                const size_t group = (rt - rt_begin) * 4 + (warp & 3);
+                const size_t group = (rt - rt_begin) * 8 + half * 4 + (warp & 3);
                 my_list = p.lists + group * p.cap_group;
                 my_offs = p.list_offs + group * ((p.k + 1023) / 1024 + 1);
                 if (row_valid && !(p.skip && p.skip[row])) thr = p.best_in[row] * p.ratio_first;
@@ -371,9 +389,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                 const size_t col0 = static_cast<size_t>(nt) * BN;
                 float* ny = ctrl->ny[warp & 3][b];
                 if (MODE == MODE_PRUNE && (nt & 3u) == 0 && lane == 0) my_offs[nt >> 2] = filled;
-                if (MODE == MODE_ARGMIN || MODE == MODE_PRUNE) {
+                if (MODE == MODE_ARGMIN) {
                     // each warp keeps its own copy, so no cross-warp barrier is needed
                     for (int j = lane; j < BN; j += 32) ny[j] = (col0 + j < p.k) ? __ldg(p.norms_y + col0 + j) : 0.f;
+                    __syncwarp();
+                }
+                if (MODE == MODE_PRUNE) {
+                    // the two warps of a row quarter fill (and read) disjoint halves of the shared copy
+                    for (int j = half * (BN / 2) + lane; j < static_cast<int>((half + 1) * (BN / 2)); j += 32) ny[j] = (col0 + j < p.k) ? __ldg(p.norms_y + col0 + j) : 0.f;
                     __syncwarp();
                 }
                 // warp-uniform outcome: the tensor-memory loads below must be executed by the whole warp
@@ -383,8 +406,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                 }
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + (lane_base << 16) + b * BN;
+                const int ch_begin = (MODE == MODE_PRUNE) ? static_cast<int>(half) * (BN / 64) : 0;
+                const int ch_end = (MODE == MODE_PRUNE) ? ch_begin + BN / 64 : BN / 32;
 #pragma unroll 1
-                for (int ch = 0; ch < BN / 32; ++ch) {
+                for (int ch = ch_begin; ch < ch_end; ++ch) {
                     uint32_t r[32];
                     tmem_ld32(taddr + ch * 32, r);
                     if (MODE == MODE_ARGMIN) {
@@ -429,7 +454,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                             if (total <= STAGE_ENTRIES) {
                                 // survivors are packed in shared memory first (predicated stores, no divergence) and
                                 // leave for global memory as contiguous runs
-                                uint2* stg = reinterpret_cast<uint2*>(smem + STAGES * STAGE_BYTES + SMEM_CTRL_BYTES) + (warp & 3) * STAGE_ENTRIES;
+                                uint2* stg = reinterpret_cast<uint2*>(smem + STAGES * STAGE_BYTES + SMEM_CTRL_BYTES) + (warp - 6) * STAGE_ENTRIES;
                                 uint32_t pos = incl - cnt;
 #pragma unroll
                                 for (int j = 0; j < 32; ++j) {
@@ -444,7 +469,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                             } else {
                                 // dense case (more than a quarter of the 32 x 32 block passes): eight columns at a time,
                                 // which always fit in the staging area
-                                uint2* stg = reinterpret_cast<uint2*>(smem + STAGES * STAGE_BYTES + SMEM_CTRL_BYTES) + (warp & 3) * STAGE_ENTRIES;
+                                uint2* stg = reinterpret_cast<uint2*>(smem + STAGES * STAGE_BYTES + SMEM_CTRL_BYTES) + (warp - 6) * STAGE_ENTRIES;
                                 uint32_t done = 0;
 #pragma unroll
                                 for (int sb = 0; sb < 4; ++sb) {
@@ -587,6 +612,7 @@ struct ChainCtrl {
 static_assert(sizeof(ChainCtrl) <= SMEM_CTRL_BYTES, "control block too large");
 constexpr uint32_t C_SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + 1024;
 constexpr uint32_t CHAIN_MAX_SEGMENTS = 64;
+constexpr int CHAIN_THREADS = 320;   // producer, MMA issuer, four splitter warps, four row warps
 
 // Order of work shared by all roles: row tile, chunk of 1024 centroids, pair of 256-centroid units, segment,
 // unit of the pair.  `a` (0 / 1) is the unit's accumulator.
@@ -609,7 +635,7 @@ constexpr uint32_t CHAIN_MAX_SEGMENTS = 64;
         }                                                                                                 \
     }
 
-__global__ void __launch_bounds__(NUM_THREADS, 1) chain_tc_kernel(const __grid_constant__ ChainMaps maps, const ChainParams p) {
+__global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid_constant__ ChainMaps maps, const ChainParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -832,15 +858,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) chain_tc_kernel(const __grid_c
             uint32_t alive[BN / 32];
 #pragma unroll
             for (int q = 0; q < BN / 32; ++q) alive[q] = a ? alive1[q] : alive0[q];
-#pragma unroll
-            for (uint32_t ch = 0; ch < BN / 32; ++ch) {
-                uint32_t r[32];
-                tmem_ld32(taddr + ch * 32, r);
-                if (ch == BN / 32 - 1) {
-                    // everything of this checkpoint is in registers: the accumulator may grow again
-                    tc_fence_before();
-                    mbar_arrive(&ctrl->acc_loaded[a]);
-                }
+            // One 32-column slice is tested while the next one is on its way from tensor memory.
+            auto test_slice = [&](const uint32_t ch, uint32_t (&r)[32]) {
                 // bit j of w = (partial distance of column ch * 32 + j < threshold), branch-free
                 uint32_t w = 0;
 #pragma unroll
@@ -900,6 +919,24 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) chain_tc_kernel(const __grid_c
                         }
                     }
                 }
+            };
+            uint32_t ra[32], rb[32];
+            tmem_ld32_issue(taddr, ra);
+            tmem_ld_wait(ra);
+#pragma unroll
+            for (uint32_t ch = 0; ch < BN / 32; ch += 2) {
+                tmem_ld32_issue(taddr + (ch + 1) * 32, rb);
+                test_slice(ch, ra);
+                tmem_ld_wait(rb);
+                if (ch + 2 < BN / 32) {
+                    tmem_ld32_issue(taddr + (ch + 2) * 32, ra);
+                } else {
+                    // everything of this checkpoint is in registers: the accumulator may grow again
+                    tc_fence_before();
+                    mbar_arrive(&ctrl->acc_loaded[a]);
+                }
+                test_slice(ch + 1, rb);
+                if (ch + 2 < BN / 32) tmem_ld_wait(ra);
             }
 #pragma unroll
             for (int q = 0; q < BN / 32; ++q) {
@@ -1255,7 +1292,7 @@ void launch_chain(const float* x, const float* y, size_t n, size_t k, size_t d, 
     SKM_CUDA(cudaFuncSetAttribute(chain_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(C_SMEM_BYTES)));
     const size_t row_tiles = (n + BM - 1) / BM;
     const int grid = static_cast<int>(std::min<size_t>(row_tiles, static_cast<size_t>(sm_count(device))));
-    chain_tc_kernel<<<grid, NUM_THREADS, C_SMEM_BYTES, stream>>>(maps, p);
+    chain_tc_kernel<<<grid, CHAIN_THREADS, C_SMEM_BYTES, stream>>>(maps, p);
     note_kernel_launch();
     SKM_CUDA(cudaGetLastError());
     refine_chain_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, d, top2_scratch, knn, dist);

@@ -32,9 +32,10 @@ void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, floa
 
 // First ADSampling test on the tensor cores for the row tiles [tile0, tile0 + n_tiles) of 128 points: partial
 // distances over the first partial_d dimensions of every (point, centroid) pair, tested against
-// best_in * ratio_first; pairs that pass go to one list per group of 32 rows ({centroid << 5 | row in group,
-// partial distance}, at most cap_group entries, in centroid order), and list_offs receives, per group, the
-// number of entries before every 1024-centroid chunk and the total (which exceeds cap_group on overflow).
+// best_in * ratio_first.  Pairs that pass go to one of eight lists per row tile (list h * 4 + q: rows 32q..32q+31,
+// columns 128h..128h+127 of every 256-centroid tile) as {centroid << 5 | row in the 32-row group, partial
+// distance}, at most cap_group entries per list, in centroid-tile order; list_offs receives, per list, the number
+// of entries before every 1024-centroid chunk and the total (which exceeds cap_group on overflow).
 void launch_first_test(const float* x, const float* y, size_t n, size_t k, size_t d, uint32_t partial_d, const float* norms_x, const float* norms_y, const float* best_in,
                        const uint32_t* skip, float ratio_first, size_t tile0, size_t n_tiles, uint2* lists, uint32_t* list_offs, uint32_t cap_group, cudaStream_t stream,
                        const float* y_split = nullptr);   // y already split by launch_presplit, optional

@@ -51,6 +51,7 @@ struct WalkShared {
     uint32_t cursor[kTileM];
     uint32_t warp_tot[4];
     uint32_t gcount[kWalkGroups];
+    uint32_t gbeg[8], glen[8];     // this chunk's slice of each of the tile's eight lists
     unsigned long long key[kTileM];
     uint32_t m;
 };
@@ -133,7 +134,10 @@ __global__ void __launch_bounds__(kWalkThreads, 3) walk_lists_kernel(const WalkP
         const size_t row0 = (w.tile0 + tile) * kTileM;
         if (tid < kTileM) {
             const size_t row = row0 + tid;
-            const uint32_t overflow = w.list_offs[(tile * 4 + (tid >> 5)) * (n_chunks + 1) + n_chunks] > w.cap_group ? 1u : 0u;
+            const uint32_t overflow = (w.list_offs[(tile * 8 + (tid >> 5)) * (n_chunks + 1) + n_chunks] > w.cap_group ||
+                                       w.list_offs[(tile * 8 + 4 + (tid >> 5)) * (n_chunks + 1) + n_chunks] > w.cap_group)
+                                          ? 1u
+                                          : 0u;
             bool active = row < w.n && !(w.skip && w.skip[row]);
             if (active && overflow) {
                 // the group's list did not fit: its points go to the dense kernel
@@ -159,18 +163,19 @@ __global__ void __launch_bounds__(kWalkThreads, 3) walk_lists_kernel(const WalkP
                 sh.key[tid] = ~0ull;
             }
 
-            // The chunk's pairs of the four row groups, taken as one sequence of `total` positions.
-            uint32_t gbeg[4], glen[4];
+            // The chunk's pairs of the tile's eight lists, taken as one sequence of `total` positions.
+            if (tid < 8) {
+                const uint32_t* offs = w.list_offs + (tile * 8 + tid) * (n_chunks + 1);
+                const uint32_t* offs_other = w.list_offs + (tile * 8 + (tid ^ 4)) * (n_chunks + 1);
+                const bool usable = offs[n_chunks] <= w.cap_group && offs_other[n_chunks] <= w.cap_group;
+                sh.gbeg[tid] = offs[chunk];
+                sh.glen[tid] = usable ? offs[chunk + 1] - offs[chunk] : 0u;
+            }
+            __syncthreads();
             uint32_t total = 0;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const uint32_t* offs = w.list_offs + (tile * 4 + q) * (n_chunks + 1);
-                const bool usable = offs[n_chunks] <= w.cap_group;
-                gbeg[q] = offs[chunk];
-                glen[q] = usable ? offs[chunk + 1] - offs[chunk] : 0u;
-                total += glen[q];
-            }
-            const uint2* base_list = w.lists + tile * 4 * static_cast<size_t>(w.cap_group);
+            for (int q = 0; q < 8; ++q) total += sh.glen[q];
+            const uint2* base_list = w.lists + tile * 8 * static_cast<size_t>(w.cap_group);
             const float* __restrict__ blk_chunk = w.y_pdx + chunk * kChunk * w.d + static_cast<size_t>(w.vertical_d) * cs;
 
             uint32_t b0 = 0;
@@ -191,21 +196,12 @@ __global__ void __launch_bounds__(kWalkThreads, 3) walk_lists_kernel(const WalkP
                     mine[u] = make_uint2(0, 0);
                     if (e < b1) {
                         uint32_t q = 0, off = e;
-                        if (off >= glen[0]) {
-                            off -= glen[0];
-                            q = 1;
-                            if (off >= glen[1]) {
-                                off -= glen[1];
-                                q = 2;
-                                if (off >= glen[2]) {
-                                    off -= glen[2];
-                                    q = 3;
-                                }
-                            }
+                        while (q < 7 && off >= sh.glen[q]) {
+                            off -= sh.glen[q];
+                            ++q;
                         }
-                        const uint32_t gb = q == 0 ? gbeg[0] : (q == 1 ? gbeg[1] : (q == 2 ? gbeg[2] : gbeg[3]));
-                        const uint2 raw = __ldg(base_list + static_cast<size_t>(q) * w.cap_group + gb + off);
-                        const uint32_t r = q * 32 + (raw.x & 31u);
+                        const uint2 raw = __ldg(base_list + static_cast<size_t>(q) * w.cap_group + sh.gbeg[q] + off);
+                        const uint32_t r = (q & 3u) * 32 + (raw.x & 31u);
                         const uint32_t col = raw.x >> 5;
                         const float pd = __uint_as_float(raw.y);
                         if (pd < sh.thr[r]) {
