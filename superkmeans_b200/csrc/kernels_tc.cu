@@ -859,7 +859,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
 #pragma unroll
             for (int q = 0; q < BN / 32; ++q) alive[q] = a ? alive1[q] : alive0[q];
             // One 32-column slice is tested while the next one is on its way from tensor memory.
-            auto test_slice = [&](const uint32_t ch, uint32_t (&r)[32]) {
+            auto test_slice = [&](const uint32_t ch, uint32_t (&r)[32], uint32_t& alive_ch) {
                 // bit j of w = (partial distance of column ch * 32 + j < threshold), branch-free
                 uint32_t w = 0;
 #pragma unroll
@@ -879,17 +879,17 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
                     const uint32_t lo = ch * 32;
                     const uint32_t valid = (cols_valid >= lo + 32) ? 0xFFFFFFFFu : (cols_valid > lo ? ((1u << (cols_valid - lo)) - 1u) : 0u);
                     const uint32_t al = w & valid;
-                    alive[ch] = al;
+                    alive_ch = al;
                     cnt += __popc(al);
                     if (static_cast<size_t>(prev) >= col0 + lo && static_cast<size_t>(prev) < col0 + lo + 32) {
                         if ((al >> (static_cast<uint32_t>(prev - col0) & 31u)) & 1u) prev_first = true;
                     }
                 }
-                if (!first && !last) alive[ch] &= w;
+                if (!first && !last) alive_ch &= w;
                 if (last) {
                     // Last checkpoint: the pairs still alive compete.  thr == best here (ratio[d] == 1).  With a
                     // single segment (first and last at once) alive[] has just been set above.
-                    uint32_t m = alive[ch];
+                    uint32_t m = alive_ch;
                     if (m) {
                         float pdv[32];
 #pragma unroll
@@ -923,10 +923,12 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
             uint32_t ra[32], rb[32];
             tmem_ld32_issue(taddr, ra);
             tmem_ld_wait(ra);
-#pragma unroll
+            // Rolled on purpose (two slices per trip): unrolled, the tests of a whole unit do not fit the instruction
+            // cache.  The survivor masks rotate through alive[0] and alive[1] so that they stay in registers.
+#pragma unroll 1
             for (uint32_t ch = 0; ch < BN / 32; ch += 2) {
                 tmem_ld32_issue(taddr + (ch + 1) * 32, rb);
-                test_slice(ch, ra);
+                test_slice(ch, ra, alive[0]);
                 tmem_ld_wait(rb);
                 if (ch + 2 < BN / 32) {
                     tmem_ld32_issue(taddr + (ch + 2) * 32, ra);
@@ -935,8 +937,13 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
                     tc_fence_before();
                     mbar_arrive(&ctrl->acc_loaded[a]);
                 }
-                test_slice(ch + 1, rb);
+                test_slice(ch + 1, rb, alive[1]);
                 if (ch + 2 < BN / 32) tmem_ld_wait(ra);
+                const uint32_t m0 = alive[0], m1 = alive[1];
+#pragma unroll
+                for (int q = 0; q < BN / 32 - 2; ++q) alive[q] = alive[q + 2];
+                alive[BN / 32 - 2] = m0;
+                alive[BN / 32 - 1] = m1;
             }
 #pragma unroll
             for (int q = 0; q < BN / 32; ++q) {
