@@ -117,6 +117,8 @@ void launch_assign_pruned_dense(const PrunedParams& p, PruneSplitWorkspace& ws, 
 // walk_lists_kernel (kernels_walk.cu), for the row tiles [tile0, tile0 + n_tiles) of 128 points.
 struct WalkParams {
     const float* x;
+    const float* y;              // row-major centroids
+    const float* norms_x;        // squared norms of the points over the first partial_d dimensions
     const float* y_pdx;
     const float* y_aux;
     const float* ratios;

@@ -471,6 +471,8 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
                 }
                 WalkParams w{};
                 w.x = p.x;
+                w.y = p.y;
+                w.norms_x = p.norms_x;
                 w.y_pdx = p.y_pdx;
                 w.y_aux = p.y_aux;
                 w.ratios = p.ratios;

@@ -41,6 +41,8 @@ struct WalkShared {
     float best[kTileM];
     float thr[kTileM];
     float prev_pd[kTileM];
+    float margin[kTileM];          // how close to `best` a final distance must be to be recomputed exactly
+    float nx[kTileM];              // squared norm of the point over the first d' dimensions
     uint32_t bestidx[kTileM];
     uint32_t prev[kTileM];
     uint32_t cnt[kTileM];          // survivors of the first test in this chunk
@@ -149,6 +151,7 @@ __global__ void __launch_bounds__(kWalkThreads, 3) walk_lists_kernel(const WalkP
             sh.best[tid] = active ? w.best_in[row] : -FLT_MAX;
             sh.bestidx[tid] = active ? w.knn[row] : 0u;
             sh.prev[tid] = active ? w.knn[row] : 0xFFFFFFFFu;
+            sh.nx[tid] = active ? w.norms_x[row] : 0.f;
             sh.npc[tid] = 0;
         }
         __syncthreads();
@@ -158,6 +161,7 @@ __global__ void __launch_bounds__(kWalkThreads, 3) walk_lists_kernel(const WalkP
             const size_t cs = min(static_cast<size_t>(kChunk), w.k - c0);
             if (tid < kTileM) {
                 sh.thr[tid] = sh.best[tid] * ratio_first;
+                sh.margin[tid] = 5e-5f * sh.best[tid] + 2e-5f * sh.nx[tid];
                 sh.cnt[tid] = 0;
                 sh.prev_flag[tid] = 0;
                 sh.key[tid] = ~0ull;
@@ -333,8 +337,25 @@ __global__ void __launch_bounds__(kWalkThreads, 3) walk_lists_kernel(const WalkP
                             }
                             pd += group_sum(s, gmask);
                         }
-                        if (gl == 0 && pd < sh.best[r]) {
-                            atomicMin(&sh.key[r], (static_cast<unsigned long long>(float_to_ordered(pd)) << 32) | static_cast<unsigned long long>(c));
+                        // The first d' dimensions of pd come from the tensor cores (three TF32 products, truncating
+                        // accumulator: a few 1e-6 of the norms off).  A pair that would win, or lose, by less than that
+                        // is settled with the distance recomputed from direct differences in fp32.
+                        if (pd < sh.best[r] + sh.margin[r]) {
+                            const float4* q4 = reinterpret_cast<const float4*>(w.x + (row0 + r) * w.d);
+                            const float4* c4 = reinterpret_cast<const float4*>(w.y + c * w.d);
+                            float s0 = 0.f, s1 = 0.f;
+                            for (uint32_t jj = gl; jj < w.d / 4; jj += 8) {
+                                const float4 a = __ldg(q4 + jj), b = __ldg(c4 + jj);
+                                float t;
+                                t = a.x - b.x; s0 = fmaf(t, t, s0);
+                                t = a.y - b.y; s1 = fmaf(t, t, s1);
+                                t = a.z - b.z; s0 = fmaf(t, t, s0);
+                                t = a.w - b.w; s1 = fmaf(t, t, s1);
+                            }
+                            const float exact = group_sum(s0 + s1, gmask);
+                            if (gl == 0 && exact < sh.best[r]) {
+                                atomicMin(&sh.key[r], (static_cast<unsigned long long>(float_to_ordered(exact)) << 32) | static_cast<unsigned long long>(c));
+                            }
                         }
                     }
                 }
