@@ -285,8 +285,9 @@ def main():
     ms, calls = phase_acc["search/dense"]
     cands.append(("chain_tc_kernel", ms, calls, "tensor", 2.0 * counters["dense_rows"] * k * d))
     ms, calls = phase_acc["search/walk"]
-    # every (pair, 64-dimension block) step reads 256 B of the centroid's PDX block and 256 B of the point
-    cands.append(("walk_lists_kernel", ms, calls, "hbm", 512.0 * counters["walk_pair_steps"]))
+    # every (pair, 64-dimension block) step gathers 256 B of the centroid's PDX block (the point's 256 B stay in
+    # registers across the pairs of a point)
+    cands.append(("walk_lists_kernel", ms, calls, "hbm", 256.0 * counters["walk_pair_steps"]))
     if prune_path not in (3, 4):
         ms, calls = phase_acc["search"]
         cands.append(("assign_pruned_kernel", ms, calls, "tensor", sum(2.0 * n_local * k * pd for pd in d_partial)))
@@ -301,8 +302,16 @@ def main():
         achieved = work / (dom_ms_per_train / 1e3) / 1e9 if dom_ms > 0 else 0.0
         roofline = {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs, "traffic": None,
                     "peak_source": f"HBM copy, {pk['_source']}", "avg_launch_ms": dom_ms / max(dom_calls, 1),
-                    "note": "gathered 256-byte blocks, mostly served by L2; bytes = 512 B per (pair, 64-dimension block) step, counted by the kernel"}
+                    "note": "gathered 256-byte centroid blocks, served by L2 rather than HBM (hence a fraction near or above 1); bytes = 256 B per (pair, 64-dimension block) step, counted by the kernel"}
     roofline["kernels_ms_per_train"] = {c[0]: round(c[1] / args.steps, 3) for c in cands}
+    # DRAM bytes per launch: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture at n = 400 000 (same d and
+    # k; profiles/assignment_kernels_n400k_d1024_k10000.md), per row, times the rows one launch covers here.  Traffic of
+    # these kernels grows with the rows (the centroid side stays in L2).  The chain's rows per launch vary: not scaled.
+    dram_per_row = {"gemm_tc_kernel<ARGMIN>": 3.60e9 / 4e5, "gemm_tc_kernel<PRUNE>": 0.377e9 / 4e5, "walk_lists_kernel": 4.92e9 / 4e5}
+    if dom in dram_per_row and dom_calls and (d, k) == (1024, 10000):
+        rows_per_launch = n_local * (1 if dom.endswith("<ARGMIN>") else len(d_partial)) * args.steps / dom_calls
+        roofline["traffic"] = dram_per_row[dom] * rows_per_launch
+        roofline["traffic_note"] = "scaled by rows per launch from an ncu capture at n=400000"
 
     # ---- end to end through the public API with host (pinned) input
     e2e = None
