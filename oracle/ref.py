@@ -210,10 +210,10 @@ class RefKMeans:
             lib().ref_destroy(self._h)
             self._h = None
 
-    def train(self, data: np.ndarray, queries: Optional[np.ndarray] = None) -> np.ndarray:
+    def train(self, data: np.ndarray, queries: Optional[np.ndarray] = None, n_queries: int = 0) -> np.ndarray:
         data = np.ascontiguousarray(data, dtype=np.float32)
         out = np.empty((self.k, self.d), dtype=np.float32)
-        q, nq = None, 0
+        q, nq = None, int(n_queries)
         if queries is not None:
             queries = np.ascontiguousarray(queries, dtype=np.float32)
             q, nq = queries.ctypes.data_as(C.c_void_p), queries.shape[0]

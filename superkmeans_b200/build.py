@@ -8,7 +8,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["kernels.cu", "kernels_pruned_dense.cu", "kernels_tc.cu", "kernels_walk.cu", "engine.cu", "noalloc.cu", "abi.cu"]
+SOURCES = ["kernels.cu", "kernels_pruned_dense.cu", "kernels_tc.cu", "kernels_walk.cu", "kernels_topk.cu", "engine.cu", "noalloc.cu", "abi.cu"]
 HEADERS = ["common.cuh", "device_utils.cuh", "gemm_simt.cuh", "kernels_tc.cuh", "noalloc.h", "engine.h", "host_logic.h", os.path.join("..", "..", "include", "skm_b200.h")]
 OUTPUT = os.path.join(HERE, "libskm_b200.so")
 

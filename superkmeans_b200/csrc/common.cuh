@@ -146,6 +146,17 @@ void launch_gather_listed(const float* x, const float* best, const uint32_t* knn
 void launch_scatter_listed(const uint32_t* idx, size_t n_listed, const uint32_t* knn_in, const float* dist_in, const uint32_t* np_in, uint32_t* knn, float* dist,
                            uint32_t* not_pruned, cudaStream_t stream);
 
+// k nearest rows of y for every row of q by ||q||^2 + ||y||^2 - 2 q.y (BatchComputer::FindKNearestNeighbors,
+// batch_computers.h:191-274): out_idx / out_dist are n_q x k, ascending by (distance, index); dots_scratch needs
+// topk_scratch_floats(n_q) floats, state n_q * k 64-bit words; k <= topk_max_k().
+size_t topk_scratch_floats(size_t n_q);
+size_t topk_max_k();
+void launch_topk_nn(const float* q, const float* y, size_t n_q, size_t n_y, size_t d, const float* norms_q, const float* norms_y, uint32_t k, uint32_t* out_idx,
+                    float* out_dist, float* dots_scratch, unsigned long long* state, cudaStream_t stream);
+// found[q] = |{j < objective_k : assignments[gt[q][j]] is one of promising[q][0 .. n_explore)}| (superkmeans.h:1063-1086)
+void launch_recall_count(const uint32_t* gt, uint32_t objective_k, const uint32_t* promising, uint32_t n_explore, const uint32_t* assignments, size_t n_assignments,
+                         size_t n_q, uint32_t* found, cudaStream_t stream);
+
 int pruned_grid_size(int device);
 size_t pruned_scratch_elems(int grid);
 void launch_assign_pruned(const PrunedParams& p, int grid, cudaStream_t stream);

@@ -659,18 +659,21 @@ void Engine::run_iteration(bool gemm_only, const IterationInput& in, size_t iter
         trace_.push_back(std::move(snap));
     }
 
+    // superkmeans.h:848-851
+    recall_ = (n_queries_ > 0 && &target == &stats_flat_) ? compute_recall(k_cur) : 0.0f;
+
     skm_iter_stats s{};
     s.iteration = iter_idx + 1;
     s.objective = cost_;
     s.shift = shift_;
     s.split = n_split_;
-    s.recall = 0.0f;
+    s.recall = recall_;
     s.is_gemm_only = gemm_only ? 1 : 0;
     s.not_pruned_pct = gemm_only ? -1.0f : avg_not_pruned;
     s.partial_d = gemm_only ? 0u : old_partial_d;
     target.push_back(s);
     if (cfg_.verbose) {
-        std::cout << "Iteration " << iter_idx + 1 << " | Objective: " << cost_ << " | Shift: " << shift_ << " | Split: " << n_split_;
+        std::cout << "Iteration " << iter_idx + 1 << " | Objective: " << cost_ << " | Shift: " << shift_ << " | Split: " << n_split_ << " | Recall: " << recall_;
         if (gemm_only) std::cout << " [GEMM-only]";
         else std::cout << " | Not Pruned %: " << avg_not_pruned * 100.0f << " | d': " << old_partial_d << " -> " << partial_d_;
         std::cout << std::endl;
@@ -695,9 +698,7 @@ void Engine::train(const float* data, size_t n, bool on_device, const float* que
         if (n_queries > 0 && queries == nullptr && !cfg_.sample_queries) {
             throw std::invalid_argument("Queries must be provided if n_queries > 0 and sample_queries is false");
         }
-        if (n_queries > 0) {
-            throw std::runtime_error("recall-driven early termination (queries) is not available in this engine");
-        }
+        if (n_queries > 0 && allreduce_fn_) throw std::runtime_error("training with queries is not available for sharded training");
     }
     if (allreduce_fn_ && cfg_.sampling_fraction != 1.0f) {
         throw std::runtime_error("sharded training requires sampling_fraction == 1.0");
@@ -708,7 +709,7 @@ void Engine::train(const float* data, size_t n, bool on_device, const float* que
     timers_.begin(PH_TRAIN_TOTAL, stream_);
     try {
         if (hierarchical_) train_hierarchical(data, n, on_device, centroids_out);
-        else train_flat(data, n, on_device, centroids_out);
+        else train_flat(data, n, on_device, queries, n_queries, centroids_out);
     } catch (...) {
         timers_.end(stream_);
         throw;
@@ -724,8 +725,9 @@ static void gather_host_rows(const float* data, const size_t* idx, size_t cnt, s
     for (size_t i = 0; i < cnt; ++i) std::memcpy(out + i * d, data + idx[i] * d, sizeof(float) * d);
 }
 
-void Engine::train_flat(const float* data, size_t n, bool on_device, float* centroids_out) {
+void Engine::train_flat(const float* data, size_t n, bool on_device, const float* queries, size_t n_queries, float* centroids_out) {
     stats_flat_.clear();
+    n_queries_ = 0;
     const size_t n_global = allreduce_fn_ ? shard_n_global_ : n;
     const size_t n_samples_global = n_vectors_to_sample(n_global, k_, cfg_.sampling_fraction, cfg_.max_points_per_cluster, false);
     if (n_samples_global < k_) {
@@ -788,8 +790,13 @@ void Engine::train_flat(const float* data, size_t n, bool on_device, float* cent
 
     launch_row_sqnorms(x_rot_.get(), n_samples_, d_, d_, data_norms_.get(), stream_);
 
+    // Ground truth for the recall figure (superkmeans.h:243-274): needs the full norms computed just above.
+    if (n_queries > 0) prepare_recall(queries, n_queries, rotate);
+
     const bool always_gemm_only = d_ < kDimensionThresholdForPruning || cfg_.use_blas_only || k_ <= kNClustersThresholdForPruning;
     bool partial_norms_computed = false;
+    float best_recall = 0.0f;
+    size_t iters_without_improvement = 0;
     IterationInput in{x_rot_.get(), n_samples_, n_samples_global, k_, data_norms_.get()};
     for (size_t iter = 0; iter < cfg_.iters; ++iter) {
         const bool gemm_only = (iter == 0) || always_gemm_only;
@@ -798,13 +805,71 @@ void Engine::train_flat(const float* data, size_t n, bool on_device, float* cent
             partial_norms_computed = true;
         }
         run_iteration(gemm_only, in, iter, iter == 0, stats_flat_);
-        if (cfg_.early_termination && should_stop_early(shift_, cost_, prev_cost_, cfg_.tol, iter)) break;
+        if (cfg_.early_termination &&
+            should_stop_early(shift_, cost_, prev_cost_, cfg_.tol, iter, n_queries_ > 0, recall_, cfg_.recall_tol, &best_recall, &iters_without_improvement)) {
+            break;
+        }
     }
+    queries_rot_.release();
+    topk_dots_.release();
     trained_ = true;
     output_centroids(centroids_out);
     check_tc_error(stream_);
     x_rot_.release();
     ws_partials_.release();
+}
+
+// Query side of Train (superkmeans.h:243-274): rotated queries (or a sample of the rotated training rows), their
+// norms, and the objective_k nearest training rows of every query.
+void Engine::prepare_recall(const float* queries, size_t n_queries, bool rotate) {
+    centroids_to_explore_ = std::max<size_t>(static_cast<size_t>(static_cast<float>(k_) * cfg_.ann_explore_fraction), 1);
+    if (cfg_.verbose) {
+        std::cout << "Centroids to explore: " << centroids_to_explore_ << " (" << cfg_.ann_explore_fraction * 100.0f << "% of " << k_ << ")" << std::endl;
+    }
+    const size_t objective_k = cfg_.objective_k;
+    if (objective_k == 0 || objective_k > topk_max_k() || centroids_to_explore_ > topk_max_k()) {
+        throw std::runtime_error("objective_k and the number of centroids to explore must lie in [1, " + std::to_string(topk_max_k()) + "]");
+    }
+    float* qr = queries_rot_.ensure(n_queries * d_);
+    if (cfg_.sample_queries) {
+        // SampleAndRotateVectors(data_to_cluster, ..., n_samples, n_queries, false): the first n_queries entries of a
+        // shuffle of the training rows, already rotated
+        if (n_queries >= n_samples_) throw std::runtime_error("sample_queries needs fewer queries than training points");
+        std::cout << "Sampling queries from data..." << std::endl;   // printed unconditionally by the reference (superkmeans.h:263)
+        const std::vector<size_t> perm = sampling_permutation(n_samples_, cfg_.seed);
+        std::vector<uint64_t> idx(perm.begin(), perm.begin() + n_queries);
+        DeviceBuffer<uint64_t> idx_dev;
+        SKM_CUDA(cudaMemcpyAsync(idx_dev.ensure(n_queries), idx.data(), sizeof(uint64_t) * n_queries, cudaMemcpyHostToDevice, stream_));
+        launch_gather_rows(x_rot_.get(), idx_dev.get(), qr, n_queries, d_, stream_);
+        sync();
+    } else if (rotate) {
+        rotate_to_device(queries, false, n_queries, qr);
+    } else {
+        upload_rows(queries, false, n_queries, qr);
+    }
+    launch_row_sqnorms(qr, n_queries, d_, d_, query_norms_.ensure(n_queries), stream_);
+    const size_t kmax = std::max(objective_k, centroids_to_explore_);
+    launch_topk_nn(qr, x_rot_.get(), n_queries, n_samples_, d_, query_norms_.get(), data_norms_.get(), static_cast<uint32_t>(objective_k), gt_idx_.ensure(n_queries * objective_k),
+                   nullptr, topk_dots_.ensure(topk_scratch_floats(n_queries)), topk_state_.ensure(n_queries * kmax), stream_);
+    promising_.ensure(n_queries * centroids_to_explore_);
+    recall_found_.ensure(n_queries);
+    recall_found_host_.ensure(n_queries);
+    n_queries_ = n_queries;
+    sync();
+}
+
+// ComputeRecall (superkmeans.h:1044-1087) on the consolidated centroids of this iteration.
+float Engine::compute_recall(size_t k_cur) {
+    launch_row_sqnorms(c_cur_.get(), k_cur, d_, d_, centroid_norms_.get(), stream_);
+    launch_topk_nn(queries_rot_.get(), c_cur_.get(), n_queries_, k_cur, d_, query_norms_.get(), centroid_norms_.get(), static_cast<uint32_t>(centroids_to_explore_),
+                   promising_.get(), nullptr, topk_dots_.get(), topk_state_.get(), stream_);
+    launch_recall_count(gt_idx_.get(), static_cast<uint32_t>(cfg_.objective_k), promising_.get(), static_cast<uint32_t>(centroids_to_explore_), assignments_.get(), n_samples_,
+                        n_queries_, recall_found_.get(), stream_);
+    SKM_CUDA(cudaMemcpyAsync(recall_found_host_.get(), recall_found_.get(), sizeof(uint32_t) * n_queries_, cudaMemcpyDeviceToHost, stream_));
+    sync();
+    float sum_recall = 0.0f;
+    for (size_t i = 0; i < n_queries_; ++i) sum_recall += static_cast<float>(recall_found_host_.get()[i]) / static_cast<float>(cfg_.objective_k);
+    return sum_recall / static_cast<float>(n_queries_);
 }
 
 // GetOutputCentroids (superkmeans.h:1341-1351)

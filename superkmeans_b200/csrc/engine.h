@@ -201,7 +201,9 @@ class Engine {
     void consolidate(size_t n_samples_global, size_t k_cur);
     void generate_centroids_from_host(const float* data, bool on_device, size_t n_points_global, size_t k_cur, bool rotate);
     void generate_centroids_from_device_rows(const float* dev_rows, size_t n_points, size_t k_cur);
-    void train_flat(const float* data, size_t n, bool on_device, float* centroids_out);
+    void train_flat(const float* data, size_t n, bool on_device, const float* queries, size_t n_queries, float* centroids_out);
+    void prepare_recall(const float* queries, size_t n_queries, bool rotate);
+    float compute_recall(size_t k_cur);
     void train_hierarchical(const float* data, size_t n, bool on_device, float* centroids_out);
     void output_centroids(float* out_host);
     void allreduce(void* buf, size_t count, int dtype);
@@ -257,6 +259,13 @@ class Engine {
     std::vector<float> ratios_host_;
     DeviceBuffer<uint2> top2_;           // candidate pairs of the tensor-core exact assignment
     DeviceBuffer<float> y_split_;        // centroids split into tf32 hi / lo parts for the tensor-core kernels
+    // training with query vectors (recall after every iteration)
+    size_t n_queries_ = 0, centroids_to_explore_ = 0;
+    DeviceBuffer<float> queries_rot_, query_norms_, topk_dots_;
+    DeviceBuffer<uint32_t> gt_idx_, promising_, recall_found_;
+    DeviceBuffer<unsigned long long> topk_state_;
+    PinnedBuffer<uint32_t> recall_found_host_;
+    float recall_ = 0.0f;
     DeviceBuffer<SplitOpDev> split_ops_dev_;
     DeviceBuffer<double> scalars_dev_;   // [0] wcss, [1] not-pruned total (as double), [2] shift
     DeviceBuffer<unsigned long long> np_total_dev_;

@@ -230,12 +230,25 @@ inline TuneResult tune_partial_d(double not_pruned_total, size_t n_samples, size
     return {avg, nd, nd != partial_d};
 }
 
-// SuperKMeans::ShouldStopEarly without the recall branch (superkmeans.h:1294-1314).
-inline bool should_stop_early(float shift, float cost, float prev_cost, float tol, size_t iter_idx) {
+// SuperKMeans::ShouldStopEarly (superkmeans.h:1294-1333).  With tracking_recall, best_recall and
+// iters_without_improvement carry the recall history from call to call.
+constexpr size_t kRecallConvergencePatience = 2;   // RECALL_CONVERGENCE_PATIENCE (common.h:111)
+inline bool should_stop_early(float shift, float cost, float prev_cost, float tol, size_t iter_idx, bool tracking_recall = false, float recall = 0.0f,
+                              float recall_tol = 0.0f, float* best_recall = nullptr, size_t* iters_without_improvement = nullptr) {
     if (shift < tol) return true;
     if (iter_idx > 0) {
         const float cost_delta = cost / prev_cost;
         if (cost_delta > 1 - tol) return true;
+    }
+    if (tracking_recall) {
+        const float improvement = recall - *best_recall;
+        if (improvement > recall_tol) {
+            *best_recall = recall;
+            *iters_without_improvement = 0;
+        } else {
+            ++*iters_without_improvement;
+            if (*iters_without_improvement >= kRecallConvergencePatience) return true;
+        }
     }
     return false;
 }

@@ -89,12 +89,13 @@ class Engine:
         check(lib.skm_set_shard(self._h, n_global, row_offset, self._keepalive, None), self._h)
 
     # -- the three calls of the reference API -----------------------------------------------------
-    def train(self, data, n: Optional[int] = None, on_device: bool = False, queries=None) -> np.ndarray:
+    def train(self, data, n: Optional[int] = None, on_device: bool = False, queries=None, n_queries: int = 0) -> np.ndarray:
+        """queries: host array of query vectors for the recall figure; with config.sample_queries pass n_queries alone."""
         if not on_device:
             data = _f32(data)
             n = data.shape[0]
         out = np.empty((self.k, self.d), dtype=np.float32)
-        nq = 0 if queries is None else int(queries.shape[0])
+        nq = int(n_queries) if queries is None else int(queries.shape[0])
         q = None if queries is None else _ptr(_f32(queries))
         check(lib.skm_train(self._h, _ptr(data), int(n), int(on_device), q, nq, out), self._h)
         self.n_trained = int(n)

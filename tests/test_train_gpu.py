@@ -219,3 +219,32 @@ def test_python_surface():
     with pytest.raises(ValueError):
         skm.SuperKMeans(20, 64).train(x[:, :10])
     assert len(km.iteration_stats) >= 1
+
+
+@pytest.mark.parametrize("sample_queries", [False, True])
+def test_train_with_queries_tracks_recall_like_the_reference(ref, sample_queries):
+    """python/tests/test_superkmeans.py:49-64 (train with queries): recall@objective_k after every iteration and the
+    recall-driven early termination (superkmeans.h:1010-1087, :1315-1331)."""
+    import superkmeans_b200 as skm
+
+    n, d, k, seed = 30000, 128, 400, 21
+    x = datagen.gaussian_mixture(n, d, k, 0.3, seed)
+    q = datagen.gaussian_mixture(300, d, k, 0.3, seed + 1)
+    kw = dict(iters=8, sampling_fraction=1.0, early_termination=1, seed=seed, objective_k=20, ann_explore_fraction=0.02, recall_tol=0.002,
+              sample_queries=int(sample_queries), suppress_warnings=1)
+    rk = ref.RefKMeans(k, d, ref.default_config(False, **kw))
+    e = skm.Engine(k, d, skm.default_config(False, **kw))
+    if sample_queries:
+        rc = rk.train(x, n_queries=300)
+        e.set_rotation(rk.rotation_matrix())
+        c = e.train(x, n_queries=300)
+    else:
+        rc = rk.train(x, queries=q)
+        e.set_rotation(rk.rotation_matrix())
+        c = e.train(x, queries=q)
+    rs, es = rk.stats(), e.stats(0)
+    assert len(rs) == len(es)          # stopped at the same iteration
+    for r, s in zip(rs, es):
+        assert r["recall"] > 0.2
+        assert abs(r["recall"] - s.recall) <= 2e-3, (r["recall"], s.recall)
+    assert _rel_l2(c, rc) < 5e-3
