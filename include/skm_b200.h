@@ -97,7 +97,12 @@ skm_status skm_set_rotation(skm_handle* h, const float* m);
 skm_status skm_get_rotation(skm_handle* h, float* m_out);
 
 /* SuperKMeans::Train / HierarchicalSuperKMeans::Train (superkmeans.h:162-332,
- * hierarchical_superkmeans.h:84-541).  centroids_out: n_clusters x d, host. */
+ * hierarchical_superkmeans.h:84-541).  centroids_out: n_clusters x d, host.  data: n x d row-major, host
+ * memory, or device memory of the handle's GPU when data_on_device != 0.  queries: n_queries x d in HOST
+ * memory, or NULL with n_queries > 0 when config.sample_queries is set (queries are then drawn from the training
+ * rows); with queries every iteration's statistics carry recall@objective_k (superkmeans.h:1044-1087) and early
+ * termination also watches it (:1315-1331).  Flat algorithm only; objective_k and
+ * n_clusters * ann_explore_fraction up to 1536. */
 skm_status skm_train(skm_handle* h, const float* data, uint64_t n, int data_on_device, const float* queries, uint64_t n_queries, float* centroids_out);
 
 /* SuperKMeans::Assign (superkmeans.h:346-382).  out: n entries, host (device if *_on_device). */
