@@ -79,44 +79,45 @@ __device__ __forceinline__ float group_sum(float s, uint32_t gmask) {
 }
 
 // One 64-dimension block for the run [beg, beg + cnt) of `list`, compacted in place; returns the new length.
-// All eight lanes of the group execute this together.  The point's slice of the block stays in registers
-// while consecutive pairs belong to the same point (the list is sorted by point).
+// All eight lanes of the group execute this together, four pairs per trip so that eight 128-byte gathers are in
+// flight per lane group.  The point's slice of the block is loaded only when the point changes (the list is
+// sorted by point).
 __device__ __forceinline__ uint32_t walk_block(uint2* list, uint32_t beg, uint32_t cnt, const float* __restrict__ blk, const float* __restrict__ xblk, size_t d,
                                                const float* best, float ratio, int gl, uint32_t gmask) {
+    constexpr int U = 4;
     uint32_t j = 0, xrow = 0xFFFFFFFFu;
     float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f), x1 = x0;
-    for (uint32_t i = 0; i < cnt; i += 2) {
-        const bool vb = i + 1 < cnt;
-        const uint2 ea = list[beg + i];
-        const uint2 eb = list[beg + (vb ? i + 1 : i)];
-        const uint32_t ra = ea.x & 127u, rb = eb.x & 127u;
-        const float* ca = blk + static_cast<size_t>(ea.x >> 7) * kHBlock;
-        const float* cb = blk + static_cast<size_t>(eb.x >> 7) * kHBlock;
-        const float4 ca0 = __ldg(reinterpret_cast<const float4*>(ca)), ca1 = __ldg(reinterpret_cast<const float4*>(ca + 4));
-        const float4 cb0 = __ldg(reinterpret_cast<const float4*>(cb)), cb1 = __ldg(reinterpret_cast<const float4*>(cb + 4));
-        if (ra != xrow) {
-            const float* q = xblk + static_cast<size_t>(ra) * d;
-            x0 = __ldg(reinterpret_cast<const float4*>(q));
-            x1 = __ldg(reinterpret_cast<const float4*>(q + 4));
-            xrow = ra;
+    for (uint32_t i = 0; i < cnt; i += U) {
+        uint2 e[U];
+        float4 c0[U], c1[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            e[u] = list[beg + min(i + u, cnt - 1)];
+            const float* c = blk + static_cast<size_t>(e[u].x >> 7) * kHBlock;
+            c0[u] = __ldg(reinterpret_cast<const float4*>(c));
+            c1[u] = __ldg(reinterpret_cast<const float4*>(c + 4));
         }
-        const float sa = group_sum(sqdiff8(x0, x1, ca0, ca1), gmask);
-        if (rb != xrow) {
-            const float* q = xblk + static_cast<size_t>(rb) * d;
-            x0 = __ldg(reinterpret_cast<const float4*>(q));
-            x1 = __ldg(reinterpret_cast<const float4*>(q + 4));
-            xrow = rb;
+        float s[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t r = e[u].x & 127u;
+            if (r != xrow) {
+                const float* q = xblk + static_cast<size_t>(r) * d;
+                x0 = __ldg(reinterpret_cast<const float4*>(q));
+                x1 = __ldg(reinterpret_cast<const float4*>(q + 4));
+                xrow = r;
+            }
+            s[u] = sqdiff8(x0, x1, c0[u], c1[u]);
         }
-        const float sb = group_sum(sqdiff8(x0, x1, cb0, cb1), gmask);
-        const float pda = __uint_as_float(ea.y) + sa;
-        const float pdb = __uint_as_float(eb.y) + sb;
-        const bool ka = pda < best[ra] * ratio;
-        const bool kb = vb && pdb < best[rb] * ratio;
-        if (gl == 0) {
-            if (ka) list[beg + j] = make_uint2(ea.x, __float_as_uint(pda));
-            if (kb) list[beg + j + (ka ? 1u : 0u)] = make_uint2(eb.x, __float_as_uint(pdb));
+#pragma unroll
+        for (int u = 0; u < U; ++u) s[u] = group_sum(s[u], gmask);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const float pd = __uint_as_float(e[u].y) + s[u];
+            const bool keep = (i + u < cnt) && pd < best[e[u].x & 127u] * ratio;
+            if (keep && gl == 0) list[beg + j] = make_uint2(e[u].x, __float_as_uint(pd));
+            j += keep ? 1u : 0u;
         }
-        j += (ka ? 1u : 0u) + (kb ? 1u : 0u);
     }
     __syncwarp(gmask);
     return j;
