@@ -59,7 +59,7 @@ struct Ctrl {
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
     uint32_t pad;
-    float ny[4][2][BN];  // per epilogue warp, per accumulator buffer
+    alignas(16) float ny[4][2][BN];  // per row quarter, per accumulator buffer (read as float4)
 };
 static_assert(sizeof(Ctrl) <= SMEM_CTRL_BYTES, "control block too large");
 
@@ -436,10 +436,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                         // survivors behind those of the lower lanes
                         uint32_t mask = 0;
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const float pd = fmaf(-2.0f, __uint_as_float(r[j]), nx) + ny[ch * 32 + j];
-                            r[j] = __float_as_uint(pd);
-                            mask |= (pd < thr && col0 + ch * 32 + j < p.k) ? (1u << j) : 0u;
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 nyv = *reinterpret_cast<const float4*>(ny + ch * 32 + j);
+                            const float p0 = fmaf(-2.0f, __uint_as_float(r[j + 0]), nx) + nyv.x;
+                            const float p1 = fmaf(-2.0f, __uint_as_float(r[j + 1]), nx) + nyv.y;
+                            const float p2 = fmaf(-2.0f, __uint_as_float(r[j + 2]), nx) + nyv.z;
+                            const float p3 = fmaf(-2.0f, __uint_as_float(r[j + 3]), nx) + nyv.w;
+                            r[j + 0] = __float_as_uint(p0);
+                            r[j + 1] = __float_as_uint(p1);
+                            r[j + 2] = __float_as_uint(p2);
+                            r[j + 3] = __float_as_uint(p3);
+                            mask |= (p0 < thr ? (1u << j) : 0u) | (p1 < thr ? (2u << j) : 0u) | (p2 < thr ? (4u << j) : 0u) | (p3 < thr ? (8u << j) : 0u);
+                        }
+                        {
+                            // columns past the last centroid (zero-filled by TMA) never count
+                            const size_t first = col0 + static_cast<size_t>(ch) * 32;
+                            const uint32_t n_valid = first >= p.k ? 0u : static_cast<uint32_t>(min(static_cast<size_t>(32), p.k - first));
+                            mask &= n_valid >= 32u ? 0xFFFFFFFFu : ((1u << n_valid) - 1u);
                         }
                         const uint32_t cnt = __popc(mask);
                         uint32_t incl = cnt;
@@ -455,12 +468,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                                 // survivors are packed in shared memory first (predicated stores, no divergence) and
                                 // leave for global memory as contiguous runs
                                 uint2* stg = reinterpret_cast<uint2*>(smem + STAGES * STAGE_BYTES + SMEM_CTRL_BYTES) + (warp - 6) * STAGE_ENTRIES;
-                                uint32_t pos = incl - cnt;
+                                // slot of column j = this lane's first slot + number of its survivors below j: no chain
+                                // of dependent additions through the 32 columns
+                                const uint32_t base = incl - cnt;
 #pragma unroll
                                 for (int j = 0; j < 32; ++j) {
-                                    const uint32_t bit = (mask >> j) & 1u;
-                                    if (bit) stg[pos] = make_uint2((colbits + (static_cast<uint32_t>(j) << 5)) | lane, r[j]);
-                                    pos += bit;
+                                    if ((mask >> j) & 1u) stg[base + __popc(mask & ((1u << j) - 1u))] = make_uint2((colbits + (static_cast<uint32_t>(j) << 5)) | lane, r[j]);
                                 }
                                 __syncwarp();
                                 for (uint32_t i = lane; i < total; i += 32)

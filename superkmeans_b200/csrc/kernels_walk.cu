@@ -79,12 +79,12 @@ __device__ __forceinline__ float group_sum(float s, uint32_t gmask) {
 }
 
 // One 64-dimension block for the run [beg, beg + cnt) of `list`, compacted in place; returns the new length.
-// All eight lanes of the group execute this together, four pairs per trip so that eight 128-byte gathers are in
+// All eight lanes of the group execute this together, two pairs per trip so that four 128-byte gathers are in
 // flight per lane group.  The point's slice of the block is loaded only when the point changes (the list is
 // sorted by point).
 __device__ __forceinline__ uint32_t walk_block(uint2* list, uint32_t beg, uint32_t cnt, const float* __restrict__ blk, const float* __restrict__ xblk, size_t d,
                                                const float* best, float ratio, int gl, uint32_t gmask) {
-    constexpr int U = 4;
+    constexpr int U = 2;
     uint32_t j = 0, xrow = 0xFFFFFFFFu;
     float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f), x1 = x0;
     for (uint32_t i = 0; i < cnt; i += U) {
@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(kWalkThreads, 3) walk_lists_kernel(const WalkP
             const size_t cs = min(static_cast<size_t>(kChunk), w.k - c0);
             if (tid < kTileM) {
                 sh.thr[tid] = sh.best[tid] * ratio_first;
-                sh.margin[tid] = 5e-5f * sh.best[tid] + 2e-5f * sh.nx[tid];
+                sh.margin[tid] = 1e-5f * sh.nx[tid];   // the tensor-core part of a distance is within ~3e-6 of the norms over d'
                 sh.cnt[tid] = 0;
                 sh.prev_flag[tid] = 0;
                 sh.key[tid] = ~0ull;
@@ -341,10 +341,13 @@ __global__ void __launch_bounds__(kWalkThreads, 3) walk_lists_kernel(const WalkP
                         // The first d' dimensions of pd come from the tensor cores (three TF32 products, truncating
                         // accumulator: a few 1e-6 of the norms off).  A pair that would win, or lose, by less than that
                         // is settled with the distance recomputed from direct differences in fp32.
-                        if (pd < sh.best[r] + sh.margin[r]) {
+                        // (The pair with the previous centroid needs none of this: its exact distance is `best` itself,
+                        // which it cannot undercut.)
+                        if (pd < sh.best[r] + sh.margin[r] && static_cast<uint32_t>(c) != sh.prev[r]) {
                             const float4* q4 = reinterpret_cast<const float4*>(w.x + (row0 + r) * w.d);
                             const float4* c4 = reinterpret_cast<const float4*>(w.y + c * w.d);
                             float s0 = 0.f, s1 = 0.f;
+#pragma unroll 8
                             for (uint32_t jj = gl; jj < w.d / 4; jj += 8) {
                                 const float4 a = __ldg(q4 + jj), b = __ldg(c4 + jj);
                                 float t;
