@@ -4,6 +4,7 @@
   reference, with the north-star gates: WCSS within 1e-4 relative, >= 99.9 % identical assignments, centroids of
   clusters with identical members within 1e-5 (any single near-tie that falls the other way moves two centroids by
   ~1/cluster size, which is why the plain centroid norm is gated at 5e-3 and not at 1e-4).
+* Config 2's data law at a size the reference finishes in seconds.
 * Configs 2, 3 and 5 at FULL size on device-generated data, through properties that do not need the reference:
   exact assignment is the float64 arg-min on sampled rows (up to near-ties of 1e-5), the pruned assignment of the
   training points agrees with the exact one on >= 98 % of the points (the reference's own bar,
@@ -51,6 +52,27 @@ def test_config1_full_size_matches_reference(ref):
     # Train + Assign, as the configuration says
     asg, rasg = e.assign(x, c), rk.assign(x, rc)
     assert (asg == rasg).mean() >= 0.999
+
+
+def test_config2_shape_matches_reference(ref):
+    """Config 2's data law (anisotropic mixture, d = 1536) at n = 60 000, k = 1024, against the reference."""
+    import superkmeans_b200 as skm
+
+    n, d, k, seed = 60_000, 1536, 1024, 7
+    x = datagen.config2(n, d, k, seed)
+    kw = dict(iters=8, sampling_fraction=1.0, early_termination=0, seed=seed)
+    rk = ref.RefKMeans(k, d, ref.default_config(False, **kw))
+    rc = rk.train(x)
+    e = skm.Engine(k, d, skm.default_config(False, **kw))
+    e.set_rotation(rk.rotation_matrix())
+    c = e.train(x)
+    assert [r["partial_d"] for r in rk.stats()] == [s.partial_d for s in e.stats(0)]
+    ra, a = rk.assignments(), e.assignments()
+    w, rw = _wcss64(x, c, a), _wcss64(x, rc, ra)
+    assert abs(w - rw) <= 1e-4 * rw, (w, rw)
+    assert (ra == a).mean() >= 0.999
+    assert np.linalg.norm(c - rc) / np.linalg.norm(rc) < 5e-3
+    assert (e.assign(x, c) == rk.assign(x, rc)).mean() >= 0.999
 
 
 def test_config4_shape_hierarchical_matches_reference(ref):
