@@ -136,6 +136,7 @@ struct WalkParams {
     uint32_t* redo;              // set to 1 for points whose group list overflowed
     uint32_t* redo_count;
     unsigned long long* pair_steps;            // += pairs advanced by one 64-dimension block
+    uint32_t rebalance_mask = 0x22;            // bit b: even the runs out after block b (here: after the 2nd and the 6th)
 };
 void launch_walk_lists(const WalkParams& w, int device, cudaStream_t stream);
 // hard_idx / *n_hard_dev from an arbitrary flag array (same buffers as launch_pruned_prepare fills)

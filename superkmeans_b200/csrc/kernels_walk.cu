@@ -15,8 +15,8 @@
 //     lanes a contiguous run of them; a group advances its run 64 horizontal dimensions at a time (128
 //     contiguous bytes of the PDX block per load, the point's slice held in registers while the point does
 //     not change), re-tests after every block and compacts the run in place, so no lane idles behind a pair
-//     that died early and no block-wide barrier is needed between blocks; the runs are evened out once,
-//     after the first two blocks;
+//     that died early and no block-wide barrier is needed between blocks; the runs are evened out twice
+//     on the way (after the second and the sixth block);
 //   * adds the vertical dimensions [d', vertical_d), takes the per-point minimum, lowers `best`.
 // `best` is constant inside a chunk, so pairs are independent and any processing order gives the same
 // result.
@@ -34,7 +34,6 @@ constexpr int kWalkGroups = kWalkThreads / 8;     // lane groups of eight, one p
 constexpr int kWalkPerThread = 8;                 // listed pairs a thread loads per batch
 constexpr int kWalkBatch = kWalkThreads * kWalkPerThread;
 constexpr int kWalkListCap = kWalkBatch + kTileM; // + the held-back pairs with the previous centroid
-constexpr int kRebalanceAfter = 2;                // blocks after which the runs are evened out once
 
 struct WalkShared {
     uint2 list[2][kWalkListCap];   // {local centroid << 7 | row in tile, partial distance}, sorted by row
@@ -271,33 +270,28 @@ __global__ void __launch_bounds__(kWalkThreads, 3) walk_lists_kernel(const WalkP
                 uint32_t run = (m + kWalkGroups - 1) / kWalkGroups;
                 uint32_t beg = min(static_cast<uint32_t>(g) * run, m);
                 uint32_t len = min(run, m - beg);
-                size_t hb = 0;
-                for (; hb < n_h && hb < static_cast<size_t>(kRebalanceAfter); ++hb) {
+                for (size_t hb = 0; hb < n_h; ++hb) {
                     steps_done += (gl == 0) ? len : 0u;
                     len = walk_block(sh.list[cur], beg, len, blk_chunk + hb * cs * kHBlock + gl * 8, w.x + row0 * w.d + w.vertical_d + hb * kHBlock + gl * 8, w.d, sh.best,
                                      __ldg(w.ratios + w.partial_d + (hb + 1) * kHBlock), gl, gmask);
-                }
-                if (hb < n_h) {
-                    // even the runs out once: early blocks remove most of what will ever be removed
-                    if (gl == 0) sh.gcount[g] = len;
-                    __syncthreads();
-                    uint32_t off = 0, tot = 0;
-                    for (int q = 0; q < kWalkGroups; ++q) {
-                        const uint32_t c = sh.gcount[q];
-                        off += (q < g) ? c : 0u;
-                        tot += c;
-                    }
-                    for (uint32_t i = gl; i < len; i += 8) sh.list[cur ^ 1][off + i] = sh.list[cur][beg + i];
-                    __syncthreads();
-                    cur ^= 1;
-                    m = tot;
-                    run = (m + kWalkGroups - 1) / kWalkGroups;
-                    beg = min(static_cast<uint32_t>(g) * run, m);
-                    len = min(run, m - beg);
-                    for (; hb < n_h; ++hb) {
-                        steps_done += (gl == 0) ? len : 0u;
-                        len = walk_block(sh.list[cur], beg, len, blk_chunk + hb * cs * kHBlock + gl * 8, w.x + row0 * w.d + w.vertical_d + hb * kHBlock + gl * 8, w.d,
-                                         sh.best, __ldg(w.ratios + w.partial_d + (hb + 1) * kHBlock), gl, gmask);
+                    if (((w.rebalance_mask >> hb) & 1u) && hb + 1 < n_h) {
+                        // even the runs out (the only block-wide barriers between blocks): runs that hold pairs of
+                        // a point with a loose threshold keep everything, others die out
+                        if (gl == 0) sh.gcount[g] = len;
+                        __syncthreads();
+                        uint32_t off = 0, tot = 0;
+                        for (int q = 0; q < kWalkGroups; ++q) {
+                            const uint32_t c = sh.gcount[q];
+                            off += (q < g) ? c : 0u;
+                            tot += c;
+                        }
+                        for (uint32_t i = gl; i < len; i += 8) sh.list[cur ^ 1][off + i] = sh.list[cur][beg + i];
+                        __syncthreads();
+                        cur ^= 1;
+                        m = tot;
+                        run = (m + kWalkGroups - 1) / kWalkGroups;
+                        beg = min(static_cast<uint32_t>(g) * run, m);
+                        len = min(run, m - beg);
                     }
                 }
 
