@@ -95,6 +95,11 @@ void skm_destroy(skm_handle* h);
  * Rotate computes X * M^T (:191-215).  Setting it replaces the matrix generated from the seed. */
 skm_status skm_set_rotation(skm_handle* h, const float* m);
 skm_status skm_get_rotation(skm_handle* h, float* m_out);
+/* Replaces the matrix by the rotation of ADSamplingPruner's DCT branch (adsampling.h:53-73, :169-188: random sign
+ * flips from the seed, then an orthonormal DCT-II), which the reference uses instead of the QR matrix when it is
+ * built with FFTW and d is a power of two >= 512.  Applied as a matrix product here (same values up to fp32
+ * rounding, not the O(d log d) cost).  Call before skm_train. */
+skm_status skm_use_dct_rotation(skm_handle* h);
 
 /* SuperKMeans::Train / HierarchicalSuperKMeans::Train (superkmeans.h:162-332,
  * hierarchical_superkmeans.h:84-541).  centroids_out: n_clusters x d, host.  data: n x d row-major, host
@@ -244,6 +249,8 @@ void skm_host_arrange_fine_clusters(uint64_t n_clusters, uint64_t n_meso, uint64
 uint64_t skm_host_pdx_offset(uint64_t row, uint64_t dim, uint64_t n, uint64_t d);
 /* The seed-derived rotation matrix (adsampling.h:76-85), d x d row-major. */
 void skm_host_rotation_matrix(uint64_t d, uint32_t seed, float* out);
+/* The sign-flip + DCT-II rotation of the reference's FFTW branch as a matrix (adsampling.h:53-73, :169-188). */
+void skm_host_dct_rotation_matrix(uint64_t d, uint32_t seed, float* out);
 
 #ifdef __cplusplus
 }

@@ -115,6 +115,8 @@ SIGNATURES = {
     "skm_host_arrange_fine_clusters": (None, [C.c_uint64, C.c_uint64, C.c_uint64, u32p, u64p]),
     "skm_host_pdx_offset": (C.c_uint64, [C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
     "skm_host_rotation_matrix": (None, [C.c_uint64, C.c_uint32, f32p]),
+    "skm_host_dct_rotation_matrix": (None, [C.c_uint64, C.c_uint32, f32p]),
+    "skm_use_dct_rotation": (C.c_int, [C.c_void_p]),
 }
 
 

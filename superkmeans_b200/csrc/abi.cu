@@ -106,6 +106,14 @@ skm_status skm_set_rotation(skm_handle* h, const float* m) {
     return guarded(h->err, [&] { h->engine->set_rotation(m); });
 }
 
+skm_status skm_use_dct_rotation(skm_handle* h) {
+    SKM_NEED(h);
+    return guarded(h->err, [&] {
+        const std::vector<float> m = skmb::make_dct_rotation_matrix(h->engine->dimensionality(), h->engine->config().seed);
+        h->engine->set_rotation(m.data());
+    });
+}
+
 skm_status skm_get_rotation(skm_handle* h, float* m_out) {
     SKM_NEED(h);
     return guarded(h->err, [&] { h->engine->get_rotation(m_out); });
@@ -308,6 +316,11 @@ uint64_t skm_host_pdx_offset(uint64_t row, uint64_t dim, uint64_t n, uint64_t d)
 
 void skm_host_rotation_matrix(uint64_t d, uint32_t seed, float* out) {
     const std::vector<float> m = skmb::make_rotation_matrix(d, seed);
+    std::memcpy(out, m.data(), sizeof(float) * m.size());
+}
+
+void skm_host_dct_rotation_matrix(uint64_t d, uint32_t seed, float* out) {
+    const std::vector<float> m = skmb::make_dct_rotation_matrix(d, seed);
     std::memcpy(out, m.data(), sizeof(float) * m.size());
 }
 

@@ -149,6 +149,8 @@ class Engine {
     void get_rotated_centroids(float* out);
 
     size_t n_clusters() const { return k_; }
+    size_t dimensionality() const { return d_; }
+    const skm_config& config() const { return cfg_; }
     bool trained() const { return trained_; }
     float sampling_fraction() const { return cfg_.sampling_fraction; }
     size_t n_mesoclusters_value() const { return n_meso_; }

@@ -292,6 +292,27 @@ inline std::vector<size_t> arrange_fine_clusters(size_t n_clusters, size_t n_mes
 // rotation.  Sign convention: each reflector maps its column to -sign(x0)*||x|| e1, as in the usual
 // LAPACK/Eigen formulation, so Q agrees with the reference's up to floating-point rounding.
 // Computed in double, rounded once to float.  Output row-major d x d.
+// The rotation of ADSamplingPruner's DCT branch (adsampling.h:53-73, :169-188) as an explicit matrix: a random sign
+// per input dimension, then the orthonormal DCT-II (FFTW's REDFT10, 2 * sum_j x_j cos(pi (j + 1/2) k / d), scaled by
+// sqrt(1 / 4d) for k = 0 and sqrt(1 / 2d) otherwise).  M[k][j] = scale_k * 2 cos(pi (j + 1/2) k / d) * sign_j, so that
+// X * M^T is what a reference built with FFTW computes for power-of-two d >= 512.
+inline std::vector<float> make_dct_rotation_matrix(size_t d, uint32_t seed) {
+    std::mt19937 gen(seed);
+    std::uniform_int_distribution<int> dist(0, 1);
+    std::vector<double> sign(d);
+    for (size_t j = 0; j < d; ++j) sign[j] = dist(gen) ? 1.0 : -1.0;
+    std::vector<float> m(d * d);
+    const double pi = 3.14159265358979323846;
+    const double s0 = std::sqrt(1.0 / (4.0 * static_cast<double>(d))), s = std::sqrt(1.0 / (2.0 * static_cast<double>(d)));
+    for (size_t k = 0; k < d; ++k) {
+        const double scale = (k == 0 ? s0 : s) * 2.0;
+        for (size_t j = 0; j < d; ++j) {
+            m[k * d + j] = static_cast<float>(scale * std::cos(pi * (static_cast<double>(j) + 0.5) * static_cast<double>(k) / static_cast<double>(d)) * sign[j]);
+        }
+    }
+    return m;
+}
+
 inline std::vector<float> make_rotation_matrix(size_t d, uint32_t seed) {
     std::mt19937 gen(seed);
     std::normal_distribution<float> dist(0.0f, 1.0f);

@@ -146,6 +146,10 @@ class Engine:
     def last_objective_f64(self) -> float:
         return float(lib.skm_last_objective_f64(self._h))
 
+    def use_dct_rotation(self):
+        """Rotate with sign flips + DCT-II (what the reference does when built with FFTW, d a power of two >= 512)."""
+        check(lib.skm_use_dct_rotation(self._h), self._h)
+
     def set_trace(self, enabled: bool = True):
         check(lib.skm_set_trace(self._h, int(enabled)), self._h)
 
@@ -334,4 +338,11 @@ def pdx_offset(row: int, dim: int, n: int, d: int) -> int:
 def rotation_matrix(d: int, seed: int) -> np.ndarray:
     out = np.empty((d, d), dtype=np.float32)
     lib.skm_host_rotation_matrix(d, seed, out)
+    return out
+
+
+def dct_rotation_matrix(d: int, seed: int) -> np.ndarray:
+    """Random sign flips + orthonormal DCT-II as a d x d matrix (the reference's FFTW rotation branch)."""
+    out = np.empty((d, d), dtype=np.float32)
+    lib.skm_host_dct_rotation_matrix(d, seed, out)
     return out

@@ -143,3 +143,19 @@ def test_forgy_indices_are_a_seeded_sample_without_replacement():
     assert len(set(a.tolist())) == 50 and a.max() < 1000
     np.testing.assert_array_equal(a, eng.forgy_indices(1000, 50, 42))
     assert (a != eng.forgy_indices(1000, 50, 43)).any()
+
+
+def test_dct_rotation_matrix_is_the_orthonormal_dct_of_sign_flipped_rows():
+    """adsampling.h:53-73, :169-188: out = DCT-II(x * signs), FFTW REDFT10 scaled to be orthonormal."""
+    import scipy.fft
+
+    from superkmeans_b200 import engine as eng
+
+    for d, seed in ((512, 42), (1024, 7), (64, 3)):
+        m = eng.dct_rotation_matrix(d, seed).astype(np.float64)
+        assert np.abs(m @ m.T - np.eye(d)).max() < 1e-6
+        signs = m[0] / np.abs(m[0])          # row 0 of the DCT is constant, so it shows the signs
+        assert set(np.unique(signs)) <= {-1.0, 1.0} and 0.3 < (signs > 0).mean() < 0.7
+        x = np.random.default_rng(seed).standard_normal((5, d))
+        want = scipy.fft.dct(x * signs, type=2, norm="ortho", axis=1)
+        assert np.abs(x @ m.T - want).max() < 1e-5

@@ -248,3 +248,24 @@ def test_train_with_queries_tracks_recall_like_the_reference(ref, sample_queries
         assert r["recall"] > 0.2
         assert abs(r["recall"] - s.recall) <= 2e-3, (r["recall"], s.recall)
     assert _rel_l2(c, rc) < 5e-3
+
+
+def test_dct_rotation_gives_an_equivalent_clustering():
+    """The sign-flip + DCT rotation (adsampling.h:53-73) is another orthogonal change of basis: exact iterations give
+    the same clustering up to rounding, pruned ones a clustering of the same quality."""
+    import superkmeans_b200 as skm
+
+    n, d, k = 20000, 512, 300
+    x = datagen.gaussian_mixture(n, d, k, 0.3, 31)
+    kw = dict(iters=5, sampling_fraction=1.0, early_termination=0, seed=31)
+    res = []
+    for dct in (False, True):
+        e = skm.Engine(k, d, skm.default_config(False, **kw))
+        if dct:
+            e.use_dct_rotation()
+            m = np.empty((d, d), dtype=np.float32)
+            assert np.abs(e.get_rotation() - skm.engine.dct_rotation_matrix(d, 31)).max() == 0
+        c = e.train(x)
+        a = e.assign(x, c)
+        res.append(float(((x.astype(np.float64) - c[a].astype(np.float64)) ** 2).sum()))
+    assert abs(res[0] - res[1]) <= 2e-2 * res[0], res
