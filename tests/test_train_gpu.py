@@ -263,7 +263,6 @@ def test_dct_rotation_gives_an_equivalent_clustering():
         e = skm.Engine(k, d, skm.default_config(False, **kw))
         if dct:
             e.use_dct_rotation()
-            m = np.empty((d, d), dtype=np.float32)
             assert np.abs(e.get_rotation() - skm.engine.dct_rotation_matrix(d, 31)).max() == 0
         c = e.train(x)
         a = e.assign(x, c)
