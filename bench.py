@@ -134,10 +134,19 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------
 # Reference arm / CPU baseline: the unmodified reference (oracle/_ref) on a bounded sample
 # ---------------------------------------------------------------------------------------------
+def host_cores() -> int:
+    """Cores this process may use (torchrun exports OMP_NUM_THREADS=1, which would otherwise throttle the reference)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def reference_train(sample: np.ndarray, k: int, iters: int, seed: int):
     from oracle import ref
 
-    cfg = ref.default_config(False, iters=iters, sampling_fraction=1.0, early_termination=0, seed=seed)
+    ref.lib().ref_set_blas_threads(host_cores())
+    cfg = ref.default_config(False, iters=iters, sampling_fraction=1.0, early_termination=0, seed=seed, n_threads=host_cores())
     km = ref.RefKMeans(k, sample.shape[1], cfg)  # rotation matrix is built here, outside the timed call, as in the reference's own drivers
     t0 = time.perf_counter()
     cent = km.train(sample)
@@ -167,7 +176,7 @@ def run_reference_arm(args):
         return
     rows = max(args.k, min(args.cpu_sample, args.n))
     sample = host_sample(args, rows)
-    cores = ref.lib().ref_get_omp_threads()
+    cores = host_cores()
     times = []
     for i in range(args.warmup + args.steps):
         dt, km, _ = reference_train(sample, args.k, args.iters, HEADLINE["seed"])
@@ -340,7 +349,7 @@ def main():
             sample = np.ascontiguousarray(x[:rows].cpu().numpy())
             dt, km, rc = reference_train(sample, k, iters, HEADLINE["seed"])
             r_it = len(km.stats())
-            cpu_baseline = {"value": rows * r_it / dt, "unit": "points*iters/s", "cores": int(ref.lib().ref_get_omp_threads()), "kind": "reference", "train_s": dt,
+            cpu_baseline = {"value": rows * r_it / dt, "unit": "points*iters/s", "cores": host_cores(), "kind": "reference", "train_s": dt,
                             "sample": f"first {rows} rows of the workload, same d, k and iterations"}
             # Parity against the reference on a separate, well-conditioned sample of the same dimensionality: as many
             # mixture centres as clusters (k_p > 256 keeps the pruned path on), ~300 points per cluster.  On the
