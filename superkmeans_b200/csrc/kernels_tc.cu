@@ -606,21 +606,36 @@ struct ChainMaps {
 // hi/lo by the splitter warps, Y hi and lo straight from global memory), two accumulators of 256 columns.
 // The two accumulators belong to two neighbouring centroid units that advance through the segments in
 // turn, so the tensor pipe works on one unit while the rows' threads test the other.
+// What the two threads of a row (one per half of the columns) tell each other at the end of a chunk.
+struct ChainPartial {
+    uint32_t cnt;          // survivors of the first test in this chunk
+    uint32_t prev_first;   // the previous centroid is among them
+    float cb;              // best final distance of the chunk, FLT_MAX if none
+    uint32_t cbi;
+    float t1, t2;          // the two smallest final distances of the row so far (candidates for the refinement)
+    uint32_t i1, i2;
+};
+
 struct ChainCtrl {
     uint64_t full[STAGES];
     uint64_t conv[STAGES];
     uint64_t empty[STAGES];
     uint64_t acc_ready[2];    // MMA -> epilogue: accumulator a holds the chain up to the current segment
     uint64_t acc_loaded[2];   // epilogue -> MMA: every row has read it
+    uint64_t xchg_bar;        // the 256 row threads have published their ChainPartial
     uint32_t tmem_base;
     uint32_t pad;
-    alignas(16) float ny[4][BN];   // per epilogue warp: centroid norms of the unit at the current checkpoint
+    alignas(16) float ny[4][BN];   // per quarter of the rows: centroid norms of the unit at the current checkpoint
     float seg_ratio[64];           // ratios[dimensions seen after segment s]
+    alignas(16) ChainPartial xchg[2][2][BM];   // [use parity][column half][row]
 };
-static_assert(sizeof(ChainCtrl) <= SMEM_CTRL_BYTES, "control block too large");
-constexpr uint32_t C_SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + 1024;
+constexpr uint32_t C_CTRL_BYTES = 24576;
+static_assert(sizeof(ChainCtrl) <= C_CTRL_BYTES, "control block too large");
+constexpr uint32_t C_SMEM_BYTES = STAGES * STAGE_BYTES + C_CTRL_BYTES + 1024;
 constexpr uint32_t CHAIN_MAX_SEGMENTS = 64;
-constexpr int CHAIN_THREADS = 320;   // producer, MMA issuer, four splitter warps, four row warps
+// producer, MMA issuer, four splitter warps, eight row warps: warps 6-9 test columns 0-127 of every 256-centroid
+// unit, warps 10-13 columns 128-255; the two threads of a row merge their findings at the end of every chunk
+constexpr int CHAIN_THREADS = 448;
 
 // Order of work shared by all roles: row tile, chunk of 1024 centroids, pair of 256-centroid units, segment,
 // unit of the pair.  `a` (0 / 1) is the unit's accumulator.
@@ -660,8 +675,9 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&ctrl->acc_ready[a], 1);
-            mbar_init(&ctrl->acc_loaded[a], 128);
+            mbar_init(&ctrl->acc_loaded[a], 256);
         }
+        mbar_init(&ctrl->xchg_bar, 256);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
     }
@@ -779,10 +795,13 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
             }
         })
     } else {
+        // (warps 6 .. 13)
         // ---------------------------------------------------------------- rows: tests at every checkpoint
+        const uint32_t half = static_cast<uint32_t>(warp - 6) >> 2;   // which 128 of a unit's 256 columns
         const uint32_t lane_base = 32u * (warp & 3);
         const uint32_t row_in_tile = lane_base + lane;
         uint32_t uses[2] = {0, 0};
+        uint32_t xchg_uses = 0;
         bool ok = true;
         size_t cur_rt = ~size_t{0};
         uint32_t cur_chunk = 0xFFFFFFFFu;
@@ -790,36 +809,77 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
         bool row_valid = false;
         float best = -1.f, cb = FLT_MAX, t1 = FLT_MAX, t2 = FLT_MAX;
         uint32_t bestidx = 0, prev = 0xFFFFFFFFu, npc = 0, cnt = 0, cbi = 0, i1 = 0xFFFFFFFFu, i2 = 0xFFFFFFFFu;
+        uint32_t o1 = 0xFFFFFFFFu, o2 = 0xFFFFFFFFu;   // merged runner-ups of the row, set at every chunk end
         bool prev_first = false;
+        constexpr int HS = BN / 64;   // 32-column slices per half
         // survivor masks of the two units in flight (kept apart so that both stay in registers)
-        uint32_t alive0[BN / 32], alive1[BN / 32];
+        uint32_t alive0[HS], alive1[HS];
 #pragma unroll
-        for (int q = 0; q < BN / 32; ++q) alive0[q] = alive1[q] = 0;
+        for (int q = 0; q < HS; ++q) alive0[q] = alive1[q] = 0;
         float* ny = ctrl->ny[warp & 3];
-        auto close_chunk = [&]() {
-            npc += cnt;
+        // End of a chunk: the two threads of the row exchange what they found in their halves of the columns and
+        // both apply the same update.  Returns false when the wait ran out.
+        auto close_chunk = [&]() -> bool {
+            ChainPartial mine;
+            mine.cnt = cnt;
+            mine.prev_first = prev_first ? 1u : 0u;
+            mine.cb = cb;
+            mine.cbi = cbi;
+            mine.t1 = t1;
+            mine.t2 = t2;
+            mine.i1 = i1;
+            mine.i2 = i2;
+            const uint32_t slot = xchg_uses & 1u;
+            ctrl->xchg[slot][half][row_in_tile] = mine;
+            __threadfence_block();
+            mbar_arrive(&ctrl->xchg_bar);
+            if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->xchg_bar, xchg_uses & 1u, p.error, 16))) return false;
+            ++xchg_uses;
+            const ChainPartial other = ctrl->xchg[slot][half ^ 1u][row_in_tile];
+            const uint32_t cnt_all = cnt + other.cnt;
+            const bool prev_all = prev_first || other.prev_first != 0u;
+            float mb = cb;
+            uint32_t mbi = cbi;
+            if (other.cb < mb || (other.cb == mb && other.cbi < mbi)) {
+                mb = other.cb;
+                mbi = other.cbi;
+            }
+            npc += cnt_all;
             // pdxearch.h:140-143: the previous centroid as the only survivor leaves the candidate untouched
-            if (cb < FLT_MAX && !(cnt == 1u && prev_first)) {
-                best = cb;
-                bestidx = cbi;
+            if (mb < FLT_MAX && !(cnt_all == 1u && prev_all)) {
+                best = mb;
+                bestidx = mbi;
+            }
+            // the two smallest of both halves, for the end of the row (the halves' own pairs cover disjoint columns
+            // and stay as they are)
+            if (other.t1 < t1) {
+                o2 = (t1 < other.t2) ? i1 : other.i2;
+                o1 = other.i1;
+            } else {
+                o1 = i1;
+                o2 = (other.t1 < t2) ? other.i1 : i2;
             }
             cnt = 0;
             prev_first = false;
             cb = FLT_MAX;
             cbi = 0;
+            return true;
         };
         auto close_row = [&]() {
-            if (row_valid) {
+            if (row_valid && half == 0) {
                 p.knn[row] = bestidx;
                 p.dist[row] = best;
                 p.not_pruned[row] = npc;
-                p.top2[row] = make_uint2(i1, i2);
+                p.top2[row] = make_uint2(o1, o2);
             }
         };
         CHAIN_FOR_EACH_UNIT_SEGMENT({
             if (rt != cur_rt) {
                 if (cur_rt != ~size_t{0}) {
-                    close_chunk();
+                    if (!close_chunk()) {
+                        ok = false;
+                        break;
+                    }
                     close_row();
                 }
                 cur_rt = rt;
@@ -837,7 +897,10 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
                 t1 = t2 = FLT_MAX;
                 i1 = i2 = 0xFFFFFFFFu;
             } else if (chunk != cur_chunk) {
-                close_chunk();
+                if (!close_chunk()) {
+                    ok = false;
+                    break;
+                }
                 cur_chunk = chunk;
             }
             const size_t col0 = c0 + static_cast<size_t>(unit) * BN;
@@ -845,15 +908,16 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
             const float thr = best * ctrl->seg_ratio[seg];
             const float nxv = row_valid ? __ldg(p.chain_norms_x + row * p.n_seg + seg) : 0.f;
             const bool first = seg == 0, last = (seg + 1 == p.n_seg);
-            // this warp's copy of the unit's centroid norms at this checkpoint
+            // centroid norms of the unit at this checkpoint: the two warps of a row quarter fill (and read) disjoint
+            // halves of the quarter's copy
             {
-                const float* __restrict__ src = p.chain_norms_y + static_cast<size_t>(seg) * p.k + col0;
-                float cur[BN / 32];
+                const float* __restrict__ src = p.chain_norms_y + static_cast<size_t>(seg) * p.k + col0 + half * (BN / 2);
+                float cur[HS];
 #pragma unroll
-                for (uint32_t q = 0; q < BN / 32; ++q) cur[q] = (q * 32 + lane < cols_valid) ? __ldg(src + q * 32 + lane) : 0.f;
+                for (uint32_t q = 0; q < HS; ++q) cur[q] = (half * (BN / 2) + q * 32 + lane < cols_valid) ? __ldg(src + q * 32 + lane) : 0.f;
                 __syncwarp();
 #pragma unroll
-                for (uint32_t q = 0; q < BN / 32; ++q) ny[q * 32 + lane] = cur[q];
+                for (uint32_t q = 0; q < HS; ++q) ny[half * (BN / 2) + q * 32 + lane] = cur[q];
                 __syncwarp();
             }
             if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->acc_ready[a], uses[a] & 1u, p.error, 15))) {
@@ -862,10 +926,10 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
             }
             ++uses[a];
             tc_fence_after();
-            const uint32_t taddr = tmem_base + (lane_base << 16) + a * BN;
-            uint32_t alive[BN / 32];
+            const uint32_t taddr = tmem_base + (lane_base << 16) + a * BN + half * (BN / 2);
+            uint32_t alive[HS];
 #pragma unroll
-            for (int q = 0; q < BN / 32; ++q) alive[q] = a ? alive1[q] : alive0[q];
+            for (int q = 0; q < HS; ++q) alive[q] = a ? alive1[q] : alive0[q];
             // One 32-column slice is tested while the next one is on its way from tensor memory.
             auto test_slice = [&](const uint32_t ch, uint32_t (&r)[32], uint32_t& alive_ch) {
                 // bit j of w = (partial distance of column ch * 32 + j < threshold), branch-free
@@ -933,35 +997,35 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
             tmem_ld_wait(ra);
             // Rolled on purpose (two slices per trip): unrolled, the tests of a whole unit do not fit the instruction
             // cache.  The survivor masks rotate through alive[0] and alive[1] so that they stay in registers.
+            const uint32_t slice0 = half * HS;   // first of this thread's slices inside the unit
 #pragma unroll 1
-            for (uint32_t ch = 0; ch < BN / 32; ch += 2) {
+            for (uint32_t ch = 0; ch < HS; ch += 2) {
                 tmem_ld32_issue(taddr + (ch + 1) * 32, rb);
-                test_slice(ch, ra, alive[0]);
+                test_slice(slice0 + ch, ra, alive[0]);
                 tmem_ld_wait(rb);
-                if (ch + 2 < BN / 32) {
+                if (ch + 2 < HS) {
                     tmem_ld32_issue(taddr + (ch + 2) * 32, ra);
                 } else {
                     // everything of this checkpoint is in registers: the accumulator may grow again
                     tc_fence_before();
                     mbar_arrive(&ctrl->acc_loaded[a]);
                 }
-                test_slice(ch + 1, rb, alive[1]);
-                if (ch + 2 < BN / 32) tmem_ld_wait(ra);
+                test_slice(slice0 + ch + 1, rb, alive[1]);
+                if (ch + 2 < HS) tmem_ld_wait(ra);
                 const uint32_t m0 = alive[0], m1 = alive[1];
 #pragma unroll
-                for (int q = 0; q < BN / 32 - 2; ++q) alive[q] = alive[q + 2];
-                alive[BN / 32 - 2] = m0;
-                alive[BN / 32 - 1] = m1;
+                for (int q = 0; q < HS - 2; ++q) alive[q] = alive[q + 2];
+                alive[HS - 2] = m0;
+                alive[HS - 1] = m1;
             }
 #pragma unroll
-            for (int q = 0; q < BN / 32; ++q) {
+            for (int q = 0; q < HS; ++q) {
                 if (a) alive1[q] = alive[q];
                 else alive0[q] = alive[q];
             }
         })
         if (ok && cur_rt != ~size_t{0}) {
-            close_chunk();
-            close_row();
+            if (close_chunk()) close_row();
         }
     }
 #undef CHAIN_FOR_EACH_UNIT_SEGMENT

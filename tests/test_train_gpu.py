@@ -268,3 +268,28 @@ def test_dct_rotation_gives_an_equivalent_clustering():
         a = e.assign(x, c)
         res.append(float(((x.astype(np.float64) - c[a].astype(np.float64)) ** 2).sum()))
     assert abs(res[0] - res[1]) <= 2e-2 * res[0], res
+
+
+@pytest.mark.parametrize("opts", [dict(angular=1), dict(data_already_rotated=1), dict(unrotate_centroids=0), dict(angular=1, unrotate_centroids=0)],
+                         ids=["angular", "already_rotated", "keep_rotated_centroids", "angular_rotated_out"])
+def test_config_switches_match_reference(ref, opts):
+    """SuperKMeansConfig switches that change what Train does around the iterations: spherical centroids
+    (superkmeans.h:1357-1371), input that is already rotated (:1183-1199, unrotate forced off, :123-140) and
+    centroids returned in the rotated domain (:1341-1351)."""
+    import superkmeans_b200 as skm
+
+    n, d, k, seed = 24000, 256, 500, 9
+    x = datagen.gaussian_mixture(n, d, k, 0.3, seed)
+    kw = dict(iters=6, sampling_fraction=1.0, early_termination=0, seed=seed, **opts)
+    rk, rc, e, c = _pair(ref, skm, x, k, **kw)
+    rs, es = rk.stats(), e.stats(0)
+    assert any(not r["is_gemm_only"] for r in rs)
+    _check_stats(rs, es, strict=False)
+    ra, a = rk.assignments(), e.assignments()
+    assert (ra == a).mean() >= 0.999
+    assert _rel_l2(c, rc) < 5e-3
+    if opts.get("angular"):
+        norms = np.linalg.norm(e.rotated_centroids(), axis=1)
+        assert np.abs(norms - 1.0).max() < 1e-5
+    asg, rasg = e.assign(x, c), rk.assign(x, rc)
+    assert (asg == rasg).mean() >= 0.999
