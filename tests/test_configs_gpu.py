@@ -75,8 +75,17 @@ def test_config2_shape_matches_reference(ref):
     # (0.11 %) by iteration 5, after which it stays put.  The per-step tests (test_ops_gpu.py) hold each iteration
     # to >= 99.9 % from identical inputs; end to end this configuration is held to 99.8 %.
     assert (ra == a).mean() >= 0.998
-    assert np.linalg.norm(c - rc) / np.linalg.norm(rc) < 5e-3
-    assert (e.assign(x, c) == rk.assign(x, rc)).mean() >= 0.998
+    # ... and a cluster emptied in one run only is re-seeded by the split step, so centroids are compared where the
+    # members are the same
+    same = np.ones(k, dtype=bool)
+    diff = a != ra
+    same[a[diff]] = False
+    same[ra[diff]] = False
+    cr, rcr = e.rotated_centroids(), rk.rotated_centroids()
+    rel = np.linalg.norm(cr[same].astype(np.float64) - rcr[same], axis=1) / (np.linalg.norm(rcr[same], axis=1) + 1e-30)
+    assert same.mean() >= 0.9 and rel.max() < 1e-5, (same.mean(), rel.max())
+    w2, rw2 = _wcss64(x, c, e.assign(x, c)), _wcss64(x, rc, rk.assign(x, rc))
+    assert abs(w2 - rw2) <= 1e-3 * rw2
 
 
 def test_config4_shape_hierarchical_matches_reference(ref):
