@@ -316,7 +316,7 @@ def main():
     # DRAM bytes per launch: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture at n = 400 000 (same d and
     # k; profiles/assignment_kernels_n400k_d1024_k10000.md), per row, times the rows one launch covers here.  Traffic of
     # these kernels grows with the rows (the centroid side stays in L2).  The chain's rows per launch vary: not scaled.
-    dram_per_row = {"gemm_tc_kernel<ARGMIN>": 3.60e9 / 4e5, "gemm_tc_kernel<PRUNE>": 0.377e9 / 4e5, "walk_lists_kernel": 4.92e9 / 4e5}
+    dram_per_row = {"gemm_tc_kernel<ARGMIN>": 3.59e9 / 4e5, "gemm_tc_kernel<PRUNE>": 0.377e9 / 4e5, "walk_lists_kernel": 5.86e9 / 4e5}
     if dom in dram_per_row and dom_calls and (d, k) == (1024, 10000):
         rows_per_launch = n_local * (1 if dom.endswith("<ARGMIN>") else len(d_partial)) * args.steps / dom_calls
         roofline["traffic"] = dram_per_row[dom] * rows_per_launch
