@@ -216,7 +216,7 @@ void Engine::allreduce(void* buf, size_t count, int dtype) {
 
 // dst[n x d] (device) = rotate(src).  Host sources are streamed through two staging buffers so
 // that the copy of chunk i+1 overlaps the rotation of chunk i.
-void Engine::rotate_to_device(const float* src, bool src_on_device, size_t n, float* dst) {
+void Engine::rotate_to_device(const float* src, bool src_on_device, size_t n, float* dst, const std::function<void(size_t, size_t)>& after_rows, size_t piece) {
     if (n == 0) return;
     ensure_rotation();
     if (src_on_device) {
@@ -234,7 +234,7 @@ void Engine::rotate_to_device(const float* src, bool src_on_device, size_t n, fl
         SKM_CUDA(cudaEventCreateWithFlags(&copied[i], cudaEventDisableTiming));
         SKM_CUDA(cudaEventCreateWithFlags(&consumed[i], cudaEventDisableTiming));
     }
-    size_t ci = 0;
+    size_t ci = 0, handed = 0;
     for (size_t r0 = 0; r0 < n; r0 += rows, ++ci) {
         const int b = static_cast<int>(ci & 1);
         const size_t cnt = std::min(rows, n - r0);
@@ -244,6 +244,11 @@ void Engine::rotate_to_device(const float* src, bool src_on_device, size_t n, fl
         SKM_CUDA(cudaStreamWaitEvent(stream_, copied[b], 0));
         launch_gemm_nt(raw[b].get(), d_, m_dev_.get(), d_, dst + r0 * d_, d_, cnt, d_, d_, stream_);
         SKM_CUDA(cudaEventRecord(consumed[b], stream_));
+        const size_t done = r0 + cnt;
+        if (after_rows && (done - handed >= piece || done == n)) {
+            after_rows(handed, done - handed);
+            handed = done;
+        }
     }
     sync();
     for (int i = 0; i < 2; ++i) {
@@ -585,7 +590,12 @@ void Engine::run_iteration(bool gemm_only, const IterationInput& in, size_t iter
     if (gemm_only) {
         launch_row_sqnorms(c_prev_.get(), k_cur, d_, d_, centroid_norms_.get(), stream_);
         PhaseScope ps(*this, PH_ASSIGN_FULL);
-        launch_assign_full(in.x, c_prev_.get(), n, k_cur, d_, norms, centroid_norms_.get(), assignments_.get(), distances_.get(), top2_.ensure(n), stream_, y_split_.ensure(2 * k_cur * d_));
+        if (is_first && first_assign_done_) {
+            first_assign_done_ = false;   // done during the upload (train_flat)
+        } else {
+            launch_assign_full(in.x, c_prev_.get(), n, k_cur, d_, norms, centroid_norms_.get(), assignments_.get(), distances_.get(), top2_.ensure(n), stream_,
+                               y_split_.ensure(2 * k_cur * d_));
+        }
     } else {
         launch_row_sqnorms(c_prev_.get(), k_cur, d_, partial_d_, centroid_norms_.get(), stream_);
         PhaseScope ps(*this, PH_ASSIGN_PRUNED);
@@ -728,6 +738,7 @@ static void gather_host_rows(const float* data, const size_t* idx, size_t cnt, s
 void Engine::train_flat(const float* data, size_t n, bool on_device, const float* queries, size_t n_queries, float* centroids_out) {
     stats_flat_.clear();
     n_queries_ = 0;
+    first_assign_done_ = false;
     const size_t n_global = allreduce_fn_ ? shard_n_global_ : n;
     const size_t n_samples_global = n_vectors_to_sample(n_global, k_, cfg_.sampling_fraction, cfg_.max_points_per_cluster, false);
     if (n_samples_global < k_) {
@@ -783,8 +794,26 @@ void Engine::train_flat(const float* data, size_t n, bool on_device, const float
             }
         }
     } else {
-        if (rotate) rotate_to_device(data, on_device, n_samples_, x_rot_.get());
-        else upload_rows(data, on_device, n_samples_, x_rot_.get());
+        if (rotate && !on_device) {
+            // Host input: the exact assignment of iteration 1 needs nothing but the rotated rows and the initial
+            // centroids, so it runs piece by piece between the uploads instead of after the last one.
+            launch_row_sqnorms(c_prev_.get(), k_, d_, d_, centroid_norms_.get(), stream_);
+            uint2* top2 = top2_.ensure(n_samples_);
+            float* y_split = y_split_.ensure(2 * k_ * d_);
+            rotate_to_device(
+                data, false, n_samples_, x_rot_.get(),
+                [&](size_t r0, size_t cnt) {
+                    launch_row_sqnorms(x_rot_.get() + r0 * d_, cnt, d_, d_, data_norms_.get() + r0, stream_);
+                    launch_assign_full(x_rot_.get() + r0 * d_, c_prev_.get(), cnt, k_, d_, data_norms_.get() + r0, centroid_norms_.get(), assignments_.get() + r0,
+                                       distances_.get() + r0, top2 + r0, stream_, y_split);
+                },
+                static_cast<size_t>(148) * 128 * 14);   // ~14 waves of row tiles per piece
+            first_assign_done_ = true;
+        } else if (rotate) {
+            rotate_to_device(data, on_device, n_samples_, x_rot_.get());
+        } else {
+            upload_rows(data, on_device, n_samples_, x_rot_.get());
+        }
     }
     sync();
 

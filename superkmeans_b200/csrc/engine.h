@@ -6,6 +6,7 @@
 #include <cstdint>
 #include <stdexcept>
 #include <string>
+#include <functional>
 #include <vector>
 
 #include "../../include/skm_b200.h"
@@ -195,7 +196,11 @@ class Engine {
     };
 
     void ensure_rotation();
-    void rotate_to_device(const float* src, bool src_on_device, size_t n, float* dst);
+    // after_rows(r0, cnt), if given, is called (host side, work enqueued on stream_) whenever rows [r0, r0 + cnt) of dst
+    // have been enqueued, in order, in pieces of at least `piece` rows: lets the caller's kernels run between the
+    // copies of a host source instead of after them.
+    void rotate_to_device(const float* src, bool src_on_device, size_t n, float* dst, const std::function<void(size_t, size_t)>& after_rows = nullptr,
+                          size_t piece = 0);
     void upload_rows(const float* src, bool src_on_device, size_t n, float* dst);
     void prepare_update_workspace(size_t n, size_t k);
     void run_iteration(bool gemm_only, const IterationInput& in, size_t iter_idx, bool is_first, std::vector<skm_iter_stats>& target);
@@ -243,6 +248,7 @@ class Engine {
 
     // iteration state
     bool trained_ = false;
+    bool first_assign_done_ = false;   // the exact assignment of iteration 1 already ran, piecewise, during the upload
     size_t n_samples_ = 0;      // rows held locally
     size_t n_split_ = 0;
     float prev_cost_ = 0.f, cost_ = 0.f, shift_ = 0.f;
