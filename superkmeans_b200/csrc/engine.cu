@@ -462,8 +462,8 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
             const uint32_t cap_group = static_cast<uint32_t>(std::max<size_t>(128, g_prune_split_mode == 5 ? p.k / 2 : p.k * 2));
             const size_t tile_bytes = 8 * static_cast<size_t>(cap_group) * sizeof(uint2);
             const size_t n_tiles = (p.n + kTileM - 1) / kTileM;
-            const size_t budget = static_cast<size_t>(6) << 30;
-            const size_t per_batch = std::min(n_tiles, std::max<size_t>(148, budget / tile_bytes));
+            const size_t list_bytes_cap = static_cast<size_t>(6) << 30;
+            const size_t per_batch = std::min(n_tiles, std::max<size_t>(148, list_bytes_cap / tile_bytes));
             uint2* lists = b.tc_lists.ensure(per_batch * 8 * cap_group);
             uint32_t* offs = b.tc_list_offs.ensure(per_batch * 8 * (n_chunks + 1));
             float* y_split = b.y_split.ensure(2 * p.k * p.d);

@@ -2,8 +2,9 @@
 //
 // The first ADSampling test (after d' dimensions) is evaluated for every (point, centroid) pair by the
 // tcgen05 GEMM kernel (first-test epilogue in kernels_tc.cu) against the loosest threshold a point can
-// have, the exact distance to its previous centroid times ratio[d'].  Pairs that pass are written to one
-// list per group of 32 rows, in centroid order, with the list position at every 1024-centroid boundary.
+// have, the exact distance to its previous centroid times ratio[d'].  Pairs that pass are written to eight
+// lists per tile of 128 points (32 rows x the lower or upper 128 columns of every 256-centroid tile), in
+// centroid-tile order, with the list position at every 1024-centroid boundary.
 //
 // walk_lists_kernel then does, for a tile of 128 points and chunk after chunk, what the reference's
 // search does inside one chunk (pdx/pdxearch.h:118-327, distance_computers/batch_computers.h:297-409):
@@ -17,7 +18,8 @@
 //     not change), re-tests after every block and compacts the run in place, so no lane idles behind a pair
 //     that died early and no block-wide barrier is needed between blocks; the runs are evened out twice
 //     on the way (after the second and the sixth block);
-//   * adds the vertical dimensions [d', vertical_d), takes the per-point minimum, lowers `best`.
+//   * adds the vertical dimensions [d', vertical_d), recomputes in fp32 any final distance that comes within
+//     rounding of the tensor-core part of `best`, takes the per-point minimum, lowers `best`.
 // `best` is constant inside a chunk, so pairs are independent and any processing order gives the same
 // result.
 #include <cfloat>
