@@ -171,6 +171,7 @@ __global__ void __launch_bounds__(kWalkThreads, kWalkCtasPerSm) walk_lists_kerne
                 sh.cnt[tid] = 0;
                 sh.prev_flag[tid] = 0;
                 sh.key[tid] = ~0ull;
+                sh.hist[tid] = 0;
             }
 
             // The chunk's pairs of the tile's eight lists, taken as one sequence of `total` positions.
@@ -192,11 +193,7 @@ __global__ void __launch_bounds__(kWalkThreads, kWalkCtasPerSm) walk_lists_kerne
             do {
                 const uint32_t b1 = min(b0 + static_cast<uint32_t>(kWalkBatch), total);
                 const bool last_batch = b1 == total;
-                if (tid < kTileM) {
-                    sh.hist[tid] = 0;
-                    sh.cursor[tid] = 0;
-                }
-                __syncthreads();
+                // (sh.hist is zero here: cleared at the start of the chunk and at the end of every batch)
                 // ---- load, re-test against the current threshold, count; the previous centroid's pair is held back
                 uint2 mine[kWalkPerThread];
                 uint32_t keep = 0;
@@ -252,7 +249,9 @@ __global__ void __launch_bounds__(kWalkThreads, kWalkCtasPerSm) walk_lists_kerne
                     for (int q = 0; q < warp; ++q) base += sh.warp_tot[q];
                     const uint32_t start = base + sh.cursor[tid];
                     sh.hist[tid] = start;
-                    sh.cursor[tid] = 0;
+                    // the held-back pair takes the first slot of its row (nobody reads the list yet)
+                    if (add_prev) sh.list[0][start] = make_uint2(((sh.prev[tid] - static_cast<uint32_t>(c0)) << 7) | tid, __float_as_uint(sh.prev_pd[tid]));
+                    sh.cursor[tid] = add_prev ? 1u : 0u;
                 }
                 __syncthreads();
                 if (tid == 0) sh.m = sh.warp_tot[0] + sh.warp_tot[1] + sh.warp_tot[2] + sh.warp_tot[3];
@@ -262,11 +261,6 @@ __global__ void __launch_bounds__(kWalkThreads, kWalkCtasPerSm) walk_lists_kerne
                         const uint32_t r = mine[u].x & 127u;
                         sh.list[0][sh.hist[r] + atomicAdd(&sh.cursor[r], 1u)] = mine[u];
                     }
-                }
-                __syncthreads();
-                if (add_prev) {
-                    sh.list[0][sh.hist[tid] + sh.cursor[tid]] =
-                        make_uint2(((sh.prev[tid] - static_cast<uint32_t>(c0)) << 7) | tid, __float_as_uint(sh.prev_pd[tid]));
                 }
                 __syncthreads();
 
@@ -363,6 +357,7 @@ __global__ void __launch_bounds__(kWalkThreads, kWalkCtasPerSm) walk_lists_kerne
                         }
                     }
                 }
+                if (tid < kTileM) sh.hist[tid] = 0;
                 __syncthreads();
                 b0 = b1;
             } while (b0 < total);
