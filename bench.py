@@ -314,7 +314,7 @@ def main():
                     "note": "gathered 256-byte centroid blocks, served by L2 rather than HBM (hence a fraction near or above 1); bytes = 256 B per (pair, 64-dimension block) step, counted by the kernel"}
     roofline["kernels_ms_per_train"] = {c[0]: round(c[1] / args.steps, 3) for c in cands}
     # DRAM bytes per launch: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture at n = 400 000 (same d and
-    # k; profiles/assignment_kernels_n400k_d1024_k10000.md), per row, times the rows one launch covers here.  Traffic of
+    # k), per row, times the rows one launch covers here.  Traffic of
     # these kernels grows with the rows (the centroid side stays in L2).  The chain's rows per launch vary: not scaled.
     dram_per_row = {"gemm_tc_kernel<ARGMIN>": 3.59e9 / 4e5, "gemm_tc_kernel<PRUNE>": 0.377e9 / 4e5, "walk_lists_kernel": 5.86e9 / 4e5}
     if dom in dram_per_row and dom_calls and (d, k) == (1024, 10000):

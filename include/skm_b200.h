@@ -123,12 +123,17 @@ int skm_is_trained(const skm_handle* h);
 float skm_sampling_fraction(const skm_handle* h);
 uint64_t skm_n_mesoclusters(const skm_handle* h);
 
+/* How many rows the training state covers: n_samples of Train (superkmeans.h:184, :1269-1277; the reference fills
+ * assignments[0 .. n_samples) and distances[0 .. n_samples), :202-207), or n after an AssignTrainingPoints over all
+ * rows of a model trained with sampling_fraction = 1.  0 before training. */
+uint64_t skm_get_n_samples(const skm_handle* h);
+
 /* iteration_stats / hierarchical_iteration_stats.  Writes at most `cap` entries; *count receives
  * the number available. */
 skm_status skm_get_iteration_stats(const skm_handle* h, int phase, skm_iter_stats* out, uint64_t cap, uint64_t* count);
 
 /* Public member `assignments` (superkmeans.h:1491) and GetDistancesPointer (:576): state left by
- * the last training pass, n entries each, copied to host. */
+ * the last training pass, n <= skm_get_n_samples(h) entries each, copied to host. */
 skm_status skm_get_assignments(skm_handle* h, uint32_t* out, uint64_t n);
 skm_status skm_get_distances(skm_handle* h, float* out, uint64_t n);
 /* horizontal_centroids after training: rotated-space centroids, n_clusters x d. */
@@ -176,8 +181,19 @@ int skm_get_tensor_cores(void);
  * for testing each kernel on its own.  No counterpart in the reference. */
 void skm_set_prune_split(int mode);
 int skm_get_prune_split(void);
+/* Test hook for the failure path of the tensor-core kernels (current device).  Every wait inside those kernels is
+ * bounded: when it runs out the kernel records a code, all of its roles leave their loops, tensor memory is released
+ * and the kernel returns; the call that launched it then reports SKM_CUDA_ERROR and the context stays usable.  This
+ * hook shortens the limit to wait_limit_cycles SM cycles (0 = back to the default of about two seconds) and makes the
+ * TMA producer of the exact-assignment kernel stop after producer_stops_after_kblocks k-blocks (0 = never), so that
+ * a test can watch that path without a fault or a hang.  No counterpart in the reference. */
+skm_status skm_debug_wait_injection(uint64_t wait_limit_cycles, uint32_t producer_stops_after_kblocks);
+
 /* Kernels launched by this library in the calling process so far. */
 uint64_t skm_kernel_launches(void);
+/* Device and pinned-host allocations (cudaMalloc, cudaMallocHost) made by this library in the calling process so
+ * far.  Lets a caller check that a code path allocates nothing.  No counterpart in the reference. */
+uint64_t skm_device_allocations(void);
 
 /* Sharded training: this handle holds rows [row_offset, row_offset + n_local) of a global data set
  * of n_global rows; per-iteration sums, counts and scalars are combined through `fn`.  The

@@ -5,6 +5,7 @@
 // libskm_b200.so.  Inputs are row-major float32 host arrays, exactly as in the reference.
 #pragma once
 
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -229,11 +230,14 @@ class SuperKMeans {
         iteration_stats = detail::fetch_stats(handle.get(), SKM_STATS_FLAT);
         assignments.reset(new uint32_t[n]);
         distances.reset(new distance_t[n]);
-        // The engine keeps one entry per training row (n_samples <= n); the rest stays unspecified, as in
-        // the reference where the buffers are allocated with n entries and filled up to n_samples.
-        uint64_t held = n;
-        while (held > 0 && skm_get_assignments(handle.get(), assignments.get(), held) != SKM_OK) held /= 2;
-        if (held) skm_get_distances(handle.get(), distances.get(), held);
+        // The engine holds one entry per training row: n_samples <= n of them (superkmeans.h:184, :1269-1277).
+        // The buffers have n entries and are filled up to n_samples, as in the reference (:202-207).
+        const uint64_t held = std::min<uint64_t>(skm_get_n_samples(handle.get()), n);
+        if (held) {
+            skm_status st = skm_get_assignments(handle.get(), assignments.get(), held);
+            if (st == SKM_OK) st = skm_get_distances(handle.get(), distances.get(), held);
+            if (st != SKM_OK) detail::raise(st, handle.get());
+        }
     }
 
     const size_t d;

@@ -81,6 +81,7 @@ SIGNATURES = {
     "skm_is_trained": (C.c_int, [C.c_void_p]),
     "skm_sampling_fraction": (C.c_float, [C.c_void_p]),
     "skm_n_mesoclusters": (C.c_uint64, [C.c_void_p]),
+    "skm_get_n_samples": (C.c_uint64, [C.c_void_p]),
     "skm_get_iteration_stats": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(IterStats), C.c_uint64, C.POINTER(C.c_uint64)]),
     "skm_get_assignments": (C.c_int, [C.c_void_p, u32p, C.c_uint64]),
     "skm_get_distances": (C.c_int, [C.c_void_p, f32p, C.c_uint64]),
@@ -94,7 +95,9 @@ SIGNATURES = {
                                 C.c_void_p, C.c_void_p]),
     "skm_get_phase_time": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
     "skm_reset_phase_times": (C.c_int, [C.c_void_p]),
+    "skm_debug_wait_injection": (C.c_int, [C.c_uint64, C.c_uint32]),
     "skm_kernel_launches": (C.c_uint64, []),
+    "skm_device_allocations": (C.c_uint64, []),
     "skm_set_prune_split": (None, [C.c_int]),
     "skm_get_prune_split": (C.c_int, []),
     "skm_set_tensor_cores": (None, [C.c_int]),

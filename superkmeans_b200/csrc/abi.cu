@@ -138,6 +138,7 @@ uint64_t skm_n_clusters(const skm_handle* h) { return (h && h->engine) ? h->engi
 int skm_is_trained(const skm_handle* h) { return (h && h->engine) ? (h->engine->trained() ? 1 : 0) : 0; }
 float skm_sampling_fraction(const skm_handle* h) { return (h && h->engine) ? h->engine->sampling_fraction() : 0.f; }
 uint64_t skm_n_mesoclusters(const skm_handle* h) { return (h && h->engine) ? h->engine->n_mesoclusters_value() : 0; }
+uint64_t skm_get_n_samples(const skm_handle* h) { return (h && h->engine) ? h->engine->n_state_rows() : 0; }
 int skm_last_prune_path(const skm_handle* h) { return (h && h->engine) ? h->engine->last_prune_path() : 0; }
 
 skm_status skm_get_prune_counters(const skm_handle* h, uint64_t* out3) {
@@ -216,7 +217,13 @@ int skm_get_tensor_cores(void) { return skmb::tc::enabled() ? 1 : 0; }
 void skm_set_prune_split(int mode) { skmb::set_prune_split_mode(mode); }
 int skm_get_prune_split(void) { return skmb::prune_split_mode(); }
 
+skm_status skm_debug_wait_injection(uint64_t wait_limit_cycles, uint32_t producer_stops_after_kblocks) {
+    g_create_error.clear();
+    return guarded(g_op_error, [&] { skmb::tc::set_debug_wait_injection(static_cast<long long>(wait_limit_cycles), producer_stops_after_kblocks); });
+}
+
 uint64_t skm_kernel_launches(void) { return skmb::kernel_launch_count(); }
+uint64_t skm_device_allocations(void) { return skmb::device_alloc_count(); }
 
 skm_status skm_set_shard(skm_handle* h, uint64_t n_global, uint64_t row_offset, skm_allreduce_fn fn, void* user) {
     SKM_NEED(h);

@@ -24,6 +24,10 @@ inline void cuda_check(cudaError_t e, const char* what, const char* file, int li
 
 unsigned long long kernel_launch_count();
 void note_kernel_launch();
+// Device and pinned-host allocations made by this library in the calling process so far (every cudaMalloc /
+// cudaMallocHost goes through DeviceBuffer, PinnedBuffer or a site that calls note_device_alloc).
+unsigned long long device_alloc_count();
+void note_device_alloc();
 // After every kernel launch: count it and surface launch-configuration errors.
 #define SKM_LAUNCH_CHECK()                                                                         \
     do {                                                                                           \
@@ -137,6 +141,7 @@ struct WalkParams {
     uint32_t* redo_count;
     unsigned long long* pair_steps;            // += pairs advanced by one 64-dimension block
     uint32_t rebalance_mask = 0x22;            // bit b: even the runs out after block b (here: after the 2nd and the 6th)
+    const int* upstream_error = nullptr;       // set when the kernel that wrote the lists gave up on a wait: the lists are then not read
 };
 void launch_walk_lists(const WalkParams& w, int device, cudaStream_t stream);
 // hard_idx / *n_hard_dev from an arbitrary flag array (same buffers as launch_pruned_prepare fills)

@@ -47,6 +47,12 @@ void check_tc_error(cudaStream_t stream) {
     if (code != 0) throw CudaError("a tensor-core kernel gave up waiting on a barrier (code " + std::to_string(code) + ")");
 }
 
+int sm_count_of(int device) {
+    int sms = 0;
+    SKM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    return std::max(sms, 1);
+}
+
 int resolve_device(int device) {
     if (device >= 0) return device;
     int cur = 0;
@@ -463,7 +469,8 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
             const size_t tile_bytes = 8 * static_cast<size_t>(cap_group) * sizeof(uint2);
             const size_t n_tiles = (p.n + kTileM - 1) / kTileM;
             const size_t list_bytes_cap = static_cast<size_t>(6) << 30;
-            const size_t per_batch = std::min(n_tiles, std::max<size_t>(148, list_bytes_cap / tile_bytes));
+            // at least one tile per batch; when even one tile's lists exceed the cap (k in the millions) the batch is that one tile
+            const size_t per_batch = std::min(n_tiles, std::max<size_t>(1, list_bytes_cap / tile_bytes));
             uint2* lists = b.tc_lists.ensure(per_batch * 8 * cap_group);
             uint32_t* offs = b.tc_list_offs.ensure(per_batch * 8 * (n_chunks + 1));
             float* y_split = b.y_split.ensure(2 * p.k * p.d);
@@ -500,6 +507,7 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
                 w.redo = redo;
                 w.redo_count = redo_count;
                 w.pair_steps = pair_steps;
+                w.upstream_error = tc::error_word();
                 Sub sub(timers, PH_PRUNE_WALK, stream);
                 launch_walk_lists(w, device, stream);
             }
@@ -807,7 +815,7 @@ void Engine::train_flat(const float* data, size_t n, bool on_device, const float
                     launch_assign_full(x_rot_.get() + r0 * d_, c_prev_.get(), cnt, k_, d_, data_norms_.get() + r0, centroid_norms_.get(), assignments_.get() + r0,
                                        distances_.get() + r0, top2 + r0, stream_, y_split);
                 },
-                static_cast<size_t>(148) * 128 * 14);   // ~14 waves of row tiles per piece
+                static_cast<size_t>(sm_count_of(device_)) * kTileM * 14);   // ~14 waves of row tiles (one per SM) per piece
             first_assign_done_ = true;
         } else if (rotate) {
             rotate_to_device(data, on_device, n_samples_, x_rot_.get());
@@ -841,6 +849,7 @@ void Engine::train_flat(const float* data, size_t n, bool on_device, const float
     }
     queries_rot_.release();
     topk_dots_.release();
+    n_state_rows_ = n_samples_;
     trained_ = true;
     output_centroids(centroids_out);
     check_tc_error(stream_);
@@ -1087,6 +1096,7 @@ void Engine::train_hierarchical(const float* data, size_t n, bool on_device, flo
         }
     }
     sync();
+    n_state_rows_ = n_all;
     trained_ = true;
     output_centroids(centroids_out);
     x_rot_.release();
@@ -1228,6 +1238,7 @@ void Engine::assign_training_points(const float* vectors, const float* centroids
     if (store_state) {
         assignments_.ensure(n);
         distances_.ensure(n);
+        n_state_rows_ = n;
     }
     const size_t rows = chunk_rows_for(d_, n);
     DeviceBuffer<float> xr, xn, dist;
@@ -1255,13 +1266,13 @@ void Engine::assign_training_points(const float* vectors, const float* centroids
 
 void Engine::get_assignments(uint32_t* out, size_t n) {
     DeviceGuard guard(device_);
-    if (n > assignments_.capacity()) throw std::invalid_argument("more assignments requested than the engine holds");
+    if (n > n_state_rows_ || n > assignments_.capacity()) throw std::invalid_argument("more assignments requested than the engine holds");
     SKM_CUDA(cudaMemcpy(out, assignments_.get(), sizeof(uint32_t) * n, cudaMemcpyDeviceToHost));
 }
 
 void Engine::get_distances(float* out, size_t n) {
     DeviceGuard guard(device_);
-    if (n > distances_.capacity()) throw std::invalid_argument("more distances requested than the engine holds");
+    if (n > n_state_rows_ || n > distances_.capacity()) throw std::invalid_argument("more distances requested than the engine holds");
     SKM_CUDA(cudaMemcpy(out, distances_.get(), sizeof(float) * n, cudaMemcpyDeviceToHost));
 }
 

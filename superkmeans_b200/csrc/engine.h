@@ -31,6 +31,7 @@ class DeviceBuffer {
     T* ensure(size_t count) {
         if (count > cap_) {
             release();
+            note_device_alloc();
             SKM_CUDA(cudaMalloc(&p_, sizeof(T) * (count ? count : 1)));
             cap_ = count;
         }
@@ -63,6 +64,7 @@ class PinnedBuffer {
     T* ensure(size_t count) {
         if (count > cap_) {
             release();
+            note_device_alloc();
             SKM_CUDA(cudaMallocHost(&p_, sizeof(T) * (count ? count : 1)));
             cap_ = count;
         }
@@ -155,6 +157,8 @@ class Engine {
     bool trained() const { return trained_; }
     float sampling_fraction() const { return cfg_.sampling_fraction; }
     size_t n_mesoclusters_value() const { return n_meso_; }
+    // rows whose assignment and distance the last training pass left behind (n_samples of Train; n after a full AssignTrainingPoints)
+    size_t n_state_rows() const { return n_state_rows_; }
     double last_objective_f64() const { return last_cost_f64_; }
     int last_prune_path() const { return prune_bufs_.last_path; }
     void prune_counters(uint64_t out[3]) const {
@@ -250,6 +254,7 @@ class Engine {
     bool trained_ = false;
     bool first_assign_done_ = false;   // the exact assignment of iteration 1 already ran, piecewise, during the upload
     size_t n_samples_ = 0;      // rows held locally
+    size_t n_state_rows_ = 0;   // valid entries of assignments_ / distances_
     size_t n_split_ = 0;
     float prev_cost_ = 0.f, cost_ = 0.f, shift_ = 0.f;
     double last_cost_f64_ = 0.0;

@@ -20,6 +20,9 @@ namespace skmb {
 static std::atomic<unsigned long long> g_kernel_launches{0};
 unsigned long long kernel_launch_count() { return g_kernel_launches.load(); }
 void note_kernel_launch() { g_kernel_launches.fetch_add(1, std::memory_order_relaxed); }
+static std::atomic<unsigned long long> g_device_allocs{0};
+unsigned long long device_alloc_count() { return g_device_allocs.load(std::memory_order_relaxed); }
+void note_device_alloc() { g_device_allocs.fetch_add(1, std::memory_order_relaxed); }
 
 // =================================================================================================
 // Row squared norms over the first `upto` columns: one warp per row.

@@ -51,6 +51,10 @@ constexpr uint32_t STAGE_ENTRIES = 256;   // per epilogue warp, first-test epilo
 constexpr uint32_t SMEM_STAGE_BYTES = 8 * STAGE_ENTRIES * 8;
 constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + SMEM_STAGE_BYTES + 1024;  // + alignment slack
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
+// Limit of every bounded wait, in SM clock cycles.  A variable rather than a constant so that a test can shorten it
+// (set_debug_wait_injection) and watch a wait run out in milliseconds instead of seconds.
+__device__ long long g_wait_limit_cycles = WAIT_LIMIT_CYCLES;
+__device__ __forceinline__ long long wait_limit_cycles() { return *reinterpret_cast<volatile long long*>(&g_wait_limit_cycles); }
 
 // kind::tf32, fp32 accumulate, K-major A and B, N = 256, M = 128
 constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
@@ -92,15 +96,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait.  Returns false (after recording `code`) when the limit expires or another role has
-// already failed.
+// Bounded wait.  Returns false (after recording `code`) when the limit expires, and also as soon as another role
+// has recorded a failure: once one role has given up the others would only run out their own limits.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
+    uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-            atomicCAS(err, 0, code);
-            return false;
+        if ((++spins & 1023u) == 0) {
+            if (*reinterpret_cast<volatile int*>(err) != 0) return false;
+            if (clock64() - t0 > wait_limit_cycles()) {
+                atomicCAS(err, 0, code);
+                return false;
+            }
         }
     }
     return true;
@@ -212,6 +220,9 @@ struct Params {
     // Y arrives already split: tmap_y covers the hi parts, tmap_ylo the lo parts, and the splitter warps
     // only treat X
     bool y_presplit;
+    // test hook: when non-zero the producer stops after this many k-blocks, so that the roles behind it wait for
+    // data that never arrives, run into the wait limit and the kernel returns with an error code
+    uint32_t debug_producer_stop;
 };
 
 enum { MODE_ARGMIN = 0, MODE_STORE = 1, MODE_PRUNE = 2 };
@@ -260,6 +271,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                 for (uint32_t nt = 0; nt < n_col_tiles && ok; ++nt) {
                     for (uint32_t kb = 0; kb < nkb; ++kb, ++kbt) {
                         const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
+                        if (p.debug_producer_stop != 0 && kbt >= p.debug_producer_stop) {
+                            ok = false;
+                            break;
+                        }
                         if (!mbar_wait(&ctrl->empty[s], ph ^ 1u, p.error, 1)) {
                             ok = false;
                             break;
@@ -1037,14 +1052,18 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
 
 // After the chain: the exact squared distance (direct differences, fp32) of a point to the chain's
 // winner and to the two runner-ups; the smallest wins, the winner keeps its place on ties.
-__global__ void __launch_bounds__(256) refine_chain_kernel(const float* __restrict__ x, const float* __restrict__ y, size_t n, size_t d, const uint2* __restrict__ top2,
-                                                           uint32_t* __restrict__ knn, float* __restrict__ dist) {
+__global__ void __launch_bounds__(256) refine_chain_kernel(const float* __restrict__ x, const float* __restrict__ y, size_t n, size_t k, size_t d,
+                                                           const uint2* __restrict__ top2, uint32_t* __restrict__ knn, float* __restrict__ dist,
+                                                           const int* __restrict__ error) {
     const size_t row = static_cast<size_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
     if (row >= n) return;
+    // a chain kernel that gave up on a wait leaves its outputs unwritten: nothing to refine, and no index to trust
+    if (*reinterpret_cast<const volatile int*>(error) != 0) return;
     const int lane = threadIdx.x & 31;
     const uint32_t w = knn[row];
     const uint2 t = top2[row];
-    uint32_t cand[3] = {w, t.x, t.y};
+    if (w >= k) return;
+    uint32_t cand[3] = {w, t.x < k ? t.x : 0xFFFFFFFFu, t.y < k ? t.y : 0xFFFFFFFFu};
     if (cand[1] == 0xFFFFFFFFu || cand[1] == w) cand[1] = w;
     if (cand[2] == 0xFFFFFFFFu || cand[2] == w) cand[2] = w;
     const float* xr = x + row * d;
@@ -1088,14 +1107,17 @@ __global__ void __launch_bounds__(256) refine_chain_kernel(const float* __restri
 // candidates with fp32 fused multiply-adds, keeps the smaller (the lower index on a tie) and stores
 // the distance clamped at zero, as the reference does (batch_computers.h:160-166).
 __global__ void __launch_bounds__(256) refine_top2_kernel(
-    const float* __restrict__ x, const float* __restrict__ y, size_t n, size_t d, const float* __restrict__ norms_x, const float* __restrict__ norms_y,
-    const uint2* __restrict__ top2, uint32_t* __restrict__ out_knn, float* __restrict__ out_dist
+    const float* __restrict__ x, const float* __restrict__ y, size_t n, size_t k, size_t d, const float* __restrict__ norms_x, const float* __restrict__ norms_y,
+    const uint2* __restrict__ top2, uint32_t* __restrict__ out_knn, float* __restrict__ out_dist, const int* __restrict__ error
 ) {
     const size_t row = static_cast<size_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
     if (row >= n) return;
+    // a tensor-core pass that gave up on a wait leaves the candidate pairs unwritten
+    if (*reinterpret_cast<const volatile int*>(error) != 0) return;
     const int lane = threadIdx.x & 31;
     const uint2 cand = top2[row];
-    const bool two = cand.y != 0xFFFFFFFFu;
+    if (cand.x >= k) return;
+    const bool two = cand.y < k;
     const float* xr = x + row * d;
     const float* y1 = y + static_cast<size_t>(cand.x) * d;
     const float* y2 = y + static_cast<size_t>(two ? cand.y : cand.x) * d;
@@ -1201,6 +1223,7 @@ int* error_flag(int device) {
     static int* flags[64] = {nullptr};
     std::lock_guard<std::mutex> lock(mu);
     if (!flags[device]) {
+        note_device_alloc();
         SKM_CUDA(cudaMalloc(&flags[device], sizeof(int)));
         SKM_CUDA(cudaMemset(flags[device], 0, sizeof(int)));
     }
@@ -1226,10 +1249,23 @@ void launch(const CUtensorMap& tx, const CUtensorMap& ty, const CUtensorMap& tyl
 }
 
 bool g_enabled = true;
+uint32_t g_debug_producer_stop = 0;
 
 } // namespace
 
+void set_debug_wait_injection(long long wait_limit_cycles, uint32_t producer_stops_after_kblocks) {
+    const long long v = wait_limit_cycles > 0 ? wait_limit_cycles : WAIT_LIMIT_CYCLES;
+    SKM_CUDA(cudaMemcpyToSymbol(g_wait_limit_cycles, &v, sizeof(v)));
+    g_debug_producer_stop = producer_stops_after_kblocks;
+}
+
 void launch_presplit(const float* y, size_t rows, size_t ld, float* y_split, cudaStream_t stream) { presplit(y, rows, ld, y_split, stream); }
+
+int* error_word() {
+    int device = 0;
+    SKM_CUDA(cudaGetDevice(&device));
+    return error_flag(device);
+}
 
 void set_enabled(bool on) { g_enabled = on; }
 bool enabled() { return g_enabled; }
@@ -1261,8 +1297,9 @@ void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size
     p.out_dist = out_dist;
     p.out_top2 = top2_scratch;
     p.error = error_flag(device);
+    p.debug_producer_stop = g_debug_producer_stop;
     launch<MODE_ARGMIN>(tx, ty, tylo, p, stream);
-    refine_top2_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, d, norms_x, norms_y, top2_scratch, out_knn, out_dist);
+    refine_top2_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, k, d, norms_x, norms_y, top2_scratch, out_knn, out_dist, p.error);
     note_kernel_launch();
     SKM_CUDA(cudaGetLastError());
 }
@@ -1283,7 +1320,7 @@ void launch_assign_full_flagged(const float* x, const float* y, size_t n, size_t
     p.out_top2 = top2_scratch;
     p.error = error_word;
     launch<MODE_ARGMIN>(tx, ty, ty, p, stream);
-    refine_top2_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, d, norms_x, norms_y, top2_scratch, out_knn, out_dist);
+    refine_top2_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, k, d, norms_x, norms_y, top2_scratch, out_knn, out_dist, p.error);
     note_kernel_launch();
     SKM_CUDA(cudaGetLastError());
 }
@@ -1374,7 +1411,7 @@ void launch_chain(const float* x, const float* y, size_t n, size_t k, size_t d, 
     chain_tc_kernel<<<grid, CHAIN_THREADS, C_SMEM_BYTES, stream>>>(maps, p);
     note_kernel_launch();
     SKM_CUDA(cudaGetLastError());
-    refine_chain_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, d, top2_scratch, knn, dist);
+    refine_chain_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, k, d, top2_scratch, knn, dist, p.error);
     note_kernel_launch();
     SKM_CUDA(cudaGetLastError());
 }

@@ -49,6 +49,16 @@ void launch_chain(const float* x, const float* y, size_t n, size_t k, size_t d, 
                   const float* chain_norms_y, const float* ratios, const float* best_in, uint32_t* knn, float* dist, uint32_t* not_pruned, uint2* top2_scratch,
                   float* y_split, cudaStream_t stream);   // y_split: 2 * k * d floats of scratch for the tf32 parts of the centroids
 
+// Test hook for the bounded waits, current device: every wait of the tensor-core kernels gives up after
+// wait_limit_cycles SM cycles (0 restores the default of about two seconds), and the TMA producer of the exact
+// assignment kernel stops after producer_stops_after_kblocks k-blocks (0 = never), so that the other roles wait
+// for tiles that never arrive.  The kernel then returns with an error code that fetch_error reports.
+void set_debug_wait_injection(long long wait_limit_cycles, uint32_t producer_stops_after_kblocks);
+
+// The per-device word (device memory) in which a tensor-core kernel records that one of its waits ran out; kernels that
+// consume such a kernel's output read it first and do nothing when it is set.
+int* error_word();
+
 // Error code (0 = none) recorded by a kernel whose bounded wait expired; clears it.  Synchronises.
 int fetch_error(cudaStream_t stream);
 

@@ -130,6 +130,7 @@ constexpr int kWalkCtasPerSm = 4;
 
 __global__ void __launch_bounds__(kWalkThreads, kWalkCtasPerSm) walk_lists_kernel(const WalkParams w) {
     __shared__ WalkShared sh;
+    if (w.upstream_error && *reinterpret_cast<const volatile int*>(w.upstream_error) != 0) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = tid >> 3, gl = tid & 7;
     const uint32_t gmask = 0xFFu << (lane & 24);

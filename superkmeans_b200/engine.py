@@ -189,14 +189,19 @@ class Engine:
         check(lib.skm_get_iteration_stats(self._h, phase, buf, cnt.value, C.byref(cnt)), self._h)
         return list(buf[: int(cnt.value)])
 
+    @property
+    def n_samples(self) -> int:
+        """Rows covered by assignments() / distances(): the sampled rows of Train, or all rows after assign_training_points."""
+        return int(lib.skm_get_n_samples(self._h))
+
     def assignments(self, n: Optional[int] = None) -> np.ndarray:
-        n = self.n_trained if n is None else n
+        n = self.n_samples if n is None else n
         out = np.empty(n, dtype=np.uint32)
         check(lib.skm_get_assignments(self._h, out, n), self._h)
         return out
 
     def distances(self, n: Optional[int] = None) -> np.ndarray:
-        n = self.n_trained if n is None else n
+        n = self.n_samples if n is None else n
         out = np.empty(n, dtype=np.float32)
         check(lib.skm_get_distances(self._h, out, n), self._h)
         return out
@@ -223,6 +228,11 @@ def set_prune_split(mode: int) -> None:
 
 def kernel_launches() -> int:
     return int(lib.skm_kernel_launches())
+
+
+def device_allocations() -> int:
+    """cudaMalloc / cudaMallocHost calls made by the library in this process so far."""
+    return int(lib.skm_device_allocations())
 
 
 # ---- stateless operators (host arrays in, host arrays out) ------------------------------------

@@ -3,6 +3,7 @@
 // Prints one line per check; exit code 0 when all pass.  With argument "gpu" it also trains.
 #include <cstdio>
 #include <cstring>
+#include <string>
 #include <random>
 #include <vector>
 
@@ -82,6 +83,26 @@ int main(int argc, char** argv) {
     {
         skmeans::SuperKMeans<> small(100, d, cfg);
         CHECK(throws<std::runtime_error>([&] { small.Train(data.data(), 50); }));
+    }
+    {
+        // Default sampling (sampling_fraction 0.3): assignments / distances are filled for the n_samples training rows
+        // (superkmeans.h:202-207) and agree with what the engine holds.
+        skmeans::SuperKMeansConfig sc;
+        sc.iters = 4;
+        sc.early_termination = false;
+        skmeans::SuperKMeans<> sk(k, d, sc);
+        (void) sk.Train(data.data(), n);
+        const uint64_t held = skm_get_n_samples(sk.Handle());
+        CHECK(held == 1800);   // floor(6000 * 0.3), below k * max_points_per_cluster
+        std::vector<uint32_t> own(held);
+        std::vector<float> own_d(held);
+        CHECK(skm_get_assignments(sk.Handle(), own.data(), held) == SKM_OK);
+        CHECK(skm_get_distances(sk.Handle(), own_d.data(), held) == SKM_OK);
+        size_t eq = 0;
+        for (uint64_t i = 0; i < held; ++i) eq += (own[i] == sk.assignments[i] && own[i] < k && own_d[i] == sk.GetDistancesPointer()[i]);
+        CHECK(eq == held);
+        CHECK(skm_get_assignments(sk.Handle(), own.data(), held + 1) == SKM_INVALID_ARGUMENT);
+        CHECK(std::string(skm_last_error(sk.Handle())).find("more assignments") != std::string::npos);
     }
     skmeans::HierarchicalSuperKMeansConfig hc;
     hc.suppress_warnings = true;

@@ -1,0 +1,89 @@
+"""Helpers shared by the parity tests: classification of the points on which two implementations of the pruned
+search (BatchComputer::FindNearestNeighborWithPruning, batch_computers.h:297-409) disagree.
+
+Both implementations run the same approximate search: a candidate is dropped as soon as its partial distance over the
+dimensions seen so far is not below best * ratio[dimensions seen] (pdx/pdxearch.h:67-80).  Two fp32 evaluations of
+that search can legitimately differ on a point in exactly two ways:
+  * near-tie: the two answers are equally good (float64 distances within 1e-5 relative);
+  * threshold flip: the better answer sat within fp32 rounding of one of its thresholds, so one side dropped it
+    (an ADSampling false prune) and the other kept it.
+Everything else would be a bug.  `classify_disagreements` replays the search of the affected points in float64 and
+returns the points that fit neither case."""
+from __future__ import annotations
+
+import numpy as np
+
+CHUNK = 1024     # VECTOR_CHUNK_SIZE (common.h:89-115)
+HBLOCK = 64      # H_DIM_SIZE
+
+
+def _checkpoints(d, partial_d, vertical_d):
+    """[(dims of the segment, ratio index after it)] in the order of PDXearch::Prune (pdxearch.h:149-216)."""
+    segs = [(np.arange(0, partial_d), partial_d)]
+    seen = partial_d
+    for h0 in range(vertical_d, d, HBLOCK):
+        seen += HBLOCK
+        segs.append((np.arange(h0, min(h0 + HBLOCK, d)), seen))
+    if partial_d < vertical_d:
+        segs.append((np.arange(partial_d, vertical_d), d))
+    return segs
+
+
+def classify_disagreements(x, y, prev, a, b, partial_d, vertical_d, ratios, tie_rel=1e-5, thr_tol=2e-5, margins=None):
+    """x [n][d] rotated points, y [k][d] rotated centroids, prev the assignment the pass started from, a / b the two
+    answers.  Returns (n_near_ties, n_threshold_flips, unexplained indices).
+
+    thr_tol: how close (relative to ||x||^2 + ||c||^2 over the dimensions seen) a partial distance must have been to
+    its threshold for a flip to count as rounding; the tensor-core accumulator is accurate to about 1e-5 of that scale."""
+    idx = np.nonzero(a != b)[0]
+    n_tie = n_flip = 0
+    bad = []
+    d = x.shape[1]
+    segs = _checkpoints(d, partial_d, vertical_d)
+    r = np.asarray(ratios, dtype=np.float64)
+    y64 = None
+    for i in idx:
+        xi = x[i].astype(np.float64)
+        da = float(((xi - y[a[i]].astype(np.float64)) ** 2).sum())
+        db = float(((xi - y[b[i]].astype(np.float64)) ** 2).sum())
+        if abs(da - db) <= tie_rel * max(min(da, db), 1e-30):
+            n_tie += 1
+            continue
+        w = int(a[i]) if da < db else int(b[i])   # the better answer: the other side must have dropped it
+        if w == int(prev[i]):
+            # the previous centroid is never dropped (its distance is the threshold): preferring a worse centroid to
+            # it cannot come from a threshold
+            bad.append(int(i))
+            continue
+        if y64 is None:
+            y64 = y.astype(np.float64)
+        # float64 replay of the chunks before w's chunk gives the running best that w was tested against
+        best = float(((xi - y64[prev[i]]) ** 2).sum())
+        wc = w // CHUNK
+        closest = np.inf
+        for c in range(wc + 1):
+            lo, hi = c * CHUNK, min((c + 1) * CHUNK, y.shape[0])
+            diff2 = (xi[None, :] - y64[lo:hi]) ** 2
+            alive = np.ones(hi - lo, dtype=bool)
+            pd = np.zeros(hi - lo)
+            n_first = 0
+            for s, (dims, seen) in enumerate(segs):
+                pd = pd + diff2[:, dims].sum(1)
+                thr = best * r[seen]
+                if c == wc:
+                    cols = np.concatenate([sg[0] for sg in segs[: s + 1]])
+                    scale = float((xi[cols] ** 2).sum() + (y64[w, cols] ** 2).sum())
+                    closest = min(closest, abs(pd[w - lo] - thr) / max(scale, 1e-30))
+                alive &= pd < thr
+                if s == 0:
+                    n_first = int(alive.sum())
+                    prev_only = n_first == 1 and lo <= prev[i] < hi and alive[prev[i] - lo]
+            if c < wc and alive.any() and not prev_only:
+                best = float(pd[alive].min())
+        if margins is not None:
+            margins.append(closest)
+        if closest <= thr_tol:
+            n_flip += 1
+        else:
+            bad.append(int(i))
+    return n_tie, n_flip, bad

@@ -9,7 +9,7 @@ Floating-point bars (fp32 arithmetic on both sides, different summation order):
 import numpy as np
 import pytest
 
-from tests import datagen
+from tests import datagen, parity_util
 
 pytestmark = pytest.mark.gpu
 
@@ -144,8 +144,12 @@ def _pruned_step_check(eng, ref, n, d, k, count_tol=1e-3):
         knn, dist, npc = eng.find_nearest_pruned(xr, prev.centroids, prev.assign, pd)
         agree = float((knn == rknn).mean())
         assert agree >= 0.999, (t, agree)
-        ok, _ = _near_tie_ok(xr, prev.centroids, knn.astype(np.int64), rknn.astype(np.int64), rel=1e-5)
-        # disagreements are near-ties or ADSampling false prunes flipped by rounding at a threshold
+        # every disagreement is a near-tie (1e-5 relative) or an ADSampling false prune that rounding flipped at a
+        # threshold (pdx/pdxearch.h:67-80); a float64 replay of the affected points must explain all of them
+        hd, vd = eng.dimension_split(d)
+        n_tie, n_flip, unexplained = parity_util.classify_disagreements(xr, prev.centroids, prev.assign.astype(np.int64), knn.astype(np.int64), rknn.astype(np.int64), pd, vd,
+                                                                        eng.ratios(d, 1.5))
+        assert not unexplained, (t, n_tie, n_flip, unexplained[:8])
         same = knn == rknn
         assert np.abs(dist[same] - rdist[same]).max() <= 2e-5 * max(1.0, float(rdist.max()))
         # not-pruned counters: integer, but each counts threshold tests on rounded partial distances

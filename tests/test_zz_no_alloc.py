@@ -23,8 +23,21 @@ def _run_noalloc(skm, torch, x, y):
     knn = torch.full((n,), 0x7FFFFFFF, dtype=torch.int32, device="cuda")
     dist = torch.full((n,), -1.0, dtype=torch.float32, device="cuda")
     torch.cuda.synchronize()
+    # The reason the entry point exists: the library itself must not allocate on this call, neither on the first one
+    # for a device nor on any later one (the counter covers every cudaMalloc / cudaMallocHost the library makes).
+    before = skm.engine.device_allocations()
     skm.engine.find_nearest_noalloc(xd.data_ptr(), yd.data_ptr(), n, y.shape[0], d, knn.data_ptr(), dist.data_ptr(), device=torch.cuda.current_device())
+    assert skm.engine.device_allocations() == before
     return knn.cpu().numpy().view(np.uint32), dist.cpu().numpy()
+
+
+def _reference_answer(x, y):
+    """FindNearestNeighbor of the compiled reference, or None where it was not built."""
+    from oracle import ref
+
+    if not ref.available():
+        return None
+    return ref.find_nearest(x, y)
 
 
 def _compare(x, y, knn, dist, knn0, dist0):
@@ -54,6 +67,10 @@ def test_noalloc_matches_regular_entry_point_twice(n, d, k):
         knn0, dist0 = skm.engine.find_nearest(x, y)
         knn, dist = _run_noalloc(skm, torch, x, y)
         _compare(x, y, knn, dist, knn0, dist0)
+        # ... and against the reference's own operator, at the bar of the regular operator's test
+        r = _reference_answer(x, y)
+        if r is not None:
+            _compare(x, y, knn, dist, r[0], r[1])
 
 
 def test_noalloc_large_then_small_call():
@@ -69,6 +86,9 @@ def test_noalloc_large_then_small_call():
         knn0, dist0 = skm.engine.find_nearest(x, y)
         knn, dist = _run_noalloc(skm, torch, x, y)
         _compare(x, y, knn, dist, knn0, dist0)
+        r = _reference_answer(x, y)
+        if r is not None:
+            _compare(x, y, knn, dist, r[0], r[1])
 
 
 def test_noalloc_rejects_sizes_beyond_the_static_scratch():
