@@ -289,15 +289,21 @@ def main():
     cands = []   # (kernel, phase ms, launches, bound, work per Train, unit)
     ms, calls = phase_acc["search/1st_blas"]
     cands.append(("gemm_tc_kernel<ARGMIN>", ms, calls, "tensor", sum(2.0 * n_local * k * d for s in stats if s.is_gemm_only)))
+    chain = e.chain_counters()      # of the last timed Train
     ms, calls = phase_acc["search/first_test"]
-    cands.append(("gemm_tc_kernel<PRUNE>", ms, calls, "tensor", sum(2.0 * n_local * k * pd for pd in d_partial) if prune_path == 4 else 0.0))
+    listed_rows = n_local * len(d_partial) - chain["rows"] if prune_path == 6 else n_local * len(d_partial)
+    cands.append(("gemm_tc_kernel<PRUNE>", ms, calls, "tensor", 2.0 * listed_rows * k * float(np.mean(d_partial)) if prune_path in (4, 6) and d_partial else 0.0))
     ms, calls = phase_acc["search/dense"]
-    cands.append(("chain_tc_kernel", ms, calls, "tensor", 2.0 * counters["dense_rows"] * k * d))
+    if prune_path == 6:
+        # union pass over the first d' dimensions of every centroid + the chain over the gathered columns (128 rows per unit)
+        cands.append(("sparse_chain_kernel", ms, calls, "tensor", 2.0 * 128 * chain["columns"] * d + 2.0 * chain["rows"] * k * float(np.mean(d_partial) if d_partial else 0)))
+    else:
+        cands.append(("chain_tc_kernel", ms, calls, "tensor", 2.0 * counters["dense_rows"] * k * d))
     ms, calls = phase_acc["search/walk"]
     # every (pair, 64-dimension block) step gathers 256 B of the centroid's PDX block (the point's 256 B stay in
     # registers across the pairs of a point)
     cands.append(("walk_lists_kernel", ms, calls, "hbm", 256.0 * counters["walk_pair_steps"]))
-    if prune_path not in (3, 4):
+    if prune_path not in (3, 4, 6):
         ms, calls = phase_acc["search"]
         cands.append(("assign_pruned_kernel", ms, calls, "tensor", sum(2.0 * n_local * k * pd for pd in d_partial)))
     dom, dom_ms, dom_calls, bound, work = max(cands, key=lambda c: c[1])

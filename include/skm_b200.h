@@ -140,12 +140,17 @@ skm_status skm_get_distances(skm_handle* h, float* out, uint64_t n);
 skm_status skm_get_rotated_centroids(skm_handle* h, float* out);
 /* Which kernels the last pruned assignment pass used: 0 none yet, 1 candidate lists (+ dense SIMT chain for
  * flagged points), 3 tensor-core chain, 4 tensor-core first test + list walk (+ tensor-core chain for flagged
- * points). */
+ * points), 6 points taken in the order of their previous centroid, every 128-point tile through first test + list
+ * walk or through the chain over the centroids its rows can still reach. */
 int skm_last_prune_path(const skm_handle* h);
 /* Work done by the pruned passes of this handle so far: out3[0] rows sent through a dense chain, out3[1]
  * (pair, 64-dimension block) steps of the candidate-list walk (each reads 256 bytes of a centroid and of a
  * point), out3[2] rows whose candidate list overflowed and were redone densely.  For roofline accounting. */
 skm_status skm_get_prune_counters(const skm_handle* h, uint64_t* out3);
+/* Work of the chain over gathered centroids (prune path 6) so far: out2[0] rows of the tiles it processed, out2[1]
+ * centroid columns its units held (each unit rounded up to a multiple of 16), summed over tiles and 1024-centroid
+ * chunks; its tensor-core work is 2 * 128 * out2[1] * d flop, counted once.  For roofline accounting. */
+skm_status skm_get_chain_counters(const skm_handle* h, uint64_t* out2);
 /* Objective of the last iteration accumulated in float64 (the reference sums float32). */
 double skm_last_objective_f64(const skm_handle* h);
 
@@ -172,13 +177,16 @@ skm_status skm_reset_phase_times(skm_handle* h);
  * No counterpart in the reference (it delegates to whatever BLAS is linked). */
 void skm_set_tensor_cores(int enabled);
 int skm_get_tensor_cores(void);
-/* Which kernels a pruned assignment pass uses: 0 (default) chosen from the survival rate of the first
- * ADSampling test on a sample of centroids (tensor-core dense chain when many pairs survive, else tensor-core
- * first test + candidate-list walk, with the few points of high survival on the dense SIMT chain); 1 SIMT
- * candidate lists for all points; 2 dense SIMT chain for all; 3 tensor-core dense chain for all; 4 tensor-core
- * first test + list walk for all; 5 as 4 with a quarter of the list capacity, so that overflowing lists take
- * their fallback.  The results do not depend on the choice (up to fp32 rounding); it exists for profiling and
- * for testing each kernel on its own.  No counterpart in the reference. */
+/* Which kernels a pruned assignment pass uses.  0 (default): with rows that TMA can address (d % 4 == 0) the points are
+ * taken in the order of their previous centroid and every tile of 128 goes through the tensor-core first test + list
+ * walk or, when many of its points keep a large share of the centroids alive, through the tensor-core chain over the
+ * centroids its rows can still reach; SIMT candidate lists otherwise.  1 SIMT candidate lists for all points; 2 dense
+ * SIMT chain for all; 3 dense tensor-core chain for all; 4 tensor-core first test + list walk for all, original
+ * order; 5 as 4 with a quarter of the list capacity, so that overflowing lists take their fallback; 6 ordered points,
+ * gathered chain for every tile; 7 ordered points, first test + list walk for every tile; 8 as 7 with the small lists
+ * of 5; 9 the automatic choice without ordering (dense chain for all points when the sampled survival is high, else
+ * first test + list walk with flagged points on the dense chain).  The results do not depend on the choice (up to
+ * fp32 rounding); it exists for profiling and for testing each kernel on its own.  No counterpart in the reference. */
 void skm_set_prune_split(int mode);
 int skm_get_prune_split(void);
 /* Test hook for the failure path of the tensor-core kernels (current device).  Every wait inside those kernels is

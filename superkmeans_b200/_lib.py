@@ -89,6 +89,7 @@ SIGNATURES = {
     "skm_last_objective_f64": (C.c_double, [C.c_void_p]),
     "skm_last_prune_path": (C.c_int, [C.c_void_p]),
     "skm_get_prune_counters": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]),
+    "skm_get_chain_counters": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]),
     "skm_set_trace": (C.c_int, [C.c_void_p, C.c_int]),
     "skm_trace_count": (C.c_uint64, [C.c_void_p]),
     "skm_trace_get": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint32), C.c_void_p, C.c_void_p, C.c_void_p,

@@ -132,6 +132,7 @@ struct WalkParams {
     size_t n, k, d;
     uint32_t partial_d, vertical_d, horizontal_d;
     size_t tile0, n_tiles;
+    const uint32_t* tile_map = nullptr;   // optional: entry t of the range stands for row tile tile_map[t] (lists stay indexed by t)
     const float* best_in;        // exact distance to the previous centroid
     const uint32_t* skip;        // may be null
     uint32_t* knn;
@@ -151,6 +152,19 @@ void launch_gather_listed(const float* x, const float* best, const uint32_t* knn
                           uint32_t* knn_out, cudaStream_t stream);
 void launch_scatter_listed(const uint32_t* idx, size_t n_listed, const uint32_t* knn_in, const float* dist_in, const uint32_t* np_in, uint32_t* knn, float* dist,
                            uint32_t* not_pruned, cudaStream_t stream);
+
+// The pass over the points in the order of their previous centroid: a batch of rows order[0 .. cnt) gathered with their
+// previous assignment (twice: knn_b is overwritten by the kernels, prev_b is not) and partial norm; the results
+// scattered back; per-tile flags from per-row flags; the starting state of the rows of listed tiles; and the sampled
+// survival classification alone (ws.best must already hold the exact distances to the previous centroids).
+void launch_gather_sorted(const float* x, const uint32_t* order, const uint32_t* knn, const float* norms_x, size_t cnt, size_t d, float* xb, uint32_t* knn_b, uint32_t* prev_b,
+                          float* nx_b, cudaStream_t stream);
+void launch_scatter_sorted(const uint32_t* order, size_t cnt, const uint32_t* knn_b, const float* dist_b, const uint32_t* np_b, uint32_t* knn, float* dist,
+                           uint32_t* not_pruned, cudaStream_t stream);
+void launch_tile_flags(const uint32_t* row_flags, size_t n, uint32_t threshold, uint32_t* tile_flags, cudaStream_t stream);
+void launch_init_chain_rows(const uint32_t* tile_map, size_t n_tiles, size_t n, const uint32_t* prev, const float* best, uint32_t* knn, float* dist, uint32_t* not_pruned,
+                            uint2* top2, cudaStream_t stream);
+void launch_classify(const PrunedParams& p, PruneSplitWorkspace& ws, cudaStream_t stream);
 
 // k nearest rows of y for every row of q by ||q||^2 + ||y||^2 - 2 q.y (BatchComputer::FindKNearestNeighbors,
 // batch_computers.h:191-274): out_idx / out_dist are n_q x k, ascending by (distance, index); dots_scratch needs
@@ -181,6 +195,10 @@ struct UpdateWorkspace {
 };
 size_t update_sort_units(size_t n);
 size_t update_tiles(size_t n);
+
+// Stable sort of the indices 0 .. n-1 by keys[i] (< k): *sorted_keys_out / *order_out point into the workspace's key and
+// value buffers (keys_a/b, vals_a/b, digit_table must be allocated for n).
+void launch_sort_by_key(const uint32_t* keys, size_t n, size_t k, UpdateWorkspace& ws, const uint32_t** sorted_keys_out, const uint32_t** order_out, cudaStream_t stream);
 
 // counts[c] = |{i : assign[i] == c}|, sums[c] = sum of x rows assigned to c (deterministic order),
 // *wcss = sum_i dist[i] (double), *not_pruned_total = sum_i not_pruned[i] (may be null).

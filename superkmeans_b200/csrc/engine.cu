@@ -381,6 +381,228 @@ void run_listed_dense(const PrunedParams& p, PruneSplitWorkspace& ws, PrunePassB
 
 } // namespace
 
+namespace {
+
+struct SubPhase {
+    PhaseTimers* t;
+    cudaStream_t s;
+    SubPhase(PhaseTimers* t_, int phase, cudaStream_t s_) : t(t_), s(s_) {
+        if (t) t->begin(phase, s);
+    }
+    ~SubPhase() {
+        if (t) t->end(s);
+    }
+};
+
+// Rows per batch of the ordered pass: about 8 GB of gathered rows, a whole number of 128-row tiles.
+size_t sorted_batch_rows(size_t n, size_t d) {
+    const size_t target = (size_t{8} << 30) / (d * sizeof(float));
+    size_t rows = std::max<size_t>(target, 16 * kTileM);
+    rows = (rows / kTileM) * kTileM;
+    return std::min(rows, ((n + kTileM - 1) / kTileM) * kTileM);
+}
+
+// The pruned pass over the points in the order of their previous centroid (modes 0, 6, 7, 8).  Points that share a
+// previous centroid have nearly the same thresholds and the same neighbourhood of centroids, so a tile of 128 of them
+// either has short candidate lists (first test + list walk) or keeps a common, limited set of centroids alive (chain
+// over the centroids named by the tile's union bits).  The order changes where work is done, not what is computed.
+void run_pruned_pass_sorted(const PrunedParams& p, PrunePassBuffers& b, float ratio_first, int device, cudaStream_t stream, PhaseTimers* timers, int mode) {
+    const uint32_t n_ck = prune_chain_checkpoints(p.partial_d, p.vertical_d, p.horizontal_d);
+    const size_t n_chunks = (p.k + kChunk - 1) / kChunk;
+    const uint32_t union_words = static_cast<uint32_t>((p.k + 31) / 32);
+    const size_t cols_stride = n_chunks * kChunk;
+
+    // ---- order of the points by previous centroid
+    const size_t units = update_sort_units(p.n);
+    b.sort_ws.keys_a = b.sort_keys_a.ensure(p.n);
+    b.sort_ws.keys_b = b.sort_keys_b.ensure(p.n);
+    b.sort_ws.vals_a = b.sort_vals_a.ensure(p.n);
+    b.sort_ws.vals_b = b.sort_vals_b.ensure(p.n);
+    b.sort_ws.digit_table = b.sort_table.ensure(256 * units + (256 * units) / 2048 + 64);
+    const uint32_t* sorted_keys = nullptr;
+    const uint32_t* order = nullptr;
+    launch_sort_by_key(p.knn, p.n, p.k, b.sort_ws, &sorted_keys, &order, stream);
+
+    // ---- centroid side, once per pass
+    float* y_split = b.y_split.ensure(2 * p.k * p.d);
+    tc::launch_presplit(p.y, p.k, p.d, y_split, stream);
+    float* chain_norms_y = b.chain_norms_y.ensure(p.k * n_ck);
+    launch_chain_norms(p.y, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, true, chain_norms_y, stream);
+
+    const size_t batch = sorted_batch_rows(p.n, p.d);
+    const size_t batch_tiles = batch / kTileM;
+    float* xb = b.xb.ensure(batch * p.d);
+    uint32_t* knn_b = b.knn_b.ensure(batch);
+    uint32_t* prev_b = b.prev_b.ensure(batch);
+    float* best_b = b.best_b.ensure(batch);
+    float* dist_b = b.dist_b.ensure(batch);
+    float* nx_b = b.nx_b.ensure(batch);
+    uint32_t* np_b = b.np_b.ensure(batch);
+    uint32_t* flags_b = b.flags_b.ensure(batch);
+    uint32_t* redo_b = b.redo.ensure(batch + 1);
+    uint2* top2_b = b.top2_b.ensure(batch);
+    uint32_t* tile_flags = b.tile_flags.ensure(batch_tiles);
+    uint32_t* tile_flags_host = b.tile_flags_host.ensure(batch_tiles);
+    uint32_t* map_dense = b.tile_map_dense.ensure(batch_tiles);
+    uint32_t* map_lists = b.tile_map_lists.ensure(batch_tiles);
+    uint32_t* map_host = b.tile_map_host.ensure(2 * batch_tiles);
+    unsigned long long* pair_steps = b.pair_steps_dev.ensure(1);
+    unsigned long long* sparse_cols = b.sparse_cols_dev.ensure(1);
+    unsigned long long* counters_host = b.counters_host.ensure(2);
+    SKM_CUDA(cudaMemsetAsync(pair_steps, 0, sizeof(unsigned long long), stream));
+    SKM_CUDA(cudaMemsetAsync(sparse_cols, 0, sizeof(unsigned long long), stream));
+
+    PruneSplitWorkspace ws;
+    ws.sample = b.sample.ensure(128 * p.d);
+    ws.sample_norms = b.sample_norms.ensure(128);
+    ws.alive_total = b.alive_total.ensure(1);
+    ws.ratio_first = ratio_first;
+    ws.flag_mult = 22;   // a point is "expensive" from 6 of 128 sampled survivors up
+
+    // candidate lists: eight per tile, each with room for an eighth of its pairs (modes 5 / 8: a thirty-second)
+    const uint32_t cap_group = static_cast<uint32_t>(std::max<size_t>(128, mode == 8 ? p.k / 2 : p.k * 2));
+    const size_t list_tile_bytes = 8 * static_cast<size_t>(cap_group) * sizeof(uint2);
+    const size_t lists_per_launch = std::max<size_t>(1, (static_cast<size_t>(6) << 30) / list_tile_bytes);
+    // chain: at most ~1 GB of column lists per launch
+    const size_t chain_per_launch = std::max<size_t>(1, (size_t{1} << 30) / (cols_stride * sizeof(uint16_t)));
+
+    b.last_path = 6;
+    b.last_n_hard = 0;
+    b.last_n_redo = 0;
+
+    // The chain over the tiles listed in map_host[0 .. n_t) (host) / map_dev (device copy of the same list).
+    auto run_chain_tiles = [&](const uint32_t* map_dev, size_t n_t, size_t rows_in_batch) {
+        if (n_t == 0) return;
+        SubPhase sub(timers, PH_PRUNE_DENSE, stream);
+        float* chain_norms_xb = b.chain_norms_x.ensure(batch * n_ck);
+        // cumulative norms for all rows of the batch are cheap next to what follows, and keep the indexing plain
+        launch_chain_norms(xb, rows_in_batch, p.d, p.partial_d, p.vertical_d, p.horizontal_d, false, chain_norms_xb, stream);
+        launch_init_chain_rows(map_dev, n_t, rows_in_batch, prev_b, best_b, knn_b, dist_b, np_b, top2_b, stream);
+        const size_t per = std::min(n_t, chain_per_launch);
+        uint32_t* ubits = b.union_bits.ensure(per * union_words);
+        uint16_t* cols = b.cols.ensure(per * cols_stride);
+        uint32_t* counts = b.col_counts.ensure(per * n_chunks);
+        for (size_t t0 = 0; t0 < n_t; t0 += per) {
+            const size_t nt = std::min(per, n_t - t0);
+            SKM_CUDA(cudaMemsetAsync(ubits, 0, sizeof(uint32_t) * nt * union_words, stream));
+            tc::launch_union(xb, rows_in_batch, p.k, p.d, p.partial_d, nx_b, p.norms_y, best_b, ratio_first, map_dev + t0, nt, ubits, union_words, y_split, stream);
+            tc::launch_build_cols(ubits, union_words, nt, p.k, cols, counts, cols_stride, sparse_cols, stream);
+            tc::launch_sparse_chain(xb, rows_in_batch, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, chain_norms_xb, chain_norms_y, p.ratios, best_b, knn_b, dist_b, np_b,
+                                    top2_b, y_split, map_dev + t0, nt, cols, counts, cols_stride, stream);
+        }
+        tc::launch_refine_chain_tiles(xb, p.y, rows_in_batch, p.k, p.d, top2_b, knn_b, dist_b, map_dev, n_t, stream);
+        b.total_sparse_rows += n_t * kTileM;
+        b.total_dense_rows += n_t * kTileM;
+        b.last_n_hard += n_t * kTileM;
+    };
+
+    for (size_t b0 = 0; b0 < p.n; b0 += batch) {
+        const size_t cnt = std::min(batch, p.n - b0);
+        const size_t n_tiles = (cnt + kTileM - 1) / kTileM;
+        launch_gather_sorted(p.x, order + b0, p.knn, p.norms_x, cnt, p.d, xb, knn_b, prev_b, nx_b, stream);
+        launch_exact_dist(xb, p.y, knn_b, cnt, p.d, best_b, stream);
+
+        // ---- which tiles take which route
+        size_t n_dense = 0, n_lists = 0;
+        if (mode == 0) {
+            PrunedParams pb = p;
+            pb.x = xb;
+            pb.n = cnt;
+            pb.norms_x = nx_b;
+            ws.best = best_b;
+            ws.flags = flags_b;
+            launch_classify(pb, ws, stream);
+            launch_tile_flags(flags_b, cnt, 16, tile_flags, stream);
+            SKM_CUDA(cudaMemcpyAsync(tile_flags_host, tile_flags, sizeof(uint32_t) * n_tiles, cudaMemcpyDeviceToHost, stream));
+            SKM_CUDA(cudaStreamSynchronize(stream));
+            for (size_t t = 0; t < n_tiles; ++t) {
+                if (tile_flags_host[t]) map_host[n_dense++] = static_cast<uint32_t>(t);
+                else map_host[batch_tiles + n_lists++] = static_cast<uint32_t>(t);
+            }
+        } else if (mode == 6) {
+            for (size_t t = 0; t < n_tiles; ++t) map_host[n_dense++] = static_cast<uint32_t>(t);
+        } else {
+            for (size_t t = 0; t < n_tiles; ++t) map_host[batch_tiles + n_lists++] = static_cast<uint32_t>(t);
+        }
+        if (n_dense) SKM_CUDA(cudaMemcpyAsync(map_dense, map_host, sizeof(uint32_t) * n_dense, cudaMemcpyHostToDevice, stream));
+        if (n_lists) SKM_CUDA(cudaMemcpyAsync(map_lists, map_host + batch_tiles, sizeof(uint32_t) * n_lists, cudaMemcpyHostToDevice, stream));
+
+        // ---- first test + list walk
+        if (n_lists) {
+            uint32_t* redo_count = redo_b + batch;
+            SKM_CUDA(cudaMemsetAsync(redo_b, 0, sizeof(uint32_t) * (batch + 1), stream));
+            const size_t per = std::min(n_lists, lists_per_launch);
+            uint2* lists = b.tc_lists.ensure(per * 8 * cap_group);
+            uint32_t* offs = b.tc_list_offs.ensure(per * 8 * (n_chunks + 1));
+            for (size_t t0 = 0; t0 < n_lists; t0 += per) {
+                const size_t nt = std::min(per, n_lists - t0);
+                {
+                    SubPhase sub(timers, PH_PRUNE_FIRST_TEST, stream);
+                    tc::launch_first_test(xb, p.y, cnt, p.k, p.d, p.partial_d, nx_b, p.norms_y, best_b, nullptr, ratio_first, 0, nt, lists, offs, cap_group, stream, y_split,
+                                          map_lists + t0);
+                }
+                WalkParams w{};
+                w.x = xb;
+                w.y = p.y;
+                w.norms_x = nx_b;
+                w.y_pdx = p.y_pdx;
+                w.y_aux = p.y_aux;
+                w.ratios = p.ratios;
+                w.lists = lists;
+                w.list_offs = offs;
+                w.cap_group = cap_group;
+                w.n = cnt;
+                w.k = p.k;
+                w.d = p.d;
+                w.partial_d = p.partial_d;
+                w.vertical_d = p.vertical_d;
+                w.horizontal_d = p.horizontal_d;
+                w.tile0 = 0;
+                w.n_tiles = nt;
+                w.tile_map = map_lists + t0;
+                w.best_in = best_b;
+                w.skip = nullptr;
+                w.knn = knn_b;
+                w.dist = dist_b;
+                w.not_pruned = np_b;
+                w.redo = redo_b;
+                w.redo_count = redo_count;
+                w.pair_steps = pair_steps;
+                w.upstream_error = tc::error_word();
+                SubPhase sub(timers, PH_PRUNE_WALK, stream);
+                launch_walk_lists(w, device, stream);
+            }
+            // tiles with a list that overflowed: the whole tile goes through the chain, from its starting state
+            launch_tile_flags(redo_b, cnt, 1, tile_flags, stream);
+            SKM_CUDA(cudaMemcpyAsync(tile_flags_host, tile_flags, sizeof(uint32_t) * n_tiles, cudaMemcpyDeviceToHost, stream));
+            SKM_CUDA(cudaMemcpyAsync(&counters_host[0], redo_count, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
+            SKM_CUDA(cudaStreamSynchronize(stream));
+            const size_t n_redo_rows = static_cast<size_t>(counters_host[0] & 0xFFFFFFFFull);
+            if (n_redo_rows) {
+                for (size_t t = 0; t < n_tiles; ++t)
+                    if (tile_flags_host[t]) map_host[n_dense++] = static_cast<uint32_t>(t);
+                SKM_CUDA(cudaMemcpyAsync(map_dense, map_host, sizeof(uint32_t) * n_dense, cudaMemcpyHostToDevice, stream));
+                b.last_n_redo += n_redo_rows;
+                b.total_redo_rows += n_redo_rows;
+            }
+        }
+
+        // ---- chain over the centroids the tile can still reach
+        run_chain_tiles(map_dense, n_dense, cnt);
+
+        launch_scatter_sorted(order + b0, cnt, knn_b, dist_b, np_b, p.knn, p.dist, p.not_pruned, stream);
+        // map_host / tile_flags_host are reused by the next batch: the copies above must have been consumed
+        SKM_CUDA(cudaStreamSynchronize(stream));
+    }
+    SKM_CUDA(cudaMemcpyAsync(&counters_host[0], pair_steps, sizeof(unsigned long long), cudaMemcpyDeviceToHost, stream));
+    SKM_CUDA(cudaMemcpyAsync(&counters_host[1], sparse_cols, sizeof(unsigned long long), cudaMemcpyDeviceToHost, stream));
+    SKM_CUDA(cudaStreamSynchronize(stream));
+    b.total_pair_steps += counters_host[0];
+    b.total_sparse_cols += counters_host[1];
+}
+
+} // namespace
+
 void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, int device, cudaStream_t stream, PhaseTimers* timers) {
     struct Sub {
         PhaseTimers* t;
@@ -393,6 +615,13 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
         }
     };
     if (p.n == 0) return;
+    int mode = g_prune_split_mode;
+    if ((mode == 0 || (mode >= 6 && mode <= 8)) && tc::eligible(p.x, p.d, p.y, p.d)) {
+        run_pruned_pass_sorted(p, b, ratio_first, device, stream, timers, mode);
+        return;
+    }
+    if (mode >= 6 && mode <= 8) throw std::invalid_argument("the ordered pruned pass needs 16-byte aligned rows (d % 4 == 0) and the tensor-core kernels switched on");
+    if (mode == 9) mode = 0;
     if (b.grid == 0) b.grid = pruned_grid_size(device);
     const uint32_t n_ck = prune_chain_checkpoints(p.partial_d, p.vertical_d, p.horizontal_d);
     PruneSplitWorkspace ws;
@@ -407,13 +636,13 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
     ws.ratio_first = ratio_first;
     ws.alive_total = b.alive_total.ensure(1);
     // with the tensor-core chain available, points from 6 of 128 sampled survivors up are cheaper there
-    if (tc::eligible(p.x, p.d, p.y, p.d) && (g_prune_split_mode == 0)) ws.flag_mult = 22;
+    if (tc::eligible(p.x, p.d, p.y, p.d) && (mode == 0)) ws.flag_mult = 22;
     launch_pruned_prepare(p, ws, stream);
     const int n_sample = static_cast<int>(std::min<size_t>(p.k, 128));
     const bool tc_ok = tc::eligible(p.x, p.d, p.y, p.d);
     size_t n_hard = 0;
     bool use_chain = false, use_tc_lists = false;
-    if (g_prune_split_mode == 0) {
+    if (mode == 0) {
         unsigned long long* host = b.counters_host.ensure(2);
         host[0] = 0;
         host[1] = 0;
@@ -428,12 +657,12 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
         // block per surviving pair and step, and their capacity is an eighth of all pairs.
         use_chain = tc_ok && (survival > 0.08 || n_hard * 2 > p.n);
         use_tc_lists = tc_ok && !use_chain;
-    } else if (g_prune_split_mode == 3) {
+    } else if (mode == 3) {
         if (!tc_ok) throw std::invalid_argument("the tensor-core chain needs 16-byte aligned rows (d % 4 == 0)");
         use_chain = true;
     } else {
-        const bool dense = g_prune_split_mode == 2;
-        use_tc_lists = g_prune_split_mode == 4 || g_prune_split_mode == 5;
+        const bool dense = mode == 2;
+        use_tc_lists = mode == 4 || mode == 5;
         if (use_tc_lists && !tc_ok) throw std::invalid_argument("the tensor-core first test needs 16-byte aligned rows (d % 4 == 0)");
         fill_iota_kernel<<<static_cast<unsigned>((p.n + 255) / 256), 256, 0, stream>>>(ws.hard_idx, ws.flags, p.n, dense ? 1u : 0u);
         note_kernel_launch();
@@ -465,7 +694,7 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
             const size_t n_chunks = (p.k + kChunk - 1) / kChunk;
             // eight lists per tile of 128 points, each with room for an eighth of its pairs (32 points x half the
             // centroids); mode 5: a thirty-second, so that lists overflow
-            const uint32_t cap_group = static_cast<uint32_t>(std::max<size_t>(128, g_prune_split_mode == 5 ? p.k / 2 : p.k * 2));
+            const uint32_t cap_group = static_cast<uint32_t>(std::max<size_t>(128, mode == 5 ? p.k / 2 : p.k * 2));
             const size_t tile_bytes = 8 * static_cast<size_t>(cap_group) * sizeof(uint2);
             const size_t n_tiles = (p.n + kTileM - 1) / kTileM;
             const size_t list_bytes_cap = static_cast<size_t>(6) << 30;

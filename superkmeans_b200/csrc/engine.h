@@ -124,12 +124,28 @@ struct PrunePassBuffers {
     // steps of the list walk, rows whose list overflowed
     unsigned long long total_dense_rows = 0, total_pair_steps = 0, total_redo_rows = 0;
     DeviceBuffer<unsigned long long> pair_steps_dev;
+    // the pass over the points in the order of their previous centroid (paths 6-8)
+    UpdateWorkspace sort_ws;
+    DeviceBuffer<uint32_t> sort_keys_a, sort_keys_b, sort_vals_a, sort_vals_b, sort_table;
+    DeviceBuffer<float> xb, best_b, dist_b, nx_b;
+    DeviceBuffer<uint32_t> knn_b, prev_b, np_b, flags_b, tile_flags, tile_map_dense, tile_map_lists, union_bits, col_counts;
+    DeviceBuffer<uint16_t> cols;
+    DeviceBuffer<uint2> top2_b;
+    DeviceBuffer<unsigned long long> sparse_cols_dev;
+    PinnedBuffer<uint32_t> tile_flags_host, tile_map_host;
+    // totals since creation: rows of tiles sent through the gathered chain, centroid columns (rounded to 16) its units
+    // held, summed over tiles and chunks - the chain's tensor-core work is 2 * 128 * columns * d flop (counted once)
+    unsigned long long total_sparse_rows = 0, total_sparse_cols = 0;
 };
-// mode: 0 = automatic (tensor-core chain for every point when the sampled survival rate is high, else the
-// tensor-core first test with list walk, flagged points on the dense SIMT chain; SIMT candidate lists when rows
-// are not 16-byte aligned), 1 = SIMT candidate lists for every point, 2 = dense SIMT chain for every point,
-// 3 = tensor-core chain for every point, 4 = tensor-core first test + list walk for every point, 5 = as 4 with
-// the list capacity cut to a quarter so that the overflow route runs.
+// mode: 0 = automatic: with rows that TMA can address, the points are taken in the order of their previous centroid and
+// every tile of 128 goes either through the first test + list walk or, when many of its points keep a large share of
+// the centroids alive, through the chain over the centroids its rows can still reach; SIMT candidate lists otherwise.
+// 1 = SIMT candidate lists for every point, 2 = dense SIMT chain for every point, 3 = dense tensor-core chain for every
+// point, 4 = tensor-core first test + list walk for every point (original order), 5 = as 4 with the list capacity cut
+// to a quarter so that the overflow route runs, 6 = ordered points, gathered chain for every tile, 7 = ordered points,
+// first test + list walk for every tile (overflowing tiles through the gathered chain), 8 = as 7 with the small lists
+// of mode 5, 9 = the automatic choice without ordering (dense chain for all points when the sampled survival rate is
+// high, else first test + list walk with flagged points on the dense chain).
 void set_prune_split_mode(int mode);
 int prune_split_mode();
 void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, int device, cudaStream_t stream, PhaseTimers* timers = nullptr);
@@ -165,6 +181,10 @@ class Engine {
         out[0] = prune_bufs_.total_dense_rows;
         out[1] = prune_bufs_.total_pair_steps;
         out[2] = prune_bufs_.total_redo_rows;
+    }
+    void chain_counters(uint64_t out[2]) const {
+        out[0] = prune_bufs_.total_sparse_rows;
+        out[1] = prune_bufs_.total_sparse_cols;
     }
     const std::vector<skm_iter_stats>& stats(int phase) const;
     int device() const { return device_; }

@@ -844,22 +844,18 @@ __global__ void __launch_bounds__(256) reduce_final_kernel(const double* __restr
     }
 }
 
-void launch_update(
-    const float* x, const uint32_t* assign, const float* dist, const uint32_t* not_pruned, size_t n, size_t k, size_t d, UpdateWorkspace& ws, float* sums, uint32_t* counts,
-    double* wcss, unsigned long long* not_pruned_total, cudaStream_t stream
-) {
-    if (n == 0) return;
+// Stable LSD radix sort of the indices 0 .. n-1 by key (keys < k): *sorted_keys and *order point into ws.keys_* / ws.vals_*.
+void launch_sort_by_key(const uint32_t* keys, size_t n, size_t k, UpdateWorkspace& ws, const uint32_t** sorted_keys_out, const uint32_t** order_out, cudaStream_t stream) {
     const size_t n_units = update_sort_units(n);
     int bits = 1;
     while ((size_t{1} << bits) < k) ++bits;
     const int passes = (bits + 7) / 8;
-    const uint32_t* kin = assign;
+    const uint32_t* kin = keys;
     const uint32_t* vin = nullptr;
     uint32_t* kout = ws.keys_a;
     uint32_t* vout = ws.vals_a;
     const unsigned unit_blocks = static_cast<unsigned>((n_units + 7) / 8);
-    // The scan's block totals reuse the front of tile_partials' sibling buffer: block_sums is too
-    // small, so a dedicated region at the end of digit_table is used (allocated by the engine).
+    // The scan's block totals live in a dedicated region at the end of digit_table (allocated by the caller).
     uint32_t* scan_totals = ws.digit_table + 256 * n_units;
     for (int pass = 0; pass < passes; ++pass) {
         const int shift = pass * 8;
@@ -873,8 +869,18 @@ void launch_update(
         kout = (kout == ws.keys_a) ? ws.keys_b : ws.keys_a;
         vout = (vout == ws.vals_a) ? ws.vals_b : ws.vals_a;
     }
-    const uint32_t* sorted_keys = kin;
-    const uint32_t* order = vin;
+    *sorted_keys_out = kin;
+    *order_out = vin;
+}
+
+void launch_update(
+    const float* x, const uint32_t* assign, const float* dist, const uint32_t* not_pruned, size_t n, size_t k, size_t d, UpdateWorkspace& ws, float* sums, uint32_t* counts,
+    double* wcss, unsigned long long* not_pruned_total, cudaStream_t stream
+) {
+    if (n == 0) return;
+    const uint32_t* sorted_keys = nullptr;
+    const uint32_t* order = nullptr;
+    launch_sort_by_key(assign, n, k, ws, &sorted_keys, &order, stream);
     segment_offsets_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(sorted_keys, n, k, ws.seg_offsets);
     SKM_LAUNCH_CHECK();
     counts_from_offsets_kernel<<<static_cast<unsigned>((k + 255) / 256), 256, 0, stream>>>(ws.seg_offsets, k, counts);

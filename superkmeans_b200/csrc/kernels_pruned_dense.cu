@@ -385,6 +385,102 @@ void launch_scatter_listed(const uint32_t* idx, size_t n_listed, const uint32_t*
     SKM_LAUNCH_CHECK();
 }
 
+// -------------------------------------------------------------------------------------------------
+// Helpers of the pass that works on the points in the order of their previous centroid
+// -------------------------------------------------------------------------------------------------
+// Rows order[b0 .. b0 + cnt) of x, their previous assignment and partial norm, gathered into a compact batch.
+__global__ void __launch_bounds__(256) gather_sorted_kernel(const float* __restrict__ x, const uint32_t* __restrict__ order, const uint32_t* __restrict__ knn,
+                                                            const float* __restrict__ norms_x, size_t cnt, size_t d, float* __restrict__ xb, uint32_t* __restrict__ knn_b,
+                                                            uint32_t* __restrict__ prev_b, float* __restrict__ nx_b) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t i = static_cast<size_t>(blockIdx.x) * 8 + warp;
+    if (i >= cnt) return;
+    const size_t row = order[i];
+    const float* src = x + row * d;
+    float* dst = xb + i * d;
+    if (d % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(xb)) & 15) == 0) {
+        for (size_t j = static_cast<size_t>(lane) * 4; j < d; j += 128) *reinterpret_cast<float4*>(dst + j) = __ldg(reinterpret_cast<const float4*>(src + j));
+    } else {
+        for (size_t j = lane; j < d; j += 32) dst[j] = src[j];
+    }
+    if (lane == 0) {
+        const uint32_t a = knn[row];
+        knn_b[i] = a;
+        prev_b[i] = a;
+        nx_b[i] = norms_x[row];
+    }
+}
+
+__global__ void scatter_sorted_kernel(const uint32_t* __restrict__ order, size_t cnt, const uint32_t* __restrict__ knn_b, const float* __restrict__ dist_b,
+                                      const uint32_t* __restrict__ np_b, uint32_t* __restrict__ knn, float* __restrict__ dist, uint32_t* __restrict__ not_pruned) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= cnt) return;
+    const size_t row = order[i];
+    knn[row] = knn_b[i];
+    dist[row] = dist_b[i];
+    not_pruned[row] = np_b[i];
+}
+
+// tile_flags[t] = 1 when at least `threshold` of the tile's rows carry a non-zero flag
+__global__ void __launch_bounds__(kTileM) tile_flags_kernel(const uint32_t* __restrict__ row_flags, size_t n, uint32_t threshold, uint32_t* __restrict__ tile_flags) {
+    const size_t row = static_cast<size_t>(blockIdx.x) * kTileM + threadIdx.x;
+    const int c = __syncthreads_count(row < n && row_flags[row] != 0u);
+    if (threadIdx.x == 0) tile_flags[blockIdx.x] = static_cast<uint32_t>(c) >= threshold ? 1u : 0u;
+}
+
+// What a chain over the listed tiles starts from (and what rows that the chain never reaches keep): the previous
+// assignment at its exact distance, no survivors, no runner-ups.
+__global__ void __launch_bounds__(kTileM) init_chain_rows_kernel(const uint32_t* __restrict__ tile_map, size_t n, const uint32_t* __restrict__ prev, const float* __restrict__ best,
+                                                                 uint32_t* __restrict__ knn, float* __restrict__ dist, uint32_t* __restrict__ not_pruned,
+                                                                 uint2* __restrict__ top2) {
+    const size_t row = static_cast<size_t>(tile_map[blockIdx.x]) * kTileM + threadIdx.x;
+    if (row >= n) return;
+    knn[row] = prev[row];
+    dist[row] = best[row];
+    not_pruned[row] = 0u;
+    top2[row] = make_uint2(0xFFFFFFFFu, 0xFFFFFFFFu);
+}
+
+void launch_gather_sorted(const float* x, const uint32_t* order, const uint32_t* knn, const float* norms_x, size_t cnt, size_t d, float* xb, uint32_t* knn_b, uint32_t* prev_b,
+                          float* nx_b, cudaStream_t stream) {
+    if (cnt == 0) return;
+    gather_sorted_kernel<<<static_cast<unsigned>((cnt + 7) / 8), 256, 0, stream>>>(x, order, knn, norms_x, cnt, d, xb, knn_b, prev_b, nx_b);
+    SKM_LAUNCH_CHECK();
+}
+
+void launch_scatter_sorted(const uint32_t* order, size_t cnt, const uint32_t* knn_b, const float* dist_b, const uint32_t* np_b, uint32_t* knn, float* dist,
+                           uint32_t* not_pruned, cudaStream_t stream) {
+    if (cnt == 0) return;
+    scatter_sorted_kernel<<<static_cast<unsigned>((cnt + 255) / 256), 256, 0, stream>>>(order, cnt, knn_b, dist_b, np_b, knn, dist, not_pruned);
+    SKM_LAUNCH_CHECK();
+}
+
+void launch_tile_flags(const uint32_t* row_flags, size_t n, uint32_t threshold, uint32_t* tile_flags, cudaStream_t stream) {
+    if (n == 0) return;
+    tile_flags_kernel<<<static_cast<unsigned>((n + kTileM - 1) / kTileM), kTileM, 0, stream>>>(row_flags, n, threshold, tile_flags);
+    SKM_LAUNCH_CHECK();
+}
+
+void launch_init_chain_rows(const uint32_t* tile_map, size_t n_tiles, size_t n, const uint32_t* prev, const float* best, uint32_t* knn, float* dist, uint32_t* not_pruned,
+                            uint2* top2, cudaStream_t stream) {
+    if (n_tiles == 0) return;
+    init_chain_rows_kernel<<<static_cast<unsigned>(n_tiles), kTileM, 0, stream>>>(tile_map, n, prev, best, knn, dist, not_pruned, top2);
+    SKM_LAUNCH_CHECK();
+}
+
+// flags / alive_total of launch_pruned_prepare without the exact distances and the compaction (the caller has the former and does not need the latter)
+void launch_classify(const PrunedParams& p, PruneSplitWorkspace& ws, cudaStream_t stream) {
+    if (p.n == 0) return;
+    const int n_sample = static_cast<int>(std::min<size_t>(p.k, kSample));
+    gather_sample_kernel<<<n_sample, 256, 0, stream>>>(p.y, p.k, p.d, n_sample, ws.sample);
+    SKM_LAUNCH_CHECK();
+    launch_row_sqnorms(ws.sample, n_sample, p.d, p.partial_d, ws.sample_norms, stream);
+    SKM_CUDA(cudaMemsetAsync(ws.alive_total, 0, sizeof(unsigned long long), stream));
+    classify_kernel<<<static_cast<unsigned>((p.n + kTileM - 1) / kTileM), 256, 0, stream>>>(p.x, ws.sample, ws.sample_norms, p.norms_x, ws.best, p.n, p.d, p.partial_d, n_sample,
+                                                                                             ws.ratio_first, ws.flag_mult, ws.flags, ws.alive_total);
+    SKM_LAUNCH_CHECK();
+}
+
 void launch_compact_flags(const uint32_t* flags, size_t n, PruneSplitWorkspace& ws, cudaStream_t stream) {
     if (n == 0) return;
     copy_u32_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(flags, ws.positions, n);

@@ -32,164 +32,10 @@
 
 #include "common.cuh"
 #include "kernels_tc.cuh"
+#include "tc_ptx.cuh"
 
 namespace skmb {
 namespace tc {
-
-constexpr int BM = 128;
-constexpr int BN = 256;
-constexpr int BK = 16;
-constexpr int STAGES = 4;
-constexpr int NUM_THREADS = 448;   // warps 10-13 work only in the first-test epilogue and in no other mode
-constexpr uint32_t A_TILE_BYTES = BM * BK * 4;   // 8192
-constexpr uint32_t B_TILE_BYTES = BN * BK * 4;   // 16384
-constexpr uint32_t STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;  // 49152
-constexpr uint32_t OFF_A_HI = 0, OFF_A_LO = A_TILE_BYTES, OFF_B_HI = 2 * A_TILE_BYTES, OFF_B_LO = 2 * A_TILE_BYTES + B_TILE_BYTES;
-constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t SMEM_CTRL_BYTES = 9216;
-constexpr uint32_t STAGE_ENTRIES = 256;   // per epilogue warp, first-test epilogue
-constexpr uint32_t SMEM_STAGE_BYTES = 8 * STAGE_ENTRIES * 8;
-constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + SMEM_CTRL_BYTES + SMEM_STAGE_BYTES + 1024;  // + alignment slack
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
-// Limit of every bounded wait, in SM clock cycles.  A variable rather than a constant so that a test can shorten it
-// (set_debug_wait_injection) and watch a wait run out in milliseconds instead of seconds.
-__device__ long long g_wait_limit_cycles = WAIT_LIMIT_CYCLES;
-__device__ __forceinline__ long long wait_limit_cycles() { return *reinterpret_cast<volatile long long*>(&g_wait_limit_cycles); }
-
-// kind::tf32, fp32 accumulate, K-major A and B, N = 256, M = 128
-constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
-
-struct Ctrl {
-    uint64_t full[STAGES];
-    uint64_t conv[STAGES];
-    uint64_t empty[STAGES];
-    uint64_t tmem_full[2];
-    uint64_t tmem_empty[2];
-    uint32_t tmem_base;
-    uint32_t pad;
-    alignas(16) float ny[4][2][BN];  // per row quarter, per accumulator buffer (read as float4)
-};
-static_assert(sizeof(Ctrl) <= SMEM_CTRL_BYTES, "control block too large");
-
-// ---------------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false (after recording `code`) when the limit expires, and also as soon as another role
-// has recorded a failure: once one role has given up the others would only run out their own limits.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 1023u) == 0) {
-            if (*reinterpret_cast<volatile int*>(err) != 0) return false;
-            if (clock64() - t0 > wait_limit_cycles()) {
-                atomicCAS(err, 0, code);
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* tmap, uint64_t* bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_dst),
-                 "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y)
-                 : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major tile of 64-byte rows, 64-byte swizzle, 8-row groups 512
-// bytes apart (version 1 = Blackwell).
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFF);
-    d |= static_cast<uint64_t>(1) << 16;            // leading byte offset (unused with swizzle)
-    d |= static_cast<uint64_t>(512 >> 4) << 32;     // stride byte offset between 8-row groups
-    d |= static_cast<uint64_t>(1) << 46;            // descriptor version
-    d |= static_cast<uint64_t>(4) << 61;            // SWIZZLE_64B
-    return d;
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, "
-        "%25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
-          "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// The same load without the wait, and the wait as a separate step that names the destination registers, so that
-// a second load can be in flight while the values of the first are being used.
-__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])::"memory");
-}
-
-__device__ __forceinline__ float to_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
-}
-
-__device__ __forceinline__ void split4(float4 v, float4& hi, float4& lo) {
-    hi.x = to_tf32(v.x); hi.y = to_tf32(v.y); hi.z = to_tf32(v.z); hi.w = to_tf32(v.w);
-    lo.x = to_tf32(v.x - hi.x); lo.y = to_tf32(v.y - hi.y); lo.z = to_tf32(v.z - hi.z); lo.w = to_tf32(v.w - hi.w);
-}
 
 struct Params {
     size_t n;         // rows of X
@@ -205,6 +51,7 @@ struct Params {
     float* out;
     size_t ldo;
     int* error;
+    long long wait_limit;   // SM cycles after which a wait gives up
     // first-test epilogue (MODE_PRUNE): rows [tile0 * 128, (tile0 + n_tiles) * 128) are processed; norms_x / norms_y
     // hold the norms over the first kdim dimensions
     size_t tile0;
@@ -217,6 +64,13 @@ struct Params {
     uint2* lists;
     uint32_t* list_offs;   // per list: (n_chunks + 1) entry counts at the start of every 1024-centroid chunk
     uint32_t cap_group;    // capacity of one list
+    // first-test and union modes: when set, entry t of the launch's tile range works on row tile tile_map[t]
+    // (rows tile_map[t] * 128 ...) instead of row tile tile0 + t; lists and union words stay indexed by t
+    const uint32_t* tile_map;
+    // union epilogue (MODE_UNION): bit c of union_bits[t * union_words + c / 32] is set when at least one row of the
+    // tile passes the (slightly widened) first test against centroid c
+    uint32_t* union_bits;
+    uint32_t union_words;
     // Y arrives already split: tmap_y covers the hi parts, tmap_ylo the lo parts, and the splitter warps
     // only treat X
     bool y_presplit;
@@ -225,7 +79,7 @@ struct Params {
     uint32_t debug_producer_stop;
 };
 
-enum { MODE_ARGMIN = 0, MODE_STORE = 1, MODE_PRUNE = 2 };
+enum { MODE_ARGMIN = 0, MODE_STORE = 1, MODE_PRUNE = 2, MODE_UNION = 3 };
 
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y,
@@ -236,6 +90,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
     uint8_t* smem = smem_raw + pad;
     const uint32_t smem_base = raw_addr + pad;
     Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + STAGES * STAGE_BYTES);
+    const WaitCtx wctx{p.error, p.wait_limit};
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -246,7 +101,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&ctrl->tmem_full[b], 1);
-            mbar_init(&ctrl->tmem_empty[b], MODE == MODE_PRUNE ? 256 : 128);
+            mbar_init(&ctrl->tmem_empty[b], (MODE == MODE_PRUNE || MODE == MODE_UNION) ? 256 : 128);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
@@ -257,8 +112,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
     tc_fence_after();
     const uint32_t tmem_base = ctrl->tmem_base;
 
-    const size_t rt_begin = (MODE == MODE_PRUNE) ? p.tile0 : 0;
-    const size_t n_row_tiles = (MODE == MODE_PRUNE) ? p.tile0 + p.n_tiles : (p.n + BM - 1) / BM;
+    constexpr bool kTiled = (MODE == MODE_PRUNE || MODE == MODE_UNION);   // works on a given range / list of row tiles
+    const size_t rt_begin = kTiled ? p.tile0 : 0;
+    const size_t n_row_tiles = kTiled ? p.tile0 + p.n_tiles : (p.n + BM - 1) / BM;
+    // row tile that entry rt of the loops below stands for
+    auto tile_of = [&](size_t rt) -> size_t { return (kTiled && p.tile_map) ? static_cast<size_t>(__ldg(p.tile_map + (rt - rt_begin))) : rt; };
     const uint32_t n_col_tiles = static_cast<uint32_t>((p.k + BN - 1) / BN);
     const uint32_t nkb = (p.kdim + BK - 1) / BK;
 
@@ -268,6 +126,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
             uint32_t kbt = 0;
             bool ok = true;
             for (size_t rt = rt_begin + blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {
+                const size_t x_row = tile_of(rt) * BM;
                 for (uint32_t nt = 0; nt < n_col_tiles && ok; ++nt) {
                     for (uint32_t kb = 0; kb < nkb; ++kb, ++kbt) {
                         const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
@@ -275,13 +134,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                             ok = false;
                             break;
                         }
-                        if (!mbar_wait(&ctrl->empty[s], ph ^ 1u, p.error, 1)) {
+                        if (!mbar_wait(&ctrl->empty[s], ph ^ 1u, wctx, 1)) {
                             ok = false;
                             break;
                         }
                         mbar_arrive_expect_tx(&ctrl->full[s], A_TILE_BYTES + (p.y_presplit ? 2 * B_TILE_BYTES : B_TILE_BYTES));
                         const uint32_t st = smem_base + s * STAGE_BYTES;
-                        tma_load_2d(st + OFF_A_HI, &tmap_x, &ctrl->full[s], static_cast<int>(kb * BK), static_cast<int>(rt * BM));
+                        tma_load_2d(st + OFF_A_HI, &tmap_x, &ctrl->full[s], static_cast<int>(kb * BK), static_cast<int>(x_row));
                         tma_load_2d(st + OFF_B_HI, &tmap_y, &ctrl->full[s], static_cast<int>(kb * BK), static_cast<int>(nt * BN));
                         if (p.y_presplit) tma_load_2d(st + OFF_B_LO, &tmap_ylo, &ctrl->full[s], static_cast<int>(kb * BK), static_cast<int>(nt * BN));
                     }
@@ -296,7 +155,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
             for (size_t rt = rt_begin + blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {
                 for (uint32_t nt = 0; nt < n_col_tiles && ok; ++nt, ++t) {
                     const uint32_t b = t & 1u, tph = (t >> 1) & 1u;
-                    if (!mbar_wait(&ctrl->tmem_empty[b], tph ^ 1u, p.error, 2)) {
+                    if (!mbar_wait(&ctrl->tmem_empty[b], tph ^ 1u, wctx, 2)) {
                         ok = false;
                         break;
                     }
@@ -304,7 +163,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                     const uint32_t acc = tmem_base + b * BN;
                     for (uint32_t kb = 0; kb < nkb; ++kb, ++kbt) {
                         const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
-                        if (!mbar_wait(&ctrl->conv[s], ph, p.error, 3)) {
+                        if (!mbar_wait(&ctrl->conv[s], ph, wctx, 3)) {
                             ok = false;
                             break;
                         }
@@ -335,7 +194,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
             for (uint32_t nt = 0; nt < n_col_tiles && ok; ++nt) {
                 for (uint32_t kb = 0; kb < nkb; ++kb, ++kbt) {
                     const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
-                    if (!mbar_wait(&ctrl->full[s], ph, p.error, 4)) {
+                    if (!mbar_wait(&ctrl->full[s], ph, wctx, 4)) {
                         ok = false;
                         break;
                     }
@@ -365,24 +224,24 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                 }
             }
         }
-    } else if (warp < 10 || MODE == MODE_PRUNE) {
+    } else if (warp < 10 || kTiled) {
         // ---------------------------------------------------------------- epilogue
         // First-test mode: eight warps, two per quarter of the tile's rows; warps 6-9 take columns 0-127 of
         // every 256-column tile, warps 10-13 columns 128-255, each with a candidate list of its own.
-        const uint32_t half = (MODE == MODE_PRUNE) ? static_cast<uint32_t>(warp - 6) >> 2 : 0u;
+        const uint32_t half = kTiled ? static_cast<uint32_t>(warp - 6) >> 2 : 0u;
         const uint32_t lane_base = 32u * (warp & 3);    // tensor-memory lanes this warp may read
         const uint32_t row_in_tile = lane_base + lane;
         uint32_t t = 0;
         bool ok = true;
         for (size_t rt = rt_begin + blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {
-            const size_t row = rt * BM + row_in_tile;
+            const size_t row = tile_of(rt) * BM + row_in_tile;
             const bool row_valid = row < p.n;
             // Best and runner-up of the tensor-core distances.  They are only candidates: the accumulator
             // in tensor memory truncates, which biases long sums by up to ~1e-5 relative, so the winner and
             // its distance are settled afterwards in fp32 by refine_top2_kernel.
             float nx = 0.f, d1 = FLT_MAX, d2 = FLT_MAX;
             uint32_t i1 = 0, i2 = 0xFFFFFFFFu;
-            if ((MODE == MODE_ARGMIN || MODE == MODE_PRUNE) && row_valid) nx = p.norms_x[row];
+            if ((MODE == MODE_ARGMIN || kTiled) && row_valid) nx = p.norms_x[row];
             // first-test epilogue: this warp's 32 rows share one candidate list; `filled` is warp-uniform
             float thr = -FLT_MAX;
             uint32_t filled = 0;
@@ -394,6 +253,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                 my_offs = p.list_offs + group * ((p.k + 1023) / 1024 + 1);
                 if (row_valid && !(p.skip && p.skip[row])) thr = p.best_in[row] * p.ratio_first;
             }
+            uint32_t* my_union = nullptr;
+            if (MODE == MODE_UNION) {
+                my_union = p.union_bits + (rt - rt_begin) * static_cast<size_t>(p.union_words);
+                // The union must contain every pair that the chain kernel's own first test will pass.  That test uses the
+                // same products but norms summed in another order (a few 1e-8 apart), so the threshold is widened a little.
+                if (row_valid && !(p.skip && p.skip[row])) {
+                    const float t0 = p.best_in[row] * p.ratio_first;
+                    thr = fmaf(t0, 1e-4f, t0) + 1e-6f * nx;
+                }
+            }
             for (uint32_t nt = 0; nt < n_col_tiles && ok; ++nt, ++t) {
                 const uint32_t b = t & 1u, tph = (t >> 1) & 1u;
                 const size_t col0 = static_cast<size_t>(nt) * BN;
@@ -404,20 +273,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                     for (int j = lane; j < BN; j += 32) ny[j] = (col0 + j < p.k) ? __ldg(p.norms_y + col0 + j) : 0.f;
                     __syncwarp();
                 }
-                if (MODE == MODE_PRUNE) {
+                if (kTiled) {
                     // the two warps of a row quarter fill (and read) disjoint halves of the shared copy
                     for (int j = half * (BN / 2) + lane; j < static_cast<int>((half + 1) * (BN / 2)); j += 32) ny[j] = (col0 + j < p.k) ? __ldg(p.norms_y + col0 + j) : 0.f;
                     __syncwarp();
                 }
                 // warp-uniform outcome: the tensor-memory loads below must be executed by the whole warp
-                if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->tmem_full[b], tph, p.error, 5))) {
+                if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->tmem_full[b], tph, wctx, 5))) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + (lane_base << 16) + b * BN;
-                const int ch_begin = (MODE == MODE_PRUNE) ? static_cast<int>(half) * (BN / 64) : 0;
-                const int ch_end = (MODE == MODE_PRUNE) ? ch_begin + BN / 64 : BN / 32;
+                const int ch_begin = kTiled ? static_cast<int>(half) * (BN / 64) : 0;
+                const int ch_end = kTiled ? ch_begin + BN / 64 : BN / 32;
 #pragma unroll 1
                 for (int ch = ch_begin; ch < ch_end; ++ch) {
                     uint32_t r[32];
@@ -441,6 +310,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                                 }
                             }
                         }
+                    } else if (MODE == MODE_UNION) {
+                        // first test for 32 centroids; only which centroids pass for ANY row of the tile is kept
+                        uint32_t mask = 0;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 nyv = *reinterpret_cast<const float4*>(ny + ch * 32 + j);
+                            const float p0 = fmaf(-2.0f, __uint_as_float(r[j + 0]), nx) + nyv.x;
+                            const float p1 = fmaf(-2.0f, __uint_as_float(r[j + 1]), nx) + nyv.y;
+                            const float p2 = fmaf(-2.0f, __uint_as_float(r[j + 2]), nx) + nyv.z;
+                            const float p3 = fmaf(-2.0f, __uint_as_float(r[j + 3]), nx) + nyv.w;
+                            mask |= (p0 < thr ? (1u << j) : 0u) | (p1 < thr ? (2u << j) : 0u) | (p2 < thr ? (4u << j) : 0u) | (p3 < thr ? (8u << j) : 0u);
+                        }
+                        const size_t first = col0 + static_cast<size_t>(ch) * 32;
+                        const uint32_t n_valid = first >= p.k ? 0u : static_cast<uint32_t>(min(static_cast<size_t>(32), p.k - first));
+                        mask &= n_valid >= 32u ? 0xFFFFFFFFu : ((1u << n_valid) - 1u);
+                        const uint32_t any = __reduce_or_sync(0xffffffffu, mask);
+                        if (any != 0 && lane == 0) atomicOr(my_union + (first >> 5), any);
                     } else if (MODE == MODE_PRUNE) {
                         // test of the first checkpoint for 32 centroids, then a warp scan places every row's
                         // survivors behind those of the lower lanes
@@ -576,6 +462,7 @@ struct ChainParams {
     uint32_t* not_pruned;
     uint2* top2;                    // out: the two smallest final distances seen by the chain, per point
     int* error;
+    long long wait_limit;
 };
 
 struct SegInfo {
@@ -680,6 +567,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
     uint8_t* smem = smem_raw + pad;
     const uint32_t smem_base = raw_addr + pad;
     ChainCtrl* ctrl = reinterpret_cast<ChainCtrl*>(smem + STAGES * STAGE_BYTES);
+    const WaitCtx wctx{p.error, p.wait_limit};
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -720,7 +608,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
                 const int yrow = static_cast<int>(c0 + static_cast<size_t>(unit) * BN);
                 for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
                     const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
-                    if (!mbar_wait(&ctrl->empty[s], ph ^ 1u, p.error, 11)) {
+                    if (!mbar_wait(&ctrl->empty[s], ph ^ 1u, wctx, 11)) {
                         ok = false;
                         break;
                     }
@@ -741,7 +629,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
             bool ok = true;
             CHAIN_FOR_EACH_UNIT_SEGMENT({
                 // the rows must have read this accumulator's previous checkpoint before it grows (or restarts)
-                if (uses[a] > 0 && !mbar_wait(&ctrl->acc_loaded[a], (uses[a] - 1) & 1u, p.error, 12)) {
+                if (uses[a] > 0 && !mbar_wait(&ctrl->acc_loaded[a], (uses[a] - 1) & 1u, wctx, 12)) {
                     ok = false;
                     break;
                 }
@@ -749,7 +637,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
                 const uint32_t acc = tmem_base + a * BN;
                 for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
                     const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
-                    if (!mbar_wait(&ctrl->conv[s], ph, p.error, 13)) {
+                    if (!mbar_wait(&ctrl->conv[s], ph, wctx, 13)) {
                         ok = false;
                         break;
                     }
@@ -779,7 +667,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
         CHAIN_FOR_EACH_UNIT_SEGMENT({
             for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
                 const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
-                if (!mbar_wait(&ctrl->full[s], ph, p.error, 14)) {
+                if (!mbar_wait(&ctrl->full[s], ph, wctx, 14)) {
                     ok = false;
                     break;
                 }
@@ -848,7 +736,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
             ctrl->xchg[slot][half][row_in_tile] = mine;
             __threadfence_block();
             mbar_arrive(&ctrl->xchg_bar);
-            if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->xchg_bar, xchg_uses & 1u, p.error, 16))) return false;
+            if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->xchg_bar, xchg_uses & 1u, wctx, 16))) return false;
             ++xchg_uses;
             const ChainPartial other = ctrl->xchg[slot][half ^ 1u][row_in_tile];
             const uint32_t cnt_all = cnt + other.cnt;
@@ -935,7 +823,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
                 for (uint32_t q = 0; q < HS; ++q) ny[half * (BN / 2) + q * 32 + lane] = cur[q];
                 __syncwarp();
             }
-            if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->acc_ready[a], uses[a] & 1u, p.error, 15))) {
+            if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->acc_ready[a], uses[a] & 1u, wctx, 15))) {
                 ok = false;
                 break;
             }
@@ -1054,8 +942,10 @@ __global__ void __launch_bounds__(CHAIN_THREADS, 1) chain_tc_kernel(const __grid
 // winner and to the two runner-ups; the smallest wins, the winner keeps its place on ties.
 __global__ void __launch_bounds__(256) refine_chain_kernel(const float* __restrict__ x, const float* __restrict__ y, size_t n, size_t k, size_t d,
                                                            const uint2* __restrict__ top2, uint32_t* __restrict__ knn, float* __restrict__ dist,
-                                                           const int* __restrict__ error) {
-    const size_t row = static_cast<size_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+                                                           const int* __restrict__ error, const uint32_t* __restrict__ tile_map) {
+    // with a tile map the grid covers the rows of the listed 128-row tiles, else rows 0 .. n-1
+    size_t row = static_cast<size_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (tile_map) row = static_cast<size_t>(tile_map[row / BM]) * BM + (row % BM);
     if (row >= n) return;
     // a chain kernel that gave up on a wait leaves its outputs unwritten: nothing to refine, and no index to trust
     if (*reinterpret_cast<const volatile int*>(error) != 0) return;
@@ -1250,16 +1140,20 @@ void launch(const CUtensorMap& tx, const CUtensorMap& ty, const CUtensorMap& tyl
 
 bool g_enabled = true;
 uint32_t g_debug_producer_stop = 0;
+long long g_wait_limit = WAIT_LIMIT_CYCLES;
 
 } // namespace
 
+long long wait_limit() { return g_wait_limit; }
+
 void set_debug_wait_injection(long long wait_limit_cycles, uint32_t producer_stops_after_kblocks) {
-    const long long v = wait_limit_cycles > 0 ? wait_limit_cycles : WAIT_LIMIT_CYCLES;
-    SKM_CUDA(cudaMemcpyToSymbol(g_wait_limit_cycles, &v, sizeof(v)));
+    g_wait_limit = wait_limit_cycles > 0 ? wait_limit_cycles : WAIT_LIMIT_CYCLES;
     g_debug_producer_stop = producer_stops_after_kblocks;
 }
 
 void launch_presplit(const float* y, size_t rows, size_t ld, float* y_split, cudaStream_t stream) { presplit(y, rows, ld, y_split, stream); }
+
+CUtensorMap make_row_major_tmap(const float* base, size_t extent, size_t rows, size_t ld, uint32_t box_rows) { return make_tmap(base, extent, rows, ld, box_rows); }
 
 int* error_word() {
     int device = 0;
@@ -1297,6 +1191,7 @@ void launch_assign_full(const float* x, const float* y, size_t n, size_t k, size
     p.out_dist = out_dist;
     p.out_top2 = top2_scratch;
     p.error = error_flag(device);
+    p.wait_limit = g_wait_limit;
     p.debug_producer_stop = g_debug_producer_stop;
     launch<MODE_ARGMIN>(tx, ty, tylo, p, stream);
     refine_top2_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, k, d, norms_x, norms_y, top2_scratch, out_knn, out_dist, p.error);
@@ -1319,6 +1214,7 @@ void launch_assign_full_flagged(const float* x, const float* y, size_t n, size_t
     p.out_dist = out_dist;
     p.out_top2 = top2_scratch;
     p.error = error_word;
+    p.wait_limit = g_wait_limit;
     launch<MODE_ARGMIN>(tx, ty, ty, p, stream);
     refine_top2_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, k, d, norms_x, norms_y, top2_scratch, out_knn, out_dist, p.error);
     note_kernel_launch();
@@ -1327,7 +1223,7 @@ void launch_assign_full_flagged(const float* x, const float* y, size_t n, size_t
 
 void launch_first_test(const float* x, const float* y, size_t n, size_t k, size_t d, uint32_t partial_d, const float* norms_x, const float* norms_y, const float* best_in,
                        const uint32_t* skip, float ratio_first, size_t tile0, size_t n_tiles, uint2* lists, uint32_t* list_offs, uint32_t cap_group, cudaStream_t stream,
-                       const float* y_split) {
+                       const float* y_split, const uint32_t* tile_map) {
     if (n_tiles == 0 || k == 0) return;
     int device = 0;
     SKM_CUDA(cudaGetDevice(&device));
@@ -1342,6 +1238,7 @@ void launch_first_test(const float* x, const float* y, size_t n, size_t k, size_
     p.norms_x = norms_x;
     p.norms_y = norms_y;
     p.error = error_flag(device);
+    p.wait_limit = g_wait_limit;
     p.tile0 = tile0;
     p.n_tiles = n_tiles;
     p.best_in = best_in;
@@ -1350,9 +1247,41 @@ void launch_first_test(const float* x, const float* y, size_t n, size_t k, size_
     p.lists = lists;
     p.list_offs = list_offs;
     p.cap_group = cap_group;
+    p.tile_map = tile_map;
     SKM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<MODE_PRUNE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES)));
     const int grid = static_cast<int>(std::min<size_t>(n_tiles, static_cast<size_t>(sm_count(device))));
     gemm_tc_kernel<MODE_PRUNE><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, ty, tylo, p);
+    note_kernel_launch();
+    SKM_CUDA(cudaGetLastError());
+}
+
+void launch_union(const float* x, size_t n, size_t k, size_t d, uint32_t partial_d, const float* norms_x, const float* norms_y, const float* best_in, float ratio_first,
+                  const uint32_t* tile_map, size_t n_tiles, uint32_t* union_bits, uint32_t union_words, const float* y_split, cudaStream_t stream) {
+    if (n_tiles == 0 || k == 0) return;
+    int device = 0;
+    SKM_CUDA(cudaGetDevice(&device));
+    const CUtensorMap tx = make_tmap(x, partial_d, n, d, BM);
+    const CUtensorMap ty = make_tmap(y_split, partial_d, k, d, BN);
+    const CUtensorMap tylo = make_tmap(y_split + k * d, partial_d, k, d, BN);
+    Params p{};
+    p.y_presplit = true;
+    p.n = n;
+    p.k = k;
+    p.kdim = partial_d;
+    p.norms_x = norms_x;
+    p.norms_y = norms_y;
+    p.error = error_flag(device);
+    p.wait_limit = g_wait_limit;
+    p.tile0 = 0;
+    p.n_tiles = n_tiles;
+    p.best_in = best_in;
+    p.ratio_first = ratio_first;
+    p.tile_map = tile_map;
+    p.union_bits = union_bits;
+    p.union_words = union_words;
+    SKM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<MODE_UNION>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES)));
+    const int grid = static_cast<int>(std::min<size_t>(n_tiles, static_cast<size_t>(sm_count(device))));
+    gemm_tc_kernel<MODE_UNION><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, ty, tylo, p);
     note_kernel_launch();
     SKM_CUDA(cudaGetLastError());
 }
@@ -1370,6 +1299,7 @@ void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, floa
     p.out = out;
     p.ldo = ldo;
     p.error = error_flag(device);
+    p.wait_limit = g_wait_limit;
     launch<MODE_STORE>(tx, ty, ty, p, stream);
 }
 
@@ -1405,13 +1335,24 @@ void launch_chain(const float* x, const float* y, size_t n, size_t k, size_t d, 
     p.not_pruned = not_pruned;
     p.top2 = top2_scratch;
     p.error = error_flag(device);
+    p.wait_limit = g_wait_limit;
     SKM_CUDA(cudaFuncSetAttribute(chain_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(C_SMEM_BYTES)));
     const size_t row_tiles = (n + BM - 1) / BM;
     const int grid = static_cast<int>(std::min<size_t>(row_tiles, static_cast<size_t>(sm_count(device))));
     chain_tc_kernel<<<grid, CHAIN_THREADS, C_SMEM_BYTES, stream>>>(maps, p);
     note_kernel_launch();
     SKM_CUDA(cudaGetLastError());
-    refine_chain_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, k, d, top2_scratch, knn, dist, p.error);
+    refine_chain_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, stream>>>(x, y, n, k, d, top2_scratch, knn, dist, p.error, nullptr);
+    note_kernel_launch();
+    SKM_CUDA(cudaGetLastError());
+}
+
+void launch_refine_chain_tiles(const float* x, const float* y, size_t n, size_t k, size_t d, const uint2* top2, uint32_t* knn, float* dist, const uint32_t* tile_map,
+                               size_t n_tiles, cudaStream_t stream) {
+    if (n_tiles == 0) return;
+    int device = 0;
+    SKM_CUDA(cudaGetDevice(&device));
+    refine_chain_kernel<<<static_cast<unsigned>(n_tiles * (BM / 8)), 256, 0, stream>>>(x, y, n, k, d, top2, knn, dist, error_flag(device), tile_map);
     note_kernel_launch();
     SKM_CUDA(cudaGetLastError());
 }

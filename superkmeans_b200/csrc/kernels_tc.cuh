@@ -38,7 +38,32 @@ void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, floa
 // of entries before every 1024-centroid chunk and the total (which exceeds cap_group on overflow).
 void launch_first_test(const float* x, const float* y, size_t n, size_t k, size_t d, uint32_t partial_d, const float* norms_x, const float* norms_y, const float* best_in,
                        const uint32_t* skip, float ratio_first, size_t tile0, size_t n_tiles, uint2* lists, uint32_t* list_offs, uint32_t cap_group, cudaStream_t stream,
-                       const float* y_split = nullptr);   // y already split by launch_presplit, optional
+                       const float* y_split = nullptr,   // y already split by launch_presplit, optional
+                       const uint32_t* tile_map = nullptr);   // optional: entry t of the range stands for row tile tile_map[t]; lists stay indexed by t
+
+// The same first test (threshold widened by 1e-4 relative) for the row tiles tile_map[0 .. n_tiles), keeping only its
+// footprint: bit c of union_bits[t * union_words + c / 32] is set (atomic OR into zeroed memory) when some row of tile t
+// passes the test against centroid c.  y_split: the centroids split by launch_presplit.
+void launch_union(const float* x, size_t n, size_t k, size_t d, uint32_t partial_d, const float* norms_x, const float* norms_y, const float* best_in, float ratio_first,
+                  const uint32_t* tile_map, size_t n_tiles, uint32_t* union_bits, uint32_t union_words, const float* y_split, cudaStream_t stream);
+
+// Pruned assignment of the row tiles tile_map[0 .. n_tiles) as a chain over the centroids their union bits name
+// (kernels_tc_sparse.cu).  For every listed tile and 1024-centroid chunk, cols[t * cols_stride + chunk * 1024 ..] holds
+// the col_counts[t * n_chunks + chunk] local indices (ascending) of the chunk's centroids that can pass the first test for
+// some row of the tile; all other centroids are skipped, which cannot change the result.  Other arguments as for
+// launch_chain; y_split must already hold the split centroids.  Rows of listed tiles whose every chunk is empty keep
+// what knn / dist / not_pruned / top2 held on entry.
+void launch_sparse_chain(const float* x, size_t n, size_t k, size_t d, uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d, const float* chain_norms_x,
+                         const float* chain_norms_y, const float* ratios, const float* best_in, uint32_t* knn, float* dist, uint32_t* not_pruned, uint2* top2_scratch,
+                         const float* y_split, const uint32_t* tile_map, size_t n_tiles, const uint16_t* cols, const uint32_t* col_counts, size_t cols_stride,
+                         cudaStream_t stream);
+// cols / col_counts from union bits: one warp per (tile, chunk); *total_cols += columns listed (rounded up to the 16 the
+// tensor cores process), for work accounting.
+void launch_build_cols(const uint32_t* union_bits, uint32_t union_words, size_t n_tiles, size_t k, uint16_t* cols, uint32_t* col_counts, size_t cols_stride,
+                       unsigned long long* total_cols, cudaStream_t stream);
+// Exact fp32 refinement of the chain's winner and runner-ups (see launch_chain) for the rows of the listed tiles only.
+void launch_refine_chain_tiles(const float* x, const float* y, size_t n, size_t k, size_t d, const uint2* top2, uint32_t* knn, float* dist, const uint32_t* tile_map,
+                               size_t n_tiles, cudaStream_t stream);
 
 // Pruned assignment for all n points as a dense ADSampling chain on the tensor cores.  chain_norms_x /
 // chain_norms_y hold, per row, the cumulative squared norm after each of the chain's checkpoints
@@ -49,7 +74,10 @@ void launch_chain(const float* x, const float* y, size_t n, size_t k, size_t d, 
                   const float* chain_norms_y, const float* ratios, const float* best_in, uint32_t* knn, float* dist, uint32_t* not_pruned, uint2* top2_scratch,
                   float* y_split, cudaStream_t stream);   // y_split: 2 * k * d floats of scratch for the tf32 parts of the centroids
 
-// Test hook for the bounded waits, current device: every wait of the tensor-core kernels gives up after
+// SM cycles after which a wait inside a tensor-core kernel gives up (about two seconds unless a test shortened it).
+long long wait_limit();
+
+// Test hook for the bounded waits: every wait of the tensor-core kernels gives up after
 // wait_limit_cycles SM cycles (0 restores the default of about two seconds), and the TMA producer of the exact
 // assignment kernel stops after producer_stops_after_kblocks k-blocks (0 = never), so that the other roles wait
 // for tiles that never arrive.  The kernel then returns with an error code that fetch_error reports.

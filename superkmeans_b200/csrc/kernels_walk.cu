@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(kWalkThreads, kWalkCtasPerSm) walk_lists_kerne
     unsigned long long steps_done = 0;
 
     for (size_t tile = blockIdx.x; tile < w.n_tiles; tile += gridDim.x) {
-        const size_t row0 = (w.tile0 + tile) * kTileM;
+        const size_t row0 = (w.tile_map ? static_cast<size_t>(w.tile_map[tile]) : w.tile0 + tile) * kTileM;
         if (tid < kTileM) {
             const size_t row = row0 + tid;
             const uint32_t overflow = (w.list_offs[(tile * 8 + (tid >> 5)) * (n_chunks + 1) + n_chunks] > w.cap_group ||

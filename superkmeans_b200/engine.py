@@ -142,6 +142,12 @@ class Engine:
         check(lib.skm_get_prune_counters(self._h, out), self._h)
         return {"dense_rows": int(out[0]), "walk_pair_steps": int(out[1]), "overflow_rows": int(out[2])}
 
+    def chain_counters(self) -> dict:
+        """Work of the chain over gathered centroids so far: rows of its tiles, centroid columns of its units (see skm_get_chain_counters)."""
+        out = (C.c_uint64 * 2)()
+        check(lib.skm_get_chain_counters(self._h, out), self._h)
+        return {"rows": int(out[0]), "columns": int(out[1])}
+
     @property
     def last_objective_f64(self) -> float:
         return float(lib.skm_last_objective_f64(self._h))
@@ -222,7 +228,9 @@ def tensor_cores_enabled() -> bool:
 
 
 def set_prune_split(mode: int) -> None:
-    """0 = automatic, 1 = SIMT candidate lists, 2 = dense SIMT chain, 3 = tensor-core chain, 4 = tensor-core first test + list walk, 5 = as 4 with small lists (see skm_set_prune_split)."""
+    """0 = automatic (ordered points, per-tile route), 1 = SIMT candidate lists, 2 = dense SIMT chain, 3 = dense tensor-core chain, 4 = tensor-core first
+    test + list walk, 5 = as 4 with small lists, 6 = ordered points + gathered chain, 7 = ordered points + lists, 8 = as 7 with small lists, 9 = automatic
+    without ordering (see skm_set_prune_split)."""
     lib.skm_set_prune_split(int(mode))
 
 
