@@ -169,7 +169,10 @@ skm_status skm_trace_get(const skm_handle* h, uint64_t idx, uint64_t* n_samples,
  * (include/superkmeans/profiler.h, SKM_PROFILE_SCOPE names): 0 rotator, 1 norms_calc,
  * 2 search/1st_blas (exact assignment), 3 search (pruned assignment), 4 update_centroids,
  * 5 consolidate, 6 shift, 7 whole Train call; parts of phase 3: 8 first ADSampling test on the tensor cores,
- * 9 candidate-list walk, 10 dense chain (the points, or all points, that are cheaper without lists). */
+ * 9 candidate-list walk, 10 chains (union pass, chain over gathered centroids, dense chain, their refinement);
+ * 11 device allocation and release (host wall clock), 12 initial centroids (Forgy shuffle, row gather, rotation),
+ * 13 sums across shards (the span of the collective on the stream, which includes waiting for the slowest shard),
+ * 14 reserved. */
 skm_status skm_get_phase_time(const skm_handle* h, int phase, double* ms, uint64_t* calls);
 skm_status skm_reset_phase_times(skm_handle* h);
 /* Process-wide choice between the tcgen05 tensor-core kernels (1, default) and the fp32 SIMT kernels
@@ -207,6 +210,32 @@ uint64_t skm_device_allocations(void);
  * of n_global rows; per-iteration sums, counts and scalars are combined through `fn`.  The
  * reference has no counterpart (single process). */
 skm_status skm_set_shard(skm_handle* h, uint64_t n_global, uint64_t row_offset, skm_allreduce_fn fn, void* user);
+
+/* The same with the sums done by NCCL inside this library, on the engine's own stream and as one launch per
+ * iteration (k x d sums, k counts and two scalars in one NCCL group): no callback, no host synchronisation around the
+ * collective, no Python.  NCCL is opened at run time (libnccl.so.2 from the loader's search path or $SKM_NCCL_LIB);
+ * there is no link-time dependency.  One rank calls skm_comm_unique_id and passes the 128 bytes to every rank by
+ * whatever means the application has (MPI, a file, torch.distributed); every rank then calls skm_comm_create (a
+ * collective) with the device it trains on.  skm_comm_wrap adopts an ncclComm_t that the application already owns.
+ * A communicator outlives the handles that use it and is destroyed by the caller.  No counterpart in the reference. */
+typedef struct skm_comm skm_comm;
+#define SKM_COMM_ID_BYTES 128
+skm_status skm_comm_unique_id(uint8_t* id_out);
+skm_status skm_comm_create(const uint8_t* id, int rank, int world, int device, skm_comm** out);
+skm_status skm_comm_wrap(void* nccl_comm, int rank, int world, skm_comm** out);
+void skm_comm_destroy(skm_comm* comm);
+skm_status skm_set_shard_comm(skm_handle* h, uint64_t n_global, uint64_t row_offset, skm_comm* comm);
+
+/* Workspace cache (off by default).  When on, device buffers of 32 MB and more that a handle releases (the rotated
+ * copy of the training rows, sort and list workspaces) are kept by the library and reused by later calls that need
+ * about the same size on the same GPU, so that repeated Train calls of one shape do not pay cudaMalloc / cudaFree of
+ * tens of gigabytes (both synchronise the device) every time.  The memory stays with the library until
+ * skm_release_cached_memory, skm_set_workspace_cache(0) or the end of the process; an allocation that fails drops the
+ * cache and retries.  No counterpart in the reference. */
+void skm_set_workspace_cache(int enabled);
+int skm_get_workspace_cache(void);
+void skm_release_cached_memory(void);
+uint64_t skm_cached_memory_bytes(void);
 
 /* ---- single operators of the path, for callers that hold their own state and for parity tests.
  * All arguments in host memory; each call uploads, runs the kernels and downloads. ------------- */

@@ -104,6 +104,15 @@ SIGNATURES = {
     "skm_set_tensor_cores": (None, [C.c_int]),
     "skm_get_tensor_cores": (C.c_int, []),
     "skm_set_shard": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, ALLREDUCE_FN, C.c_void_p]),
+    "skm_comm_unique_id": (C.c_int, [C.c_void_p]),
+    "skm_comm_create": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
+    "skm_comm_wrap": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
+    "skm_comm_destroy": (None, [C.c_void_p]),
+    "skm_set_shard_comm": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p]),
+    "skm_set_workspace_cache": (None, [C.c_int]),
+    "skm_get_workspace_cache": (C.c_int, []),
+    "skm_release_cached_memory": (None, []),
+    "skm_cached_memory_bytes": (C.c_uint64, []),
     "skm_op_rotate": (C.c_int, [C.c_int, f32p, f32p, C.c_uint64, C.c_uint64, f32p]),
     "skm_op_unrotate": (C.c_int, [C.c_int, f32p, f32p, C.c_uint64, C.c_uint64, f32p]),
     "skm_op_find_nearest": (C.c_int, [C.c_int, f32p, f32p, C.c_uint64, C.c_uint64, C.c_uint64, u32p, f32p]),

@@ -11,6 +11,10 @@
 
 using skmb::Engine;
 
+struct skm_comm {
+    std::unique_ptr<skmb::NcclComm> comm;
+};
+
 struct skm_handle {
     std::unique_ptr<Engine> engine;
     mutable std::string err;
@@ -235,6 +239,47 @@ skm_status skm_set_shard(skm_handle* h, uint64_t n_global, uint64_t row_offset, 
     SKM_NEED(h);
     return guarded(h->err, [&] { h->engine->set_shard(n_global, row_offset, fn, user); });
 }
+
+skm_status skm_comm_unique_id(uint8_t* id_out) {
+    g_create_error.clear();
+    if (!id_out) return SKM_INVALID_ARGUMENT;
+    return guarded(g_op_error, [&] { skmb::NcclComm::unique_id(id_out); });
+}
+
+skm_status skm_comm_create(const uint8_t* id, int rank, int world, int device, skm_comm** out) {
+    g_create_error.clear();
+    if (!id || !out) return SKM_INVALID_ARGUMENT;
+    *out = nullptr;
+    auto c = std::make_unique<skm_comm>();
+    skm_status st = guarded(g_op_error, [&] { c->comm.reset(skmb::NcclComm::create(id, rank, world, device)); });
+    if (st == SKM_RUNTIME_ERROR) st = SKM_COMM_ERROR;
+    if (st == SKM_OK) *out = c.release();
+    return st;
+}
+
+skm_status skm_comm_wrap(void* nccl_comm, int rank, int world, skm_comm** out) {
+    g_create_error.clear();
+    if (!out) return SKM_INVALID_ARGUMENT;
+    *out = nullptr;
+    auto c = std::make_unique<skm_comm>();
+    skm_status st = guarded(g_op_error, [&] { c->comm.reset(skmb::NcclComm::wrap(nccl_comm, rank, world)); });
+    if (st == SKM_RUNTIME_ERROR) st = SKM_COMM_ERROR;
+    if (st == SKM_OK) *out = c.release();
+    return st;
+}
+
+void skm_comm_destroy(skm_comm* comm) { delete comm; }
+
+skm_status skm_set_shard_comm(skm_handle* h, uint64_t n_global, uint64_t row_offset, skm_comm* comm) {
+    SKM_NEED(h);
+    if (!comm || !comm->comm) return SKM_INVALID_ARGUMENT;
+    return guarded(h->err, [&] { h->engine->set_shard_nccl(n_global, row_offset, comm->comm.get()); });
+}
+
+void skm_set_workspace_cache(int enabled) { skmb::set_workspace_cache(enabled != 0); }
+int skm_get_workspace_cache(void) { return skmb::workspace_cache_enabled() ? 1 : 0; }
+void skm_release_cached_memory(void) { skmb::release_cached_memory(); }
+uint64_t skm_cached_memory_bytes(void) { return skmb::cached_memory_bytes(); }
 
 // ---- operators ------------------------------------------------------------------------------
 skm_status skm_op_rotate(int device, const float* m, const float* x, uint64_t n, uint64_t d, float* out) {

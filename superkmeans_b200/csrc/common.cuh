@@ -28,6 +28,20 @@ void note_kernel_launch();
 // cudaMallocHost goes through DeviceBuffer, PinnedBuffer or a site that calls note_device_alloc).
 unsigned long long device_alloc_count();
 void note_device_alloc();
+
+// Device memory of DeviceBuffer.  With the workspace cache switched on (off by default), blocks of 32 MB and more are
+// kept when released and handed out again to later requests of about the same size on the same device, so that
+// repeated Train calls of one shape do not pay cudaMalloc / cudaFree (both synchronise the device, and both take
+// tens of milliseconds at tens of gigabytes) every time.  The price: the memory stays with this library until
+// release_cached_memory() or the end of the process.
+void* device_alloc(size_t bytes);
+void device_free(void* p, size_t bytes);
+void set_workspace_cache(bool on);
+bool workspace_cache_enabled();
+void release_cached_memory();
+size_t cached_memory_bytes();
+// wall-clock milliseconds this thread has spent inside cudaMalloc / cudaFree through device_alloc / device_free
+double alloc_free_ms();
 // After every kernel launch: count it and surface launch-configuration errors.
 #define SKM_LAUNCH_CHECK()                                                                         \
     do {                                                                                           \
@@ -220,7 +234,7 @@ void launch_pdxify(const float* c, float* pdx, float* aux, size_t k, size_t d, s
 // *out = sum_c ||a[c] - b[c]||^2
 void launch_shift(const float* a, const float* b, size_t k, size_t d, double* block_sums, double* out, cudaStream_t stream);
 
-// out[i][:] = in[idx[i]][:]
+// out[i][:] = in[idx[i]][:]; an index of all ones gives a row of zeros
 void launch_gather_rows(const float* in, const uint64_t* idx, float* out, size_t n_out, size_t d, cudaStream_t stream);
 void launch_gather_f32(const float* in, const uint64_t* idx, float* out, size_t n_out, cudaStream_t stream);
 // out[idx[i]] = in[i] + offset

@@ -8,6 +8,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <future>
 #include <iostream>
 #include <numeric>
 #include <random>
@@ -210,14 +211,45 @@ void Engine::set_shard(size_t n_global, size_t row_offset, skm_allreduce_fn fn, 
     shard_row_offset_ = row_offset;
     allreduce_fn_ = fn;
     allreduce_user_ = user;
+    comm_ = nullptr;
 }
 
+void Engine::set_shard_nccl(size_t n_global, size_t row_offset, NcclComm* comm) {
+    shard_n_global_ = n_global;
+    shard_row_offset_ = row_offset;
+    allreduce_fn_ = nullptr;
+    allreduce_user_ = nullptr;
+    comm_ = comm;
+}
+
+// Sum of one buffer across the shards.  Through NCCL the sum is enqueued on the engine's stream and nothing waits on the
+// host; through the callback the stream is drained first (the callback works on its own stream).
 void Engine::allreduce(void* buf, size_t count, int dtype) {
-    if (!allreduce_fn_) return;
+    if (!sharded_()) return;
+    PhaseScope ps(*this, PH_ALLREDUCE);
+    if (comm_) {
+        comm_->allreduce_group(dtype == 0 ? static_cast<float*>(buf) : nullptr, dtype == 0 ? count : 0, dtype == 2 ? static_cast<uint32_t*>(buf) : nullptr, dtype == 2 ? count : 0,
+                               dtype == 1 ? static_cast<double*>(buf) : nullptr, dtype == 1 ? count : 0, stream_);
+        return;
+    }
     sync();
     if (allreduce_fn_(allreduce_user_, buf, count, dtype) != 0) {
         throw std::runtime_error("all-reduce callback reported a failure");
     }
+}
+
+// The per-iteration sum (superkmeans.h:729-765 run on every shard): k x d row sums, k counts and two scalars.  One NCCL
+// group, hence one launch, when a communicator is set; three callback calls otherwise.
+void Engine::allreduce_iteration(float* sums, size_t n_sums, uint32_t* counts, size_t n_counts, double* scalars, size_t n_scalars) {
+    if (!sharded_()) return;
+    if (comm_) {
+        PhaseScope ps(*this, PH_ALLREDUCE);
+        comm_->allreduce_group(sums, n_sums, counts, n_counts, scalars, n_scalars, stream_);
+        return;
+    }
+    allreduce(sums, n_sums, 0);
+    allreduce(counts, n_counts, 2);
+    allreduce(scalars, n_scalars, 1);
 }
 
 // dst[n x d] (device) = rotate(src).  Host sources are streamed through two staging buffers so
@@ -288,44 +320,44 @@ void Engine::prepare_update_workspace(size_t n, size_t k) {
 // -------------------------------------------------------------------------------------------------
 // Initial centroids (superkmeans.h:1100-1142): Forgy rows, optionally rotated, into c_prev_.
 // -------------------------------------------------------------------------------------------------
-void Engine::generate_centroids_from_host(const float* data, bool on_device, size_t n_points_global, size_t k_cur, bool rotate) {
-    const std::vector<size_t> idx = forgy_indices(n_points_global, k_cur, cfg_.seed);
-    DeviceBuffer<float> raw;
-    raw.ensure(k_cur * d_);
-    const bool sharded = allreduce_fn_ != nullptr;
+void Engine::generate_centroids_from_host(const float* data, bool on_device, size_t n_points_global, size_t k_cur, bool rotate, const std::vector<size_t>* precomputed) {
+    PhaseScope ps(*this, PH_INIT_CENTROIDS);
+    std::vector<size_t> own;
+    if (!precomputed) own = forgy_indices(n_points_global, k_cur, cfg_.seed);
+    const std::vector<size_t>& idx = precomputed ? *precomputed : own;
+    float* raw = init_raw_.ensure(k_cur * d_);
+    const bool sharded = sharded_();
     const size_t n_local = n_samples_;
-    if (on_device && !sharded) {
-        std::vector<uint64_t> idx64(idx.begin(), idx.end());
-        DeviceBuffer<uint64_t> idx_dev;
-        SKM_CUDA(cudaMemcpyAsync(idx_dev.ensure(k_cur), idx64.data(), sizeof(uint64_t) * k_cur, cudaMemcpyHostToDevice, stream_));
-        launch_gather_rows(data, idx_dev.get(), raw.get(), k_cur, d_, stream_);
-        sync();
-    } else {
-        // Rows owned by other shards stay zero and arrive through the sum all-reduce.
-        std::vector<float> host(k_cur * d_, 0.0f);
+    if (on_device) {
+        // Rows this shard holds are gathered by a kernel; rows of other shards stay zero and arrive through the sum.
+        uint64_t* idx_host = init_idx_host_.ensure(k_cur);
+        const uint64_t none = ~uint64_t{0};
         for (size_t i = 0; i < k_cur; ++i) {
             size_t g = idx[i];
-            if (sharded) {
-                if (g < shard_row_offset_ || g >= shard_row_offset_ + n_local) continue;
-                g -= shard_row_offset_;
-            }
-            if (on_device) {
-                SKM_CUDA(cudaMemcpy(&host[i * d_], data + g * d_, sizeof(float) * d_, cudaMemcpyDeviceToHost));
-            } else {
-                std::memcpy(&host[i * d_], data + g * d_, sizeof(float) * d_);
-            }
+            if (sharded) g = (g >= shard_row_offset_ && g < shard_row_offset_ + n_local) ? g - shard_row_offset_ : none;
+            idx_host[i] = g;
         }
-        SKM_CUDA(cudaMemcpyAsync(raw.get(), host.data(), sizeof(float) * k_cur * d_, cudaMemcpyHostToDevice, stream_));
-        sync();
-        if (sharded) allreduce(raw.get(), k_cur * d_, 0);
+        SKM_CUDA(cudaMemcpyAsync(init_idx_dev_.ensure(k_cur), idx_host, sizeof(uint64_t) * k_cur, cudaMemcpyHostToDevice, stream_));
+        launch_gather_rows(data, init_idx_dev_.get(), raw, k_cur, d_, stream_);
+    } else {
+        float* host = init_rows_host_.ensure(k_cur * d_);
+#pragma omp parallel for
+        for (size_t i = 0; i < k_cur; ++i) {
+            size_t g = idx[i];
+            const bool mine = !sharded || (g >= shard_row_offset_ && g < shard_row_offset_ + n_local);
+            if (sharded) g -= shard_row_offset_;
+            if (mine) std::memcpy(host + i * d_, data + g * d_, sizeof(float) * d_);
+            else std::memset(host + i * d_, 0, sizeof(float) * d_);
+        }
+        SKM_CUDA(cudaMemcpyAsync(raw, host, sizeof(float) * k_cur * d_, cudaMemcpyHostToDevice, stream_));
     }
+    if (sharded) allreduce(raw, k_cur * d_, 0);
     if (rotate) {
         ensure_rotation();
-        launch_gemm_nt(raw.get(), d_, m_dev_.get(), d_, c_prev_.get(), d_, k_cur, d_, d_, stream_);
+        launch_gemm_nt(raw, d_, m_dev_.get(), d_, c_prev_.get(), d_, k_cur, d_, d_, stream_);
     } else {
-        SKM_CUDA(cudaMemcpyAsync(c_prev_.get(), raw.get(), sizeof(float) * k_cur * d_, cudaMemcpyDeviceToDevice, stream_));
+        SKM_CUDA(cudaMemcpyAsync(c_prev_.get(), raw, sizeof(float) * k_cur * d_, cudaMemcpyDeviceToDevice, stream_));
     }
-    sync();
 }
 
 // Fine-clustering variant (hierarchical_superkmeans.h:333-342): rows of an already rotated device
@@ -488,7 +520,7 @@ void run_pruned_pass_sorted(const PrunedParams& p, PrunePassBuffers& b, float ra
             tc::launch_union(xb, rows_in_batch, p.k, p.d, p.partial_d, nx_b, p.norms_y, best_b, ratio_first, map_dev + t0, nt, ubits, union_words, y_split, stream);
             tc::launch_build_cols(ubits, union_words, nt, p.k, cols, counts, cols_stride, sparse_cols, stream);
             tc::launch_sparse_chain(xb, rows_in_batch, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, chain_norms_xb, chain_norms_y, p.ratios, best_b, knn_b, dist_b, np_b,
-                                    top2_b, y_split, map_dev + t0, nt, cols, counts, cols_stride, stream);
+                                    top2_b, p.y, map_dev + t0, nt, cols, counts, cols_stride, stream);
         }
         tc::launch_refine_chain_tiles(xb, p.y, rows_in_batch, p.k, p.d, top2_b, knn_b, dist_b, map_dev, n_t, stream);
         b.total_sparse_rows += n_t * kTileM;
@@ -849,11 +881,7 @@ void Engine::run_iteration(bool gemm_only, const IterationInput& in, size_t iter
             SKM_CUDA(cudaGetLastError());
         }
     }
-    if (allreduce_fn_) {
-        allreduce(c_cur_.get(), k_cur * d_, 0);
-        allreduce(counts_.get(), k_cur, 2);
-        allreduce(scalars_dev_.get(), 2, 1);
-    }
+    allreduce_iteration(c_cur_.get(), k_cur * d_, counts_.get(), k_cur, scalars_dev_.get(), 2);
     SKM_CUDA(cudaMemcpyAsync(counts_host_.ensure(k_), counts_.get(), sizeof(uint32_t) * k_cur, cudaMemcpyDeviceToHost, stream_));
     SKM_CUDA(cudaMemcpyAsync(scalars_host_.get(), scalars_dev_.get(), sizeof(double) * 2, cudaMemcpyDeviceToHost, stream_));
     sync();
@@ -934,7 +962,7 @@ void Engine::train(const float* data, size_t n, bool on_device, const float* que
     DeviceGuard guard(device_);
     ensure_positive(n > 0, "n");
     if (trained_) throw std::runtime_error("The clustering has already been trained");
-    const size_t n_global = allreduce_fn_ ? shard_n_global_ : n;
+    const size_t n_global = sharded_() ? shard_n_global_ : n;
     if (hierarchical_) {
         if (n_queries > 0 && !cfg_.suppress_warnings) {
             std::cout << "WARNING: Early Termination by Recall is not supported in HierarchicalSuperKMeans" << std::endl;
@@ -945,14 +973,15 @@ void Engine::train(const float* data, size_t n, bool on_device, const float* que
         if (n_queries > 0 && queries == nullptr && !cfg_.sample_queries) {
             throw std::invalid_argument("Queries must be provided if n_queries > 0 and sample_queries is false");
         }
-        if (n_queries > 0 && allreduce_fn_) throw std::runtime_error("training with queries is not available for sharded training");
+        if (n_queries > 0 && sharded_()) throw std::runtime_error("training with queries is not available for sharded training");
     }
-    if (allreduce_fn_ && cfg_.sampling_fraction != 1.0f) {
+    if (sharded_() && cfg_.sampling_fraction != 1.0f) {
         throw std::runtime_error("sharded training requires sampling_fraction == 1.0");
     }
-    if (allreduce_fn_ && hierarchical_) {
+    if (sharded_() && hierarchical_) {
         throw std::runtime_error("sharded training is available for the flat algorithm only");
     }
+    const double alloc_ms0 = alloc_free_ms();
     timers_.begin(PH_TRAIN_TOTAL, stream_);
     try {
         if (hierarchical_) train_hierarchical(data, n, on_device, centroids_out);
@@ -963,6 +992,7 @@ void Engine::train(const float* data, size_t n, bool on_device, const float* que
     }
     timers_.end(stream_);
     sync();
+    timers_.add_host(PH_ALLOC_FREE, alloc_free_ms() - alloc_ms0);
 }
 
 // Copies (and rotates unless the data is pre-rotated) the training rows into x_rot_; with sampling
@@ -976,14 +1006,24 @@ void Engine::train_flat(const float* data, size_t n, bool on_device, const float
     stats_flat_.clear();
     n_queries_ = 0;
     first_assign_done_ = false;
-    const size_t n_global = allreduce_fn_ ? shard_n_global_ : n;
+    const size_t n_global = sharded_() ? shard_n_global_ : n;
     const size_t n_samples_global = n_vectors_to_sample(n_global, k_, cfg_.sampling_fraction, cfg_.max_points_per_cluster, false);
     if (n_samples_global < k_) {
         throw std::runtime_error("Not enough samples to train. Try increasing the sampling_fraction or max_points_per_cluster");
     }
-    n_samples_ = allreduce_fn_ ? n : n_samples_global;
+    n_samples_ = sharded_() ? n : n_samples_global;
     const bool rotate = !cfg_.data_already_rotated;
     partial_d_ = initial_partial_d(vertical_d_);
+    // The Forgy shuffle runs over all n_samples indices with std::mt19937 (a tenth of a second at 1e7): on a thread of
+    // its own, while this one allocates the buffers and starts the rotation.
+    std::future<std::vector<size_t>> forgy = std::async(std::launch::async, [n_samples_global, k = k_, seed = cfg_.seed] { return forgy_indices(n_samples_global, k, seed); });
+    bool centroids_ready = false;
+    auto make_centroids = [&] {
+        if (centroids_ready) return;
+        const std::vector<size_t> idx = forgy.get();
+        generate_centroids_from_host(data, on_device, n_samples_global, k_, rotate, &idx);
+        centroids_ready = true;
+    };
 
     c_cur_.ensure(k_ * d_);
     c_prev_.ensure(k_ * d_);
@@ -1001,9 +1041,8 @@ void Engine::train_flat(const float* data, size_t n, bool on_device, const float
     prepare_update_workspace(n_samples_, k_);
 
     // GenerateCentroids picks among the first n_samples rows of the caller's data (:221-222).
-    generate_centroids_from_host(data, on_device, n_samples_global, k_, rotate);
-
     if (n_samples_global < n_global) {
+        make_centroids();
         sampled_indices_ = sampling_permutation(n, cfg_.seed);
         const size_t rows = chunk_rows_for(d_, n_samples_);
         if (on_device) {
@@ -1034,12 +1073,15 @@ void Engine::train_flat(const float* data, size_t n, bool on_device, const float
         if (rotate && !on_device) {
             // Host input: the exact assignment of iteration 1 needs nothing but the rotated rows and the initial
             // centroids, so it runs piece by piece between the uploads instead of after the last one.
-            launch_row_sqnorms(c_prev_.get(), k_, d_, d_, centroid_norms_.get(), stream_);
             uint2* top2 = top2_.ensure(n_samples_);
             float* y_split = y_split_.ensure(2 * k_ * d_);
             rotate_to_device(
                 data, false, n_samples_, x_rot_.get(),
                 [&](size_t r0, size_t cnt) {
+                    if (!centroids_ready) {
+                        make_centroids();
+                        launch_row_sqnorms(c_prev_.get(), k_, d_, d_, centroid_norms_.get(), stream_);
+                    }
                     launch_row_sqnorms(x_rot_.get() + r0 * d_, cnt, d_, d_, data_norms_.get() + r0, stream_);
                     launch_assign_full(x_rot_.get() + r0 * d_, c_prev_.get(), cnt, k_, d_, data_norms_.get() + r0, centroid_norms_.get(), assignments_.get() + r0,
                                        distances_.get() + r0, top2 + r0, stream_, y_split);
@@ -1052,9 +1094,13 @@ void Engine::train_flat(const float* data, size_t n, bool on_device, const float
             upload_rows(data, on_device, n_samples_, x_rot_.get());
         }
     }
+    make_centroids();
     sync();
 
-    launch_row_sqnorms(x_rot_.get(), n_samples_, d_, d_, data_norms_.get(), stream_);
+    {
+        PhaseScope ps(*this, PH_NORMS);
+        launch_row_sqnorms(x_rot_.get(), n_samples_, d_, d_, data_norms_.get(), stream_);
+    }
 
     // Ground truth for the recall figure (superkmeans.h:243-274): needs the full norms computed just above.
     if (n_queries > 0) prepare_recall(queries, n_queries, rotate);
@@ -1067,6 +1113,7 @@ void Engine::train_flat(const float* data, size_t n, bool on_device, const float
     for (size_t iter = 0; iter < cfg_.iters; ++iter) {
         const bool gemm_only = (iter == 0) || always_gemm_only;
         if (!gemm_only && !partial_norms_computed) {
+            PhaseScope ps(*this, PH_NORMS);
             launch_row_sqnorms(x_rot_.get(), n_samples_, d_, partial_d_, data_norms_.get(), stream_);
             partial_norms_computed = true;
         }
@@ -1141,6 +1188,7 @@ float Engine::compute_recall(size_t k_cur) {
 
 // GetOutputCentroids (superkmeans.h:1341-1351)
 void Engine::output_centroids(float* out_host) {
+    PhaseScope ps(*this, PH_ROTATE);   // the reference's profiler books Unrotate under "rotator" too
     if (cfg_.unrotate_centroids) {
         ensure_rotation();
         DeviceBuffer<float> tmp;

@@ -11,6 +11,7 @@
 
 #include "../../include/skm_b200.h"
 #include "common.cuh"
+#include "comm_nccl.h"
 #include "host_logic.h"
 
 namespace skmb {
@@ -23,16 +24,17 @@ class DeviceBuffer {
     DeviceBuffer& operator=(const DeviceBuffer&) = delete;
     ~DeviceBuffer() { release(); }
     void release() {
-        if (p_) cudaFree(p_);
+        if (p_) device_free(p_, bytes_);
         p_ = nullptr;
         cap_ = 0;
+        bytes_ = 0;
     }
     // Grows (never shrinks) to at least `count` elements; contents are not preserved on growth.
     T* ensure(size_t count) {
         if (count > cap_) {
             release();
-            note_device_alloc();
-            SKM_CUDA(cudaMalloc(&p_, sizeof(T) * (count ? count : 1)));
+            bytes_ = sizeof(T) * (count ? count : 1);
+            p_ = static_cast<T*>(device_alloc(bytes_));
             cap_ = count;
         }
         return p_;
@@ -42,11 +44,13 @@ class DeviceBuffer {
     void swap(DeviceBuffer& o) {
         std::swap(p_, o.p_);
         std::swap(cap_, o.cap_);
+        std::swap(bytes_, o.bytes_);
     }
 
   private:
     T* p_ = nullptr;
     size_t cap_ = 0;
+    size_t bytes_ = 0;
 };
 
 template <class T>
@@ -81,7 +85,12 @@ class PinnedBuffer {
 // sections of the reference's profiler (profiler.h): rotator, norms_calc, search/1st_blas, search,
 // update_centroids, consolidate, shift.
 // The last three are parts of the pruned assignment: first ADSampling test on the tensor cores, candidate-list walk, dense chain.
-enum Phase { PH_ROTATE = 0, PH_NORMS, PH_ASSIGN_FULL, PH_ASSIGN_PRUNED, PH_UPDATE, PH_CONSOLIDATE, PH_SHIFT, PH_TRAIN_TOTAL, PH_PRUNE_FIRST_TEST, PH_PRUNE_WALK, PH_PRUNE_DENSE, PH_COUNT };
+// Then four spans that no kernel phase covers: device allocation and release (host wall clock), the initial centroids (Forgy
+// shuffle on the host, row gather, their rotation), the per-iteration sum across shards (device span of the collective,
+// which includes waiting for the slowest shard), and host-side work of an iteration between kernels (split decisions,
+// statistics, synchronisation).
+enum Phase { PH_ROTATE = 0, PH_NORMS, PH_ASSIGN_FULL, PH_ASSIGN_PRUNED, PH_UPDATE, PH_CONSOLIDATE, PH_SHIFT, PH_TRAIN_TOTAL, PH_PRUNE_FIRST_TEST, PH_PRUNE_WALK, PH_PRUNE_DENSE,
+             PH_ALLOC_FREE, PH_INIT_CENTROIDS, PH_ALLREDUCE, PH_HOST_OTHER, PH_COUNT };
 
 class PhaseTimers {
   public:
@@ -90,6 +99,10 @@ class PhaseTimers {
     void end(cudaStream_t s);
     void flush();  // call only after the stream has been synchronised
     void reset();
+    void add_host(int phase, double milliseconds) {
+        ms[phase] += milliseconds;
+        calls[phase] += 1;
+    }
     double ms[PH_COUNT] = {};
     uint64_t calls[PH_COUNT] = {};
 
@@ -158,6 +171,7 @@ class Engine {
     void set_rotation(const float* m_host);
     void get_rotation(float* m_out);
     void set_shard(size_t n_global, size_t row_offset, skm_allreduce_fn fn, void* user);
+    void set_shard_nccl(size_t n_global, size_t row_offset, NcclComm* comm);
 
     void train(const float* data, size_t n, bool on_device, const float* queries, size_t n_queries, float* centroids_out);
     void assign(const float* vectors, const float* centroids, size_t n, size_t n_centroids, bool on_device, uint32_t* out);
@@ -230,7 +244,9 @@ class Engine {
     void run_iteration(bool gemm_only, const IterationInput& in, size_t iter_idx, bool is_first, std::vector<skm_iter_stats>& target);
     void run_pruned_pass(const float* x, size_t n, size_t k_cur, const float* y, const float* norms_x, const float* norms_y, uint32_t* knn, float* dist, uint32_t* not_pruned);
     void consolidate(size_t n_samples_global, size_t k_cur);
-    void generate_centroids_from_host(const float* data, bool on_device, size_t n_points_global, size_t k_cur, bool rotate);
+    // `precomputed`: the Forgy indices when the caller has already drawn them (on another thread, while buffers were allocated)
+    void generate_centroids_from_host(const float* data, bool on_device, size_t n_points_global, size_t k_cur, bool rotate, const std::vector<size_t>* precomputed = nullptr);
+    bool sharded_() const { return allreduce_fn_ != nullptr || comm_ != nullptr; }
     void generate_centroids_from_device_rows(const float* dev_rows, size_t n_points, size_t k_cur);
     void train_flat(const float* data, size_t n, bool on_device, const float* queries, size_t n_queries, float* centroids_out);
     void prepare_recall(const float* queries, size_t n_queries, bool rotate);
@@ -238,6 +254,7 @@ class Engine {
     void train_hierarchical(const float* data, size_t n, bool on_device, float* centroids_out);
     void output_centroids(float* out_host);
     void allreduce(void* buf, size_t count, int dtype);
+    void allreduce_iteration(float* sums, size_t n_sums, uint32_t* counts, size_t n_counts, double* scalars, size_t n_scalars);
     void sync() {
         SKM_CUDA(cudaStreamSynchronize(stream_));
         timers_.flush();
@@ -262,6 +279,11 @@ class Engine {
     size_t shard_n_global_ = 0, shard_row_offset_ = 0;
     skm_allreduce_fn allreduce_fn_ = nullptr;
     void* allreduce_user_ = nullptr;
+    NcclComm* comm_ = nullptr;          // when set, the sums go through NCCL on the engine's stream (comm_nccl.h)
+    DeviceBuffer<float> init_raw_;      // initial centroids before rotation
+    DeviceBuffer<uint64_t> init_idx_dev_;
+    PinnedBuffer<uint64_t> init_idx_host_;
+    PinnedBuffer<float> init_rows_host_;
 
     // pruner state
     float epsilon0_;

@@ -13,6 +13,9 @@
 
 #include <atomic>
 #include <cfloat>
+#include <chrono>
+#include <mutex>
+#include <vector>
 
 namespace skmb {
 
@@ -23,6 +26,101 @@ void note_kernel_launch() { g_kernel_launches.fetch_add(1, std::memory_order_rel
 static std::atomic<unsigned long long> g_device_allocs{0};
 unsigned long long device_alloc_count() { return g_device_allocs.load(std::memory_order_relaxed); }
 void note_device_alloc() { g_device_allocs.fetch_add(1, std::memory_order_relaxed); }
+
+// ---- device memory with an optional cache of large blocks (see common.cuh)
+namespace {
+struct CachedBlock {
+    void* p;
+    size_t bytes;
+    int device;
+};
+std::mutex g_cache_mu;
+std::vector<CachedBlock> g_cache;
+bool g_cache_on = false;
+constexpr size_t kCacheMinBytes = size_t{32} << 20;
+thread_local double g_alloc_ms = 0.0;
+
+struct AllocClock {
+    std::chrono::steady_clock::time_point t0 = std::chrono::steady_clock::now();
+    ~AllocClock() { g_alloc_ms += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count(); }
+};
+
+void drop_cache_locked() {
+    int cur = 0;
+    cudaGetDevice(&cur);
+    for (auto& b : g_cache) {
+        cudaSetDevice(b.device);
+        cudaFree(b.p);
+    }
+    g_cache.clear();
+    cudaSetDevice(cur);
+}
+} // namespace
+
+void* device_alloc(size_t bytes) {
+    AllocClock clock;
+    int device = 0;
+    SKM_CUDA(cudaGetDevice(&device));
+    if (g_cache_on && bytes >= kCacheMinBytes) {
+        std::lock_guard<std::mutex> lock(g_cache_mu);
+        size_t best = g_cache.size();
+        for (size_t i = 0; i < g_cache.size(); ++i) {
+            const CachedBlock& b = g_cache[i];
+            if (b.device == device && b.bytes >= bytes && b.bytes <= bytes + bytes / 4 && (best == g_cache.size() || b.bytes < g_cache[best].bytes)) best = i;
+        }
+        if (best != g_cache.size()) {
+            void* p = g_cache[best].p;
+            g_cache.erase(g_cache.begin() + static_cast<long>(best));
+            return p;
+        }
+    }
+    note_device_alloc();
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e == cudaErrorMemoryAllocation) {
+        // what the cache holds may be exactly what is missing
+        cudaGetLastError();
+        {
+            std::lock_guard<std::mutex> lock(g_cache_mu);
+            drop_cache_locked();
+        }
+        e = cudaMalloc(&p, bytes);
+    }
+    cuda_check(e, "cudaMalloc", __FILE__, __LINE__);
+    return p;
+}
+
+void device_free(void* p, size_t bytes) {
+    if (!p) return;
+    AllocClock clock;
+    if (g_cache_on && bytes >= kCacheMinBytes) {
+        int device = 0;
+        if (cudaGetDevice(&device) == cudaSuccess) {
+            std::lock_guard<std::mutex> lock(g_cache_mu);
+            g_cache.push_back(CachedBlock{p, bytes, device});
+            return;
+        }
+    }
+    cudaFree(p);
+}
+
+void set_workspace_cache(bool on) {
+    std::lock_guard<std::mutex> lock(g_cache_mu);
+    g_cache_on = on;
+    if (!on) drop_cache_locked();
+}
+bool workspace_cache_enabled() { return g_cache_on; }
+void release_cached_memory() {
+    std::lock_guard<std::mutex> lock(g_cache_mu);
+    drop_cache_locked();
+}
+size_t cached_memory_bytes() {
+    std::lock_guard<std::mutex> lock(g_cache_mu);
+    size_t total = 0;
+    for (const auto& b : g_cache) total += b.bytes;
+    return total;
+}
+double alloc_free_ms() { return g_alloc_ms; }
 
 // =================================================================================================
 // Row squared norms over the first `upto` columns: one warp per row.
@@ -1038,8 +1136,13 @@ void launch_shift(const float* a, const float* b, size_t k, size_t d, double* bl
 // =================================================================================================
 __global__ void gather_rows_kernel(const float* __restrict__ in, const uint64_t* __restrict__ idx, float* __restrict__ out, size_t n_out, size_t d) {
     const size_t row = blockIdx.x;
-    const float* src = in + idx[row] * d;
     float* dst = out + row * d;
+    if (idx[row] == ~uint64_t{0}) {
+        // "no row here" (held by another shard): zeros
+        for (size_t j = threadIdx.x; j < d; j += blockDim.x) dst[j] = 0.f;
+        return;
+    }
+    const float* src = in + idx[row] * d;
     for (size_t j = threadIdx.x; j < d; j += blockDim.x) dst[j] = src[j];
 }
 

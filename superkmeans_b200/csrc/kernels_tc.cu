@@ -80,6 +80,7 @@ struct Params {
 };
 
 enum { MODE_ARGMIN = 0, MODE_STORE = 1, MODE_PRUNE = 2, MODE_UNION = 3 };
+constexpr float kUnionSlack = 1.0f / 512.0f;   // see the union epilogue
 
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y,
@@ -138,11 +139,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                             ok = false;
                             break;
                         }
-                        mbar_arrive_expect_tx(&ctrl->full[s], A_TILE_BYTES + (p.y_presplit ? 2 * B_TILE_BYTES : B_TILE_BYTES));
+                        // (the union pass multiplies hi parts only and never loads the lo parts of Y)
+                        const bool load_ylo = p.y_presplit && MODE != MODE_UNION;
+                        mbar_arrive_expect_tx(&ctrl->full[s], A_TILE_BYTES + (load_ylo ? 2 * B_TILE_BYTES : B_TILE_BYTES));
                         const uint32_t st = smem_base + s * STAGE_BYTES;
                         tma_load_2d(st + OFF_A_HI, &tmap_x, &ctrl->full[s], static_cast<int>(kb * BK), static_cast<int>(x_row));
                         tma_load_2d(st + OFF_B_HI, &tmap_y, &ctrl->full[s], static_cast<int>(kb * BK), static_cast<int>(nt * BN));
-                        if (p.y_presplit) tma_load_2d(st + OFF_B_LO, &tmap_ylo, &ctrl->full[s], static_cast<int>(kb * BK), static_cast<int>(nt * BN));
+                        if (load_ylo) tma_load_2d(st + OFF_B_LO, &tmap_ylo, &ctrl->full[s], static_cast<int>(kb * BK), static_cast<int>(nt * BN));
                     }
                 }
             }
@@ -176,8 +179,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                             const uint64_t b_hi = make_desc(st + OFF_B_HI + kk * 32);
                             const uint64_t b_lo = make_desc(st + OFF_B_LO + kk * 32);
                             umma_tf32(acc, a_hi, b_hi, (kb | kk) != 0 ? 1u : 0u);
-                            umma_tf32(acc, a_hi, b_lo, 1u);
-                            umma_tf32(acc, a_lo, b_hi, 1u);
+                            if (MODE != MODE_UNION) {
+                                umma_tf32(acc, a_hi, b_lo, 1u);
+                                umma_tf32(acc, a_lo, b_hi, 1u);
+                            }
                         }
                         umma_commit(&ctrl->empty[s]);
                     }
@@ -256,11 +261,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
             uint32_t* my_union = nullptr;
             if (MODE == MODE_UNION) {
                 my_union = p.union_bits + (rt - rt_begin) * static_cast<size_t>(p.union_words);
-                // The union must contain every pair that the chain kernel's own first test will pass.  That test uses the
-                // same products but norms summed in another order (a few 1e-8 apart), so the threshold is widened a little.
+                // The union must contain every pair that the chain kernel's own first test will pass.  This pass multiplies
+                // the tf32 hi parts only (one product instead of three): x.c is then off by at most 2^-10 |x| |c|, the
+                // partial distance by at most 2^-10 (|x|^2 + |c|^2).  The test is widened by twice that (kUnionSlack; the
+                // |c|^2 share is folded into the centroid norms below), plus a little for norms summed in another order.
                 if (row_valid && !(p.skip && p.skip[row])) {
                     const float t0 = p.best_in[row] * p.ratio_first;
-                    thr = fmaf(t0, 1e-4f, t0) + 1e-6f * nx;
+                    thr = fmaf(t0, 1e-4f, t0) + (kUnionSlack + 1e-6f) * nx;
                 }
             }
             for (uint32_t nt = 0; nt < n_col_tiles && ok; ++nt, ++t) {
@@ -275,7 +282,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                 }
                 if (kTiled) {
                     // the two warps of a row quarter fill (and read) disjoint halves of the shared copy
-                    for (int j = half * (BN / 2) + lane; j < static_cast<int>((half + 1) * (BN / 2)); j += 32) ny[j] = (col0 + j < p.k) ? __ldg(p.norms_y + col0 + j) : 0.f;
+                    const float ny_scale = MODE == MODE_UNION ? 1.0f - kUnionSlack : 1.0f;
+                    for (int j = half * (BN / 2) + lane; j < static_cast<int>((half + 1) * (BN / 2)); j += 32) ny[j] = (col0 + j < p.k) ? ny_scale * __ldg(p.norms_y + col0 + j) : 0.f;
                     __syncwarp();
                 }
                 // warp-uniform outcome: the tensor-memory loads below must be executed by the whole warp

@@ -51,11 +51,11 @@ void launch_union(const float* x, size_t n, size_t k, size_t d, uint32_t partial
 // (kernels_tc_sparse.cu).  For every listed tile and 1024-centroid chunk, cols[t * cols_stride + chunk * 1024 ..] holds
 // the col_counts[t * n_chunks + chunk] local indices (ascending) of the chunk's centroids that can pass the first test for
 // some row of the tile; all other centroids are skipped, which cannot change the result.  Other arguments as for
-// launch_chain; y_split must already hold the split centroids.  Rows of listed tiles whose every chunk is empty keep
-// what knn / dist / not_pruned / top2 held on entry.
+// launch_chain (y: the centroids themselves).  Rows of listed tiles whose every chunk is empty keep what knn / dist /
+// not_pruned / top2 held on entry.
 void launch_sparse_chain(const float* x, size_t n, size_t k, size_t d, uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d, const float* chain_norms_x,
                          const float* chain_norms_y, const float* ratios, const float* best_in, uint32_t* knn, float* dist, uint32_t* not_pruned, uint2* top2_scratch,
-                         const float* y_split, const uint32_t* tile_map, size_t n_tiles, const uint16_t* cols, const uint32_t* col_counts, size_t cols_stride,
+                         const float* y, const uint32_t* tile_map, size_t n_tiles, const uint16_t* cols, const uint32_t* col_counts, size_t cols_stride,
                          cudaStream_t stream);
 // cols / col_counts from union bits: one warp per (tile, chunk); *total_cols += columns listed (rounded up to the 16 the
 // tensor cores process), for work accounting.

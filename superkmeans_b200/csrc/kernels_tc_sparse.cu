@@ -16,10 +16,11 @@
 // Kernel roles (448 threads, one persistent CTA per SM), stage layout and accumulators are those of the dense chain:
 //   warp 0      TMA producer of the X tile (128 points x 16 dimensions per stage);
 //   warp 1      MMA issuer: tcgen05.mma kind::tf32, M = 128, N = the unit's column count rounded up to 16;
-//   warps 2-5   split the X tile into tf32 hi / lo parts in place AND gather the unit's centroid rows: each thread
-//               copies, for eight of the unit's centroids, 16 bytes of the hi part and of the lo part per stage from
-//               the pre-split centroid matrix (global memory, L2 resident) into the stage, in the 64-byte swizzled
-//               layout the MMA descriptors expect (16-byte unit u of row r at unit u ^ ((r >> 1) & 3));
+//   warps 2-5   split the X tile into tf32 hi / lo parts in place AND gather the unit's centroid rows: two groups of
+//               two warps take the stages in turn; for its stage a thread copies 16 bytes of sixteen of the unit's
+//               centroids from the centroid matrix (global memory, L2 resident), splits them into tf32 hi / lo parts
+//               and stores both into the stage in the 64-byte swizzled layout the MMA descriptors expect (16-byte
+//               unit u of row r at unit u ^ ((r >> 1) & 3));
 //   warps 6-13  the rows' threads: two per point (columns 0-127 and 128-255 of a unit); tests after every segment,
 //               merge at chunk ends, as in the dense chain.
 // Every wait is bounded; on expiry the kernel records a code, every role leaves its loops, tensor memory is released
@@ -50,8 +51,7 @@ struct SparseParams {
     float* dist;
     uint32_t* not_pruned;
     uint2* top2;                    // out: the two smallest final distances seen by the chain, per point
-    const float* y_hi;              // k x d, tf32 hi parts of the centroids
-    const float* y_lo;              // k x d, tf32 lo parts
+    const float* y;                 // k x d centroids (fp32; split into tf32 parts as they are gathered)
     const uint32_t* tile_map;       // n_tiles row-tile indices
     size_t n_tiles;
     const uint16_t* cols;           // [n_tiles][cols_stride]
@@ -120,10 +120,10 @@ struct SparseCtrl {
     alignas(16) float ny[4][BN];          // per quarter of the rows: centroid norms of the unit at the current checkpoint
     float seg_ratio[64];                  // ratios[dimensions seen after segment s]
     alignas(16) uint16_t colid[4][2][BN]; // per quarter of the rows and accumulator: local centroid index of each unit column
-    uint32_t rowoff[2][BN];               // per accumulator: element offset (centroid * d) of each unit column; entry r is written and read by one gather thread only
+    uint32_t rowoff[2][2][BN];            // per gather group and accumulator: element offset (centroid * d) of each unit column
     alignas(16) RowPartial xchg[2][2][BM];   // [use parity][column half][row]
 };
-constexpr uint32_t S_CTRL_BYTES = 28672;
+constexpr uint32_t S_CTRL_BYTES = 30720;
 static_assert(sizeof(SparseCtrl) <= S_CTRL_BYTES, "control block too large");
 constexpr uint32_t S_SMEM_BYTES = STAGES * STAGE_BYTES + S_CTRL_BYTES + 1024;
 static_assert(S_SMEM_BYTES <= 232448, "over the shared memory of one CTA");
@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&ctrl->full[s], 1);
-            mbar_init(&ctrl->conv[s], 128);
+            mbar_init(&ctrl->conv[s], 64);   // the 64 threads of the gather group that owns the stage
             mbar_init(&ctrl->empty[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -250,34 +250,37 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
         }
     } else if (warp < 6) {
         // ---------------------------------------------------------------- X splitter + centroid gather
-        const int cid = threadIdx.x - 64;
-        // This thread's part of a centroid tile: 16-byte unit c16 of rows r0, r0 + 32, ..., r0 + 224.
-        const uint32_t c16 = static_cast<uint32_t>(cid) & 3u;
-        const uint32_t r0 = static_cast<uint32_t>(cid) >> 2;
+        // Two groups of two warps take the stages in turn (group g the stages with kbt % 2 == g), so that each has two
+        // stage times for the round trip of its loads to L2.  For its stage a thread copies 16-byte unit c16 of the
+        // centroid rows r0, r0 + 16, ..., r0 + 240 of the unit (fp32 from global memory, split into tf32 hi / lo parts
+        // in registers: the same split as split_tf32_kernel) and splits an eighth of the X tile in place.
+        const uint32_t group = static_cast<uint32_t>(warp - 2) >> 1;
+        const uint32_t gid = (threadIdx.x - 64u) & 63u;   // 0 .. 63 inside the group
+        const uint32_t c16 = gid & 3u;
+        const uint32_t r0 = gid >> 2;                     // 0 .. 15
+        uint32_t* rowoff = ctrl->rowoff[group][0];
         uint32_t kbt = 0;
         bool ok = true;
         SPARSE_FOR_EACH_UNIT_SEGMENT({
             if (seg == 0) {
-                // rows past the unit's last centroid repeat it (finite values; their columns are never tested)
+                // element offsets of this thread's centroid rows; rows past the unit's last centroid repeat it (finite
+                // values; their columns are never tested).  Entry r is written and read by this thread only.
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint32_t r = r0 + 32u * i;
-                    const uint32_t col = static_cast<uint32_t>(c0) + __ldg(unit_cols + min(r, nu - 1u));
-                    ctrl->rowoff[a][r] = col * p.d;   // element offset of the centroid's row
+                for (int i = 0; i < 16; ++i) {
+                    const uint32_t r = r0 + 16u * i;
+                    if (r < nmma) rowoff[a * BN + r] = (static_cast<uint32_t>(c0) + __ldg(unit_cols + min(r, nu - 1u))) * p.d;
                 }
             }
             for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
+                if ((kbt & 1u) != group) continue;
                 const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
                 // the centroid parts of this stage, on their way before the stage is even free
                 const uint32_t xc = si.x_begin + kb * BK + c16 * 4u;
-                float4 bh[8], bl[8];
+                float4 raw[16];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    if (r0 + 32u * i < nmma) {
-                        const uint32_t off = ctrl->rowoff[a][r0 + 32u * i] + xc;
-                        bh[i] = __ldg(reinterpret_cast<const float4*>(p.y_hi + off));
-                        bl[i] = __ldg(reinterpret_cast<const float4*>(p.y_lo + off));
-                    }
+                for (int i = 0; i < 16; ++i) {
+                    const uint32_t r = r0 + 16u * i;
+                    if (r < nmma) raw[i] = __ldg(reinterpret_cast<const float4*>(p.y + rowoff[a * BN + r] + xc));
                 }
                 // full[s]: the X tile has landed, and (the producer waited for it) the MMAs that read this stage before are done
                 if (!mbar_wait(&ctrl->full[s], ph, wctx, 24)) {
@@ -289,8 +292,8 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                 float4* a_lo = reinterpret_cast<float4*>(st + OFF_A_LO);
                 const bool mask = (kb == 0) && (si.mask_below > si.x_begin);
 #pragma unroll
-                for (int i = 0; i < static_cast<int>(A_TILE_BYTES / 16 / 128); ++i) {
-                    const int q = cid + 128 * i;
+                for (int i = 0; i < static_cast<int>(A_TILE_BYTES / 16 / 64); ++i) {
+                    const int q = static_cast<int>(gid) + 64 * i;
                     float4 v = a_hi[q];
                     if (mask) {
                         // 64-byte swizzle: 16-byte unit u of row r sits at unit u ^ ((r >> 1) & 3)
@@ -309,12 +312,14 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                 float4* b_hi = reinterpret_cast<float4*>(st + OFF_B_HI);
                 float4* b_lo = reinterpret_cast<float4*>(st + OFF_B_LO);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint32_t r = r0 + 32u * i;
+                for (int i = 0; i < 16; ++i) {
+                    const uint32_t r = r0 + 16u * i;
                     if (r < nmma) {
+                        float4 hi, lo;
+                        split4(raw[i], hi, lo);
                         const uint32_t slot = r * 4u + (c16 ^ ((r >> 1) & 3u));
-                        b_hi[slot] = bh[i];
-                        b_lo[slot] = bl[i];
+                        b_hi[slot] = hi;
+                        b_lo[slot] = lo;
                     }
                 }
                 fence_proxy_async();
@@ -658,7 +663,7 @@ void launch_build_cols(const uint32_t* union_bits, uint32_t union_words, size_t 
 
 void launch_sparse_chain(const float* x, size_t n, size_t k, size_t d, uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d, const float* chain_norms_x,
                          const float* chain_norms_y, const float* ratios, const float* best_in, uint32_t* knn, float* dist, uint32_t* not_pruned, uint2* top2_scratch,
-                         const float* y_split, const uint32_t* tile_map, size_t n_tiles, const uint16_t* cols, const uint32_t* col_counts, size_t cols_stride,
+                         const float* y, const uint32_t* tile_map, size_t n_tiles, const uint16_t* cols, const uint32_t* col_counts, size_t cols_stride,
                          cudaStream_t stream) {
     if (n_tiles == 0 || n == 0 || k == 0) return;
     if (k * d >= (size_t{1} << 32)) throw std::invalid_argument("centroid matrix too large for the gathered chain (k * d must stay below 2^32)");
@@ -685,8 +690,7 @@ void launch_sparse_chain(const float* x, size_t n, size_t k, size_t d, uint32_t 
     p.dist = dist;
     p.not_pruned = not_pruned;
     p.top2 = top2_scratch;
-    p.y_hi = y_split;
-    p.y_lo = y_split + k * d;
+    p.y = y;
     p.tile_map = tile_map;
     p.n_tiles = n_tiles;
     p.cols = cols;

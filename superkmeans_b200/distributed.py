@@ -50,7 +50,25 @@ def make_allreduce(device, group=None) -> Callable[[int, int, int], None]:
     return fn
 
 
-def train_sharded(engine, local_rows, n_local: int, n_global: int, row_offset: int, device, on_device: bool = True, group=None):
-    """Trains `engine` on this rank's rows; every rank returns the same centroids."""
-    engine.set_shard(n_global, row_offset, make_allreduce(device, group))
+def make_comm(device_index: int, group=None):
+    """An NCCL communicator inside the library for the ranks of `group` (default: all ranks): rank 0 draws the unique id,
+    torch.distributed carries it to the others (any backend), every rank joins.  The per-iteration sums then run on the
+    engine's own stream without a callback into Python."""
+    import torch.distributed as dist
+
+    from .engine import Comm
+
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    box = [Comm.unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+    return Comm(box[0], rank, world, device_index)
+
+
+def train_sharded(engine, local_rows, n_local: int, n_global: int, row_offset: int, device, on_device: bool = True, group=None, comm=None):
+    """Trains `engine` on this rank's rows; every rank returns the same centroids.  With `comm` (make_comm) the sums go
+    through NCCL inside the library, else through torch.distributed."""
+    if comm is not None:
+        engine.set_shard_comm(n_global, row_offset, comm)
+    else:
+        engine.set_shard(n_global, row_offset, make_allreduce(device, group))
     return engine.train(local_rows, n=n_local, on_device=on_device)

@@ -88,6 +88,11 @@ class Engine:
         self._keepalive = _lib.ALLREDUCE_FN(_cb)
         check(lib.skm_set_shard(self._h, n_global, row_offset, self._keepalive, None), self._h)
 
+    def set_shard_comm(self, n_global: int, row_offset: int, comm: "Comm"):
+        """Sharded training with the sums done by NCCL inside the library (see skm_set_shard_comm)."""
+        self._keepalive = comm
+        check(lib.skm_set_shard_comm(self._h, n_global, row_offset, comm._c), self._h)
+
     # -- the three calls of the reference API -----------------------------------------------------
     def train(self, data, n: Optional[int] = None, on_device: bool = False, queries=None, n_queries: int = 0) -> np.ndarray:
         """queries: host array of query vectors for the recall figure; with config.sample_queries pass n_queries alone."""
@@ -174,7 +179,8 @@ class Engine:
             out.append(dict(n_samples=ns.value, n_clusters=nc.value, partial_d_next=pd.value, centroids=cen, assign=asg, dist=dst, sizes_pre=s0, sizes_post=s1))
         return out
 
-    PHASES = ("rotator", "norms_calc", "search/1st_blas", "search", "update_centroids", "consolidate", "shift", "train", "search/first_test", "search/walk", "search/dense")
+    PHASES = ("rotator", "norms_calc", "search/1st_blas", "search", "update_centroids", "consolidate", "shift", "train", "search/first_test", "search/walk", "search/dense",
+              "alloc_free", "init_centroids", "allreduce")
 
     def phase_times(self) -> dict:
         """{phase name: (device milliseconds, calls)} accumulated since creation / reset."""
@@ -216,6 +222,47 @@ class Engine:
         out = np.empty((self.k, self.d), dtype=np.float32)
         check(lib.skm_get_rotated_centroids(self._h, out), self._h)
         return out
+
+
+class Comm:
+    """An NCCL communicator owned by the library (skm_comm): `Comm.unique_id()` on one rank, the 128 bytes passed to all
+    ranks, then `Comm(id, rank, world, device)` on every rank (a collective)."""
+
+    def __init__(self, unique_id: bytes, rank: int, world: int, device: int):
+        if len(unique_id) != 128:
+            raise ValueError("the unique id has 128 bytes")
+        c = C.c_void_p()
+        buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        check(lib.skm_comm_create(buf, rank, world, device, C.byref(c)))
+        self._c = c
+        self.rank, self.world = rank, world
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = (C.c_uint8 * 128)()
+        check(lib.skm_comm_unique_id(buf))
+        return bytes(buf)
+
+    def close(self):
+        if getattr(self, "_c", None) and lib is not None:
+            lib.skm_comm_destroy(self._c)
+            self._c = None
+
+    def __del__(self):
+        self.close()
+
+
+def set_workspace_cache(enabled: bool) -> None:
+    """Keep large device buffers between calls (see skm_set_workspace_cache); off by default."""
+    lib.skm_set_workspace_cache(int(enabled))
+
+
+def release_cached_memory() -> None:
+    lib.skm_release_cached_memory()
+
+
+def cached_memory_bytes() -> int:
+    return int(lib.skm_cached_memory_bytes())
 
 
 def set_tensor_cores(enabled: bool) -> None:

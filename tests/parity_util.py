@@ -4,7 +4,9 @@ search (BatchComputer::FindNearestNeighborWithPruning, batch_computers.h:297-409
 Both implementations run the same approximate search: a candidate is dropped as soon as its partial distance over the
 dimensions seen so far is not below best * ratio[dimensions seen] (pdx/pdxearch.h:67-80).  Two fp32 evaluations of
 that search can legitimately differ on a point in exactly two ways:
-  * near-tie: the two answers are equally good (float64 distances within 1e-5 relative);
+  * near-tie: the two answers are equally good: float64 distances within 1e-5 relative, or within the rounding of the
+    reference's own distance formula ||x||^2 + ||c||^2 - 2 x.c (batch_computers.h:152-163), which is about 1e-7 of the
+    norms whatever the distance (twin centroids left by a split sit that close);
   * threshold flip: the better answer sat within fp32 rounding of one of its thresholds, so one side dropped it
     (an ADSampling false prune) and the other kept it.
 Everything else would be a bug.  `classify_disagreements` replays the search of the affected points in float64 and
@@ -29,7 +31,7 @@ def _checkpoints(d, partial_d, vertical_d):
     return segs
 
 
-def classify_disagreements(x, y, prev, a, b, partial_d, vertical_d, ratios, tie_rel=1e-5, thr_tol=2e-5, margins=None):
+def classify_disagreements(x, y, prev, a, b, partial_d, vertical_d, ratios, tie_rel=1e-5, tie_norm=1e-6, thr_tol=2e-5, margins=None):
     """x [n][d] rotated points, y [k][d] rotated centroids, prev the assignment the pass started from, a / b the two
     answers.  Returns (n_near_ties, n_threshold_flips, unexplained indices).
 
@@ -46,7 +48,8 @@ def classify_disagreements(x, y, prev, a, b, partial_d, vertical_d, ratios, tie_
         xi = x[i].astype(np.float64)
         da = float(((xi - y[a[i]].astype(np.float64)) ** 2).sum())
         db = float(((xi - y[b[i]].astype(np.float64)) ** 2).sum())
-        if abs(da - db) <= tie_rel * max(min(da, db), 1e-30):
+        norms = float((xi ** 2).sum()) + float((y[a[i]].astype(np.float64) ** 2).sum())
+        if abs(da - db) <= tie_rel * max(min(da, db), 1e-30) + tie_norm * norms:
             n_tie += 1
             continue
         w = int(a[i]) if da < db else int(b[i])   # the better answer: the other side must have dropped it
