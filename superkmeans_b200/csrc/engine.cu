@@ -1398,8 +1398,15 @@ void Engine::assign(const float* vectors, const float* centroids, size_t n, size
     launch_row_sqnorms(c_dev, n_centroids, d_, d_, cn.ensure(n_centroids), stream_);
     if (on_device) {
         DeviceBuffer<float> xn, dist;
-        launch_row_sqnorms(vectors, n, d_, d_, xn.ensure(n), stream_);
-        launch_assign_full(vectors, c_dev, n, n_centroids, d_, xn.get(), cn.get(), out, dist.ensure(n), top2_.ensure(n), stream_, y_split_.ensure(2 * n_centroids * d_));
+        xn.ensure(n);
+        dist.ensure(n);
+        top2_.ensure(n);
+        y_split_.ensure(2 * n_centroids * d_);
+        {
+            PhaseScope ps(*this, PH_ASSIGN_FULL);
+            launch_row_sqnorms(vectors, n, d_, d_, xn.get(), stream_);
+            launch_assign_full(vectors, c_dev, n, n_centroids, d_, xn.get(), cn.get(), out, dist.get(), top2_.get(), stream_, y_split_.get());
+        }
         sync();
         check_tc_error(stream_);
         return;
@@ -1417,6 +1424,9 @@ void Engine::assign(const float* vectors, const float* centroids, size_t n, size
         SKM_CUDA(cudaEventCreateWithFlags(&consumed[i], cudaEventDisableTiming));
     }
     size_t ci = 0;
+    top2_.ensure(rows);
+    y_split_.ensure(2 * n_centroids * d_);
+    timers_.begin(PH_ASSIGN_FULL, stream_);
     for (size_t r0 = 0; r0 < n; r0 += rows, ++ci) {
         const int b = static_cast<int>(ci & 1);
         const size_t cnt = std::min(rows, n - r0);
@@ -1429,6 +1439,7 @@ void Engine::assign(const float* vectors, const float* centroids, size_t n, size
         SKM_CUDA(cudaMemcpyAsync(out + r0, knn[b].get(), sizeof(uint32_t) * cnt, cudaMemcpyDeviceToHost, stream_));
         SKM_CUDA(cudaEventRecord(consumed[b], stream_));
     }
+    timers_.end(stream_);
     sync();
     for (int i = 0; i < 2; ++i) {
         cudaEventDestroy(copied[i]);

@@ -117,9 +117,9 @@ struct SparseCtrl {
     uint64_t xchg_bar;        // the 256 row threads have published their RowPartial
     uint32_t tmem_base;
     uint32_t pad;
-    alignas(16) float ny[4][BN];          // per quarter of the rows: centroid norms of the unit at the current checkpoint
+    alignas(16) float ny[8][BN / 2];      // per row warp: centroid norms of its share of the unit's columns at the current checkpoint
     float seg_ratio[64];                  // ratios[dimensions seen after segment s]
-    alignas(16) uint16_t colid[4][2][BN]; // per quarter of the rows and accumulator: local centroid index of each unit column
+    alignas(16) uint16_t colid[8][2][BN / 2]; // per row warp and accumulator: local centroid index of each column of its share
     uint32_t rowoff[2][2][BN];            // per gather group and accumulator: element offset (centroid * d) of each unit column
     alignas(16) RowPartial xchg[2][2][BM];   // [use parity][column half][row]
 };
@@ -131,8 +131,9 @@ constexpr uint32_t SPARSE_MAX_SEGMENTS = 64;
 constexpr int SPARSE_THREADS = 448;
 
 // Order of work shared by all roles: listed tile, chunk of 1024 centroids (skipped when it lists nothing), pair of
-// units of up to 256 listed centroids, segment, unit of the pair.  `a` (0 / 1) is the unit's accumulator, `nu` its
-// number of listed centroids and `nmma` that number rounded up to the tensor cores' multiple of 16.
+// units, segment, unit of the pair.  A chunk's listed centroids are cut into units of equal width (a multiple of 16, at
+// most 256).  `a` (0 / 1) is the unit's accumulator, `nu` its number of listed centroids and `nmma` that number
+// rounded up to the tensor cores' multiple of 16.
 #define SPARSE_FOR_EACH_UNIT_SEGMENT(...)                                                                 \
     for (size_t lt = blockIdx.x; lt < p.n_tiles && ok; lt += gridDim.x) {                                 \
         [[maybe_unused]] const size_t rt = static_cast<size_t>(__ldg(p.tile_map + lt));                               \
@@ -141,16 +142,18 @@ constexpr int SPARSE_THREADS = 448;
             if (n_listed == 0) continue;                                                                  \
             const size_t c0 = static_cast<size_t>(chunk) * kChunk;                                        \
             const uint16_t* chunk_cols = p.cols + lt * p.cols_stride + c0;                                \
-            const uint32_t n_units = (n_listed + BN - 1) / BN;                                            \
+            /* at least two units whenever there is enough to split, so that one unit's tests overlap the other's products */ \
+            const uint32_t n_units = n_listed <= 16u ? 1u : max(2u, (n_listed + BN - 1) / BN);            \
+            const uint32_t unit_w = (((n_listed + n_units - 1) / n_units) + 15u) & ~15u;                  \
             for (uint32_t pair = 0; pair * 2 < n_units && ok; ++pair) {                                   \
                 for (uint32_t seg = 0; seg < p.n_seg && ok; ++seg) {                                      \
                     const Seg si = sparse_segment(p, seg);                                                \
                     for (uint32_t a = 0; a < 2 && ok; ++a) {                                              \
                         const uint32_t unit = pair * 2 + a;                                               \
-                        if (unit >= n_units) break;                                                       \
-                        [[maybe_unused]] const uint32_t nu = min(static_cast<uint32_t>(BN), n_listed - unit * BN); \
+                        if (unit >= n_units || unit * unit_w >= n_listed) break;                          \
+                        [[maybe_unused]] const uint32_t nu = min(unit_w, n_listed - unit * unit_w);      \
                         [[maybe_unused]] const uint32_t nmma = (nu + 15u) & ~15u;                         \
-                        [[maybe_unused]] const uint16_t* unit_cols = chunk_cols + unit * BN;              \
+                        [[maybe_unused]] const uint16_t* unit_cols = chunk_cols + unit * unit_w;          \
                         __VA_ARGS__                                                                       \
                     }                                                                                     \
                 }                                                                                         \
@@ -351,7 +354,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
         uint32_t prevpos0 = 0xFFFFFFFFu, prevpos1 = 0xFFFFFFFFu;
 #pragma unroll
         for (int q = 0; q < HS; ++q) alive0[q] = alive1[q] = 0;
-        float* ny = ctrl->ny[quarter];
+        float* ny = ctrl->ny[warp - 6];
         // End of a chunk: the two threads of the row exchange what they found in their halves of the columns and
         // both apply the same update.  Returns false when the wait ran out.
         auto close_chunk = [&]() -> bool {
@@ -439,20 +442,23 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                 cur_chunk = chunk;
             }
             const bool first = seg == 0, last = (seg + 1 == p.n_seg);
-            // columns of the unit that belong to this thread's half, and the 32-column slices they fill
-            const uint32_t my_cols = nu > half * (BN / 2) ? min(static_cast<uint32_t>(BN / 2), nu - half * (BN / 2)) : 0u;
+            // The unit's columns are shared between the two threads of a row: the first hw columns (a multiple of 32) and
+            // the rest.  my_cols: how many belong to this thread, n_sl: the 32-column slices they fill.
+            const uint32_t hw = ((nu + 63u) >> 6) << 5;
+            const uint32_t hb = half * hw;   // first column of this thread's share
+            const uint32_t my_cols = nu > hb ? min(hw, nu - hb) : 0u;
             const uint32_t n_sl = (my_cols + 31u) >> 5;
-            uint16_t* colid = ctrl->colid[quarter][a];
+            uint16_t* colid = ctrl->colid[warp - 6][a];
             uint32_t cidx[HS];
             uint32_t prevpos;
             if (first) {
-                // Local centroid indices of the unit's columns, into the warp's half of the quarter's shared copy: read back
-                // per lane for the norm gathers of every segment, and per column when a survivor needs its centroid.
+                // Local centroid indices of this warp's share of the unit's columns, into the warp's own table: read back per
+                // lane for the norm gathers of every segment, and per column when a survivor needs its centroid.
 #pragma unroll
                 for (uint32_t q = 0; q < HS; ++q) {
                     const uint32_t j = q * 32 + lane;
-                    cidx[q] = j < my_cols ? static_cast<uint32_t>(__ldg(unit_cols + half * (BN / 2) + j)) : 0u;
-                    colid[half * (BN / 2) + j] = static_cast<uint16_t>(cidx[q]);
+                    cidx[q] = j < my_cols ? static_cast<uint32_t>(__ldg(unit_cols + hb + j)) : 0u;
+                    colid[j] = static_cast<uint16_t>(cidx[q]);
                 }
                 __syncwarp();
                 // where the row's previous centroid sits among this half's columns (ascending indices: binary search)
@@ -462,23 +468,22 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                     uint32_t lo = 0, hi = my_cols;
                     while (lo < hi) {
                         const uint32_t mid = (lo + hi) >> 1;
-                        if (colid[half * (BN / 2) + mid] < want) lo = mid + 1;
+                        if (colid[mid] < want) lo = mid + 1;
                         else hi = mid;
                     }
-                    if (lo < my_cols && colid[half * (BN / 2) + lo] == want) prevpos = lo;
+                    if (lo < my_cols && colid[lo] == want) prevpos = lo;
                 }
                 if (a) prevpos1 = prevpos;
                 else prevpos0 = prevpos;
             } else {
                 // this lane's columns (q * 32 + lane of this half), from the copy the first segment left
 #pragma unroll
-                for (uint32_t q = 0; q < HS; ++q) cidx[q] = colid[half * (BN / 2) + q * 32 + lane];
+                for (uint32_t q = 0; q < HS; ++q) cidx[q] = colid[q * 32 + lane];
                 prevpos = a ? prevpos1 : prevpos0;
             }
             const float thr = best * ctrl->seg_ratio[seg];
             const float nxv = row_valid ? __ldg(p.chain_norms_x + row * p.n_seg + seg) : 0.f;
-            // centroid norms of the unit's columns at this checkpoint: the two warps of a row quarter fill (and read)
-            // disjoint halves of the quarter's copy
+            // centroid norms of this warp's share of the unit's columns at this checkpoint
             {
                 const float* __restrict__ src = p.chain_norms_y + static_cast<size_t>(seg) * p.k + c0;
                 float cur[HS];
@@ -486,7 +491,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                 for (uint32_t q = 0; q < HS; ++q) cur[q] = (q * 32 + lane < my_cols) ? __ldg(src + cidx[q]) : 0.f;
                 __syncwarp();
 #pragma unroll
-                for (uint32_t q = 0; q < HS; ++q) ny[half * (BN / 2) + q * 32 + lane] = cur[q];
+                for (uint32_t q = 0; q < HS; ++q) ny[q * 32 + lane] = cur[q];
                 __syncwarp();
             }
             if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->acc_ready[a], uses[a] & 1u, wctx, 25))) {
@@ -495,13 +500,13 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
             }
             ++uses[a];
             tc_fence_after();
-            const uint32_t taddr = tmem_base + (lane_base << 16) + a * BN + half * (BN / 2);
+            const uint32_t taddr = tmem_base + (lane_base << 16) + a * BN + hb;
             uint32_t alive[HS];
 #pragma unroll
             for (int q = 0; q < HS; ++q) alive[q] = a ? alive1[q] : alive0[q];
             // One 32-column slice (slice `sl` of this half) is tested while the next one is on its way from tensor memory.
             auto test_slice = [&](const uint32_t sl, uint32_t (&r)[32], uint32_t& alive_ch) {
-                const uint32_t cb0 = half * (BN / 2) + sl * 32;   // first column of the slice inside the unit
+                const uint32_t cb0 = sl * 32;   // first column of the slice inside this thread's share of the unit
                 // bit j of w = (partial distance of column cb0 + j < threshold), branch-free
                 uint32_t w = 0;
 #pragma unroll
@@ -563,35 +568,45 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                 }
             };
             uint32_t ra[32], rb[32];
-            if (n_sl > 0) {
+            if (n_sl <= 2) {
+                // At most two slices: both fit in registers, so the accumulator goes back to the MMA warp before any test.
+                if (n_sl > 0) tmem_ld32_issue(taddr, ra);
+                if (n_sl > 1) tmem_ld32_issue(taddr + 32, rb);
+                if (n_sl > 0) tmem_ld_wait(ra);
+                if (n_sl > 1) tmem_ld_wait(rb);
+                tc_fence_before();
+                mbar_arrive(&ctrl->acc_loaded[a]);
+                if (n_sl > 0) test_slice(0, ra, alive[0]);
+                if (n_sl > 1) test_slice(1, rb, alive[1]);
+            } else {
                 tmem_ld32_issue(taddr, ra);
                 tmem_ld_wait(ra);
-            }
-            // Two slices per trip, always HS / 2 trips so that the survivor masks, which rotate through alive[0] and
-            // alive[1] to stay in registers, are back in place afterwards; slices beyond the unit's columns are skipped.
-            // The accumulator is handed back as soon as this thread's last slice is in registers.
-            bool handed_back = false;
+                // Two slices per trip, always HS / 2 trips so that the survivor masks, which rotate through alive[0] and
+                // alive[1] to stay in registers, are back in place afterwards; slices beyond the unit's columns are skipped.
+                // The accumulator is handed back as soon as this thread's last slice is in registers.
+                bool handed_back = false;
 #pragma unroll 1
-            for (uint32_t ch = 0; ch < HS; ch += 2) {
-                const bool has0 = ch < n_sl, has1 = ch + 1 < n_sl, has2 = ch + 2 < n_sl;
-                if (has1) tmem_ld32_issue(taddr + (ch + 1) * 32, rb);
-                if (has0) test_slice(ch, ra, alive[0]);
-                if (has1) tmem_ld_wait(rb);
-                if (has2) {
-                    tmem_ld32_issue(taddr + (ch + 2) * 32, ra);
-                } else if (!handed_back) {
-                    // everything of this checkpoint is in registers: the accumulator may grow again
-                    tc_fence_before();
-                    mbar_arrive(&ctrl->acc_loaded[a]);
-                    handed_back = true;
-                }
-                if (has1) test_slice(ch + 1, rb, alive[1]);
-                if (has2) tmem_ld_wait(ra);
-                const uint32_t m0 = alive[0], m1 = alive[1];
+                for (uint32_t ch = 0; ch < HS; ch += 2) {
+                    const bool has0 = ch < n_sl, has1 = ch + 1 < n_sl, has2 = ch + 2 < n_sl;
+                    if (has1) tmem_ld32_issue(taddr + (ch + 1) * 32, rb);
+                    if (has0) test_slice(ch, ra, alive[0]);
+                    if (has1) tmem_ld_wait(rb);
+                    if (has2) {
+                        tmem_ld32_issue(taddr + (ch + 2) * 32, ra);
+                    } else if (!handed_back) {
+                        // everything of this checkpoint is in registers: the accumulator may grow again
+                        tc_fence_before();
+                        mbar_arrive(&ctrl->acc_loaded[a]);
+                        handed_back = true;
+                    }
+                    if (has1) test_slice(ch + 1, rb, alive[1]);
+                    if (has2) tmem_ld_wait(ra);
+                    const uint32_t m0 = alive[0], m1 = alive[1];
 #pragma unroll
-                for (int q = 0; q < HS - 2; ++q) alive[q] = alive[q + 2];
-                alive[HS - 2] = m0;
-                alive[HS - 1] = m1;
+                    for (int q = 0; q < HS - 2; ++q) alive[q] = alive[q + 2];
+                    alive[HS - 2] = m0;
+                    alive[HS - 1] = m1;
+                }
             }
 #pragma unroll
             for (int q = 0; q < HS; ++q) {
@@ -642,9 +657,12 @@ __global__ void __launch_bounds__(256) build_cols_kernel(const uint32_t* __restr
     if (lane == 0) {
         col_counts[t * n_chunks + chunk] = total;
         if (total_cols && total) {
-            // columns as the tensor cores see them: every unit of up to 256 rounded up to a multiple of 16
-            const uint32_t full = total / BN, rest = total % BN;
-            atomicAdd(total_cols, static_cast<unsigned long long>(full) * BN + ((rest + 15u) & ~15u));
+            // columns as the tensor cores see them: the chunk's units (cut as in sparse_chain_kernel), each rounded up to 16
+            const uint32_t n_units = total <= 16u ? 1u : max(2u, (total + BN - 1) / BN);
+            const uint32_t unit_w = (((total + n_units - 1) / n_units) + 15u) & ~15u;
+            unsigned long long cols16 = 0;
+            for (uint32_t u = 0; u * unit_w < total; ++u) cols16 += (min(unit_w, total - u * unit_w) + 15u) & ~15u;
+            atomicAdd(total_cols, cols16);
         }
     }
 }
