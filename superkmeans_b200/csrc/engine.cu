@@ -520,7 +520,7 @@ void run_pruned_pass_sorted(const PrunedParams& p, PrunePassBuffers& b, float ra
             tc::launch_union(xb, rows_in_batch, p.k, p.d, p.partial_d, nx_b, p.norms_y, best_b, ratio_first, map_dev + t0, nt, ubits, union_words, y_split, stream);
             tc::launch_build_cols(ubits, union_words, nt, p.k, cols, counts, cols_stride, sparse_cols, stream);
             tc::launch_sparse_chain(xb, rows_in_batch, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, chain_norms_xb, chain_norms_y, p.ratios, best_b, knn_b, dist_b, np_b,
-                                    top2_b, p.y, map_dev + t0, nt, cols, counts, cols_stride, stream);
+                                    top2_b, y_split, map_dev + t0, nt, cols, counts, cols_stride, stream);
         }
         tc::launch_refine_chain_tiles(xb, p.y, rows_in_batch, p.k, p.d, top2_b, knn_b, dist_b, map_dev, n_t, stream);
         b.total_sparse_rows += n_t * kTileM;

@@ -191,9 +191,13 @@ __global__ void __launch_bounds__(256, 2) gemm_nt_kernel(
 
 void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, float* out, size_t ldo, size_t n, size_t n_out, size_t k_dim, cudaStream_t stream) {
     if (n == 0 || n_out == 0) return;
-    // The tensor-core store variant (tc::launch_gemm_nt) is not used here: its accumulator truncates, and
-    // a 1e-5 relative error in the rotated data would shift every later distance.  Rotation is 2*n*d^2
-    // flops, a small share of the assignment work, and runs on the fp32 kernel.
+    // Tensor cores when TMA can address both operands: the rotation kernel cuts the accumulation into four chains summed
+    // in fp32 registers, which keeps the result at the accuracy of this file's fp32 kernel (a single chain in tensor
+    // memory would be ~1e-5 off, and rotated rows feed every later distance).
+    if (tc::eligible(a, lda, b, ldb) && k_dim >= 32) {
+        tc::launch_rotate(a, lda, b, ldb, out, ldo, n, n_out, k_dim, nullptr, stream);
+        return;
+    }
     // The point dimension is on grid.x (limit 2^31-1); output columns on grid.y.
     dim3 grid(static_cast<unsigned>((n + kTileM - 1) / kTileM), static_cast<unsigned>((n_out + kTileN - 1) / kTileN));
     gemm_nt_kernel<<<grid, 256, 0, stream>>>(a, lda, b, ldb, out, ldo, n, n_out, k_dim);

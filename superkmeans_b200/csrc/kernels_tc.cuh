@@ -29,6 +29,10 @@ void launch_presplit(const float* y, size_t rows, size_t ld, float* y_split, cud
 void launch_assign_full_flagged(const float* x, const float* y, size_t n, size_t k, size_t d, const float* norms_x, const float* norms_y, uint32_t* out_knn, float* out_dist,
                                 uint2* top2_scratch, int* error_word, cudaStream_t stream);
 void launch_gemm_nt(const float* a, size_t lda, const float* b, size_t ldb, float* out, size_t ldo, size_t n, size_t n_out, size_t k_dim, cudaStream_t stream);
+// out[n][n_out] = a[n][k_dim] * b[n_out][k_dim]^T with the accumulation cut into four chains that are summed in fp32
+// registers (kernels_tc_rotate.cu): the rotation and un-rotation GEMM.  out_sqnorms (optional): squared norm of every output row.
+void launch_rotate(const float* a, size_t lda, const float* b, size_t ldb, float* out, size_t ldo, size_t n, size_t n_out, size_t k_dim, float* out_sqnorms,
+                   cudaStream_t stream);
 
 // First ADSampling test on the tensor cores for the row tiles [tile0, tile0 + n_tiles) of 128 points: partial
 // distances over the first partial_d dimensions of every (point, centroid) pair, tested against
@@ -51,11 +55,11 @@ void launch_union(const float* x, size_t n, size_t k, size_t d, uint32_t partial
 // (kernels_tc_sparse.cu).  For every listed tile and 1024-centroid chunk, cols[t * cols_stride + chunk * 1024 ..] holds
 // the col_counts[t * n_chunks + chunk] local indices (ascending) of the chunk's centroids that can pass the first test for
 // some row of the tile; all other centroids are skipped, which cannot change the result.  Other arguments as for
-// launch_chain (y: the centroids themselves).  Rows of listed tiles whose every chunk is empty keep what knn / dist /
-// not_pruned / top2 held on entry.
+// launch_chain; y_split must already hold the split centroids.  Rows of listed tiles whose every chunk is empty keep
+// what knn / dist / not_pruned / top2 held on entry.
 void launch_sparse_chain(const float* x, size_t n, size_t k, size_t d, uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d, const float* chain_norms_x,
                          const float* chain_norms_y, const float* ratios, const float* best_in, uint32_t* knn, float* dist, uint32_t* not_pruned, uint2* top2_scratch,
-                         const float* y, const uint32_t* tile_map, size_t n_tiles, const uint16_t* cols, const uint32_t* col_counts, size_t cols_stride,
+                         const float* y_split, const uint32_t* tile_map, size_t n_tiles, const uint16_t* cols, const uint32_t* col_counts, size_t cols_stride,
                          cudaStream_t stream);
 // cols / col_counts from union bits: one warp per (tile, chunk); *total_cols += columns listed (rounded up to the 16 the
 // tensor cores process), for work accounting.

@@ -16,11 +16,11 @@
 // Kernel roles (448 threads, one persistent CTA per SM), stage layout and accumulators are those of the dense chain:
 //   warp 0      TMA producer of the X tile (128 points x 16 dimensions per stage);
 //   warp 1      MMA issuer: tcgen05.mma kind::tf32, M = 128, N = the unit's column count rounded up to 16;
-//   warps 2-5   split the X tile into tf32 hi / lo parts in place AND gather the unit's centroid rows: two groups of
-//               two warps take the stages in turn; for its stage a thread copies 16 bytes of sixteen of the unit's
-//               centroids from the centroid matrix (global memory, L2 resident), splits them into tf32 hi / lo parts
-//               and stores both into the stage in the 64-byte swizzled layout the MMA descriptors expect (16-byte
-//               unit u of row r at unit u ^ ((r >> 1) & 3));
+//   warps 2-3   split the X tile into tf32 hi / lo parts in place;
+//   warps 4-5   gather the unit's centroid rows: asynchronous 16-byte copies (cp.async) of the hi and lo parts from the
+//               pre-split centroid matrix (global memory, L2 resident) into the stage, in the 64-byte swizzled layout
+//               the MMA descriptors expect (16-byte unit u of row r at unit u ^ ((r >> 1) & 3)); up to three stages
+//               of copies are in flight, and a stage is announced once its copies have landed;
 //   warps 6-13  the rows' threads: two per point (columns 0-127 and 128-255 of a unit); tests after every segment,
 //               merge at chunk ends, as in the dense chain.
 // Every wait is bounded; on expiry the kernel records a code, every role leaves its loops, tensor memory is released
@@ -51,7 +51,8 @@ struct SparseParams {
     float* dist;
     uint32_t* not_pruned;
     uint2* top2;                    // out: the two smallest final distances seen by the chain, per point
-    const float* y;                 // k x d centroids (fp32; split into tf32 parts as they are gathered)
+    const float* y_hi;              // k x d, tf32 hi parts of the centroids
+    const float* y_lo;              // k x d, tf32 lo parts
     const uint32_t* tile_map;       // n_tiles row-tile indices
     size_t n_tiles;
     const uint16_t* cols;           // [n_tiles][cols_stride]
@@ -120,7 +121,7 @@ struct SparseCtrl {
     alignas(16) float ny[8][BN / 2];      // per row warp: centroid norms of its share of the unit's columns at the current checkpoint
     float seg_ratio[64];                  // ratios[dimensions seen after segment s]
     alignas(16) uint16_t colid[8][2][BN / 2]; // per row warp and accumulator: local centroid index of each column of its share
-    uint32_t rowoff[2][2][BN];            // per gather group and accumulator: element offset (centroid * d) of each unit column
+    uint32_t rowoff[1][2][BN];            // per accumulator: element offset (centroid * d) of each unit column (entry r belongs to one gather thread)
     alignas(16) RowPartial xchg[2][2][BM];   // [use parity][column half][row]
 };
 constexpr uint32_t S_CTRL_BYTES = 30720;
@@ -174,7 +175,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&ctrl->full[s], 1);
-            mbar_init(&ctrl->conv[s], 64);   // the 64 threads of the gather group that owns the stage
+            mbar_init(&ctrl->conv[s], 128);   // 64 X-splitter threads + 64 gather threads
             mbar_init(&ctrl->empty[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -251,41 +252,14 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                 ++uses[a];
             })
         }
-    } else if (warp < 6) {
-        // ---------------------------------------------------------------- X splitter + centroid gather
-        // Two groups of two warps take the stages in turn (group g the stages with kbt % 2 == g), so that each has two
-        // stage times for the round trip of its loads to L2.  For its stage a thread copies 16-byte unit c16 of the
-        // centroid rows r0, r0 + 16, ..., r0 + 240 of the unit (fp32 from global memory, split into tf32 hi / lo parts
-        // in registers: the same split as split_tf32_kernel) and splits an eighth of the X tile in place.
-        const uint32_t group = static_cast<uint32_t>(warp - 2) >> 1;
-        const uint32_t gid = (threadIdx.x - 64u) & 63u;   // 0 .. 63 inside the group
-        const uint32_t c16 = gid & 3u;
-        const uint32_t r0 = gid >> 2;                     // 0 .. 15
-        uint32_t* rowoff = ctrl->rowoff[group][0];
+    } else if (warp < 4) {
+        // ---------------------------------------------------------------- X splitter (warps 2, 3)
+        const int cid = threadIdx.x - 64;   // 0 .. 63
         uint32_t kbt = 0;
         bool ok = true;
         SPARSE_FOR_EACH_UNIT_SEGMENT({
-            if (seg == 0) {
-                // element offsets of this thread's centroid rows; rows past the unit's last centroid repeat it (finite
-                // values; their columns are never tested).  Entry r is written and read by this thread only.
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const uint32_t r = r0 + 16u * i;
-                    if (r < nmma) rowoff[a * BN + r] = (static_cast<uint32_t>(c0) + __ldg(unit_cols + min(r, nu - 1u))) * p.d;
-                }
-            }
             for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
-                if ((kbt & 1u) != group) continue;
                 const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
-                // the centroid parts of this stage, on their way before the stage is even free
-                const uint32_t xc = si.x_begin + kb * BK + c16 * 4u;
-                float4 raw[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const uint32_t r = r0 + 16u * i;
-                    if (r < nmma) raw[i] = __ldg(reinterpret_cast<const float4*>(p.y + rowoff[a * BN + r] + xc));
-                }
-                // full[s]: the X tile has landed, and (the producer waited for it) the MMAs that read this stage before are done
                 if (!mbar_wait(&ctrl->full[s], ph, wctx, 24)) {
                     ok = false;
                     break;
@@ -296,7 +270,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                 const bool mask = (kb == 0) && (si.mask_below > si.x_begin);
 #pragma unroll
                 for (int i = 0; i < static_cast<int>(A_TILE_BYTES / 16 / 64); ++i) {
-                    const int q = static_cast<int>(gid) + 64 * i;
+                    const int q = cid + 64 * i;
                     float4 v = a_hi[q];
                     if (mask) {
                         // 64-byte swizzle: 16-byte unit u of row r sits at unit u ^ ((r >> 1) & 3)
@@ -312,23 +286,66 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                     a_hi[q] = hi;
                     a_lo[q] = lo;
                 }
-                float4* b_hi = reinterpret_cast<float4*>(st + OFF_B_HI);
-                float4* b_lo = reinterpret_cast<float4*>(st + OFF_B_LO);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const uint32_t r = r0 + 16u * i;
-                    if (r < nmma) {
-                        float4 hi, lo;
-                        split4(raw[i], hi, lo);
-                        const uint32_t slot = r * 4u + (c16 ^ ((r >> 1) & 3u));
-                        b_hi[slot] = hi;
-                        b_lo[slot] = lo;
-                    }
-                }
                 fence_proxy_async();
                 mbar_arrive(&ctrl->conv[s]);
             }
         })
+    } else if (warp < 6) {
+        // ---------------------------------------------------------------- centroid gather (warps 4, 5)
+        // Asynchronous 16-byte copies (cp.async) from the pre-split centroid matrix straight into the stage, in the
+        // swizzled layout; no registers are tied up, so the copies of up to three stages are in flight per thread.  A
+        // thread copies unit c16 of the hi and of the lo part of rows r0, r0 + 16, ..., r0 + 240.  A stage is announced
+        // to the MMA warp two stages after its copies were issued, once cp.async.wait_group says they have landed.
+        const uint32_t gid = threadIdx.x - 128u;   // 0 .. 63
+        const uint32_t c16 = gid & 3u;
+        const uint32_t r0 = gid >> 2;              // 0 .. 15
+        uint32_t* rowoff = ctrl->rowoff[0][0];
+        uint32_t kbt = 0;
+        bool ok = true;
+        SPARSE_FOR_EACH_UNIT_SEGMENT({
+            if (seg == 0) {
+                // element offsets of this thread's centroid rows; rows past the unit's last centroid repeat it (finite
+                // values; their columns are never tested).  Entry r is written and read by this thread only.
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const uint32_t r = r0 + 16u * i;
+                    if (r < nmma) rowoff[a * BN + r] = (static_cast<uint32_t>(c0) + __ldg(unit_cols + min(r, nu - 1u))) * p.d;
+                }
+            }
+            for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
+                const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
+                // the MMAs that read this stage four k-blocks ago must be done before it is overwritten
+                if (!mbar_wait(&ctrl->empty[s], ph ^ 1u, wctx, 27)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t xc = si.x_begin + kb * BK + c16 * 4u;
+                const uint32_t st = smem_base + s * STAGE_BYTES;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const uint32_t r = r0 + 16u * i;
+                    if (r < nmma) {
+                        const uint32_t off = rowoff[a * BN + r] + xc;
+                        const uint32_t slot = (r * 4u + (c16 ^ ((r >> 1) & 3u))) * 16u;
+                        cp_async_16(st + OFF_B_HI + slot, p.y_hi + off);
+                        cp_async_16(st + OFF_B_LO + slot, p.y_lo + off);
+                    }
+                }
+                cp_async_commit();
+                if (kbt >= 2) {
+                    cp_async_wait_group<2>();   // everything but the two newest groups: the stage of two k-blocks ago
+                    fence_proxy_async();
+                    mbar_arrive(&ctrl->conv[(kbt - 2) % STAGES]);
+                }
+            }
+        })
+        // the last two stages
+        cp_async_wait_group<0>();
+        if (ok) {
+            fence_proxy_async();
+            if (kbt >= 2) mbar_arrive(&ctrl->conv[(kbt - 2) % STAGES]);
+            if (kbt >= 1) mbar_arrive(&ctrl->conv[(kbt - 1) % STAGES]);
+        }
     } else {
         // (warps 6 .. 13)
         // ---------------------------------------------------------------- rows: tests at every checkpoint
@@ -620,6 +637,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
     }
 #undef SPARSE_FOR_EACH_UNIT_SEGMENT
 
+    cp_async_wait_group<0>();   // no copy may still be on its way into shared memory when the CTA ends
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
@@ -681,7 +699,7 @@ void launch_build_cols(const uint32_t* union_bits, uint32_t union_words, size_t 
 
 void launch_sparse_chain(const float* x, size_t n, size_t k, size_t d, uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d, const float* chain_norms_x,
                          const float* chain_norms_y, const float* ratios, const float* best_in, uint32_t* knn, float* dist, uint32_t* not_pruned, uint2* top2_scratch,
-                         const float* y, const uint32_t* tile_map, size_t n_tiles, const uint16_t* cols, const uint32_t* col_counts, size_t cols_stride,
+                         const float* y_split, const uint32_t* tile_map, size_t n_tiles, const uint16_t* cols, const uint32_t* col_counts, size_t cols_stride,
                          cudaStream_t stream) {
     if (n_tiles == 0 || n == 0 || k == 0) return;
     if (k * d >= (size_t{1} << 32)) throw std::invalid_argument("centroid matrix too large for the gathered chain (k * d must stay below 2^32)");
@@ -708,7 +726,8 @@ void launch_sparse_chain(const float* x, size_t n, size_t k, size_t d, uint32_t 
     p.dist = dist;
     p.not_pruned = not_pruned;
     p.top2 = top2_scratch;
-    p.y = y;
+    p.y_hi = y_split;
+    p.y_lo = y_split + k * d;
     p.tile_map = tile_map;
     p.n_tiles = n_tiles;
     p.cols = cols;
