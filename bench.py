@@ -499,6 +499,24 @@ def main():
         roofline["traffic"] = traffic * rows_per_launch
         roofline["traffic_note"] = "dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture at n = 400000 (same d and k), per row, times the rows one launch covers"
 
+    # ---- the configurations that say "Train + Assign": Assign and AssignTrainingPoints of the training rows, device-resident
+    extra_calls = None
+    if args.workload in ("c1", "c4") and world == 1:
+        cd = torch.from_numpy(res).to(device)
+        out_a = torch.empty(n_local, dtype=torch.int32, device=device)
+        out_f = torch.empty(n_local, dtype=torch.int32, device=device)
+        times = {}
+        for name, fn, out in (("assign", e.assign, out_a), ("assign_training_points", e.assign_training_points, out_f)):
+            fn(x, cd, n=n_local, on_device=True, out=out)   # warm-up (allocations)
+            torch.cuda.synchronize(device)
+            t0 = time.perf_counter()
+            fn(x, cd, n=n_local, on_device=True, out=out)
+            torch.cuda.synchronize(device)
+            times[name + "_s"] = time.perf_counter() - t0
+        times["fast_equals_brute_force"] = float((out_a == out_f).float().mean())
+        extra_calls = times
+        del cd, out_a, out_f
+
     # ---- end to end through the public API with host input: pinned, then pageable (what a caller of Train(const float*, n) has)
     e2e, e2e_pageable = None, None
     if not args.no_e2e:
@@ -604,7 +622,7 @@ def main():
             "ms_per_step": ms_per_step, "seconds_per_step": ms_per_step / 1e3, "wall_ms_per_step": float(np.mean(walls)), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
             "phases_ms_per_step": {name: round(v, 3) for name, v in phases.items()},
-            "roofline": roofline, "cpu_baseline": cpu_baseline, "parity_on_sample": parity, "sharded_parity": sharded_parity, "e2e": e2e, "e2e_pageable": e2e_pageable,
+            "after_train": extra_calls, "roofline": roofline, "cpu_baseline": cpu_baseline, "parity_on_sample": parity, "sharded_parity": sharded_parity, "e2e": e2e, "e2e_pageable": e2e_pageable,
             "gpu_launches": int(launches), "clocks": clocks,
         }
         print(json.dumps(line))

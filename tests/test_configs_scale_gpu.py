@@ -1,0 +1,165 @@
+"""The benchmark configurations against the compiled reference at the sizes the reference can run on the host:
+
+* config 2 (flat, n = 1 000 000, d = 1536, k = 4096, seed 7) at FULL size;
+* config 3 (flat headline shape, d = 1024, k = 10 000, Zipf sizes, seed 123) on a slice of n = 1 000 000 rows;
+* config 4 (hierarchical, d = 768, two-level mixture, seed 2024) on a slice of n = 1 000 000 rows with k = 16 384
+  (128 mesoclusters; the full k = 65 536 would leave 15 points per cluster on the slice).
+
+Each flat configuration is checked twice:
+  step-wise  - pruned iterations replayed from the reference's own state (its rotated points, centroids, previous
+               assignment and d'): >= 99.9 % identical assignments, every sampled disagreement explained as a near-tie
+               or a threshold flip, not-pruned totals and the next d' as the reference's;
+  end to end - same d' schedule, WCSS within 1e-4, centroids of clusters with identical members within 1e-5, and
+               the share of identical assignments (reported; gated at the level single near-tie flips allow, see
+               the comment at the gate).
+"""
+import numpy as np
+import pytest
+
+from tests import datagen, parity_util
+
+pytestmark = pytest.mark.gpu
+
+
+def _wcss64(x, c, a, block=200_000):
+    tot = 0.0
+    for s in range(0, x.shape[0], block):
+        xs = x[s:s + block].astype(np.float64)
+        tot += float(((xs - c[a[s:s + block]].astype(np.float64)) ** 2).sum())
+    return tot
+
+
+def _identical_cluster_centroids(c, rc, a, ra, k):
+    same = np.ones(k, dtype=bool)
+    diff = a != ra
+    same[a[diff]] = False
+    same[ra[diff]] = False
+    num = np.linalg.norm(c[same].astype(np.float64) - rc[same].astype(np.float64), axis=1)
+    den = np.linalg.norm(rc[same].astype(np.float64), axis=1) + 1e-30
+    return float(same.mean()), float((num / den).max()) if same.any() else 0.0
+
+
+def _flat_against_reference(ref, x, k, seed, iters, replay, end_to_end_agree, classify_cap=150):
+    import superkmeans_b200 as skm
+    from superkmeans_b200 import engine as eng
+
+    n, d = x.shape
+    kw = dict(iters=iters, sampling_fraction=1.0, early_termination=0, seed=seed)
+    rk = ref.RefKMeans(k, d, ref.default_config(False, **kw), trace=True)
+    rc = rk.train(x)
+    m = rk.rotation_matrix()
+    trace, stats = rk.trace(), rk.stats()
+    hd, vd = eng.dimension_split(d)
+    ratios = eng.ratios(d, 1.5)
+
+    # ---- step-wise, from the reference's state
+    xr = eng.rotate(m, x)
+    rng = np.random.default_rng(1)
+    for t in replay:
+        prev, cur, st = trace[t - 1], trace[t], stats[t]
+        assert not st["is_gemm_only"]
+        pd = st["partial_d"]
+        rknn, rdist, rnp = ref.find_nearest_pruned(xr, prev.centroids, prev.assign, pd)
+        knn, dist, npc = eng.find_nearest_pruned(xr, prev.centroids, prev.assign, pd)
+        agree = float((knn == rknn).mean())
+        assert agree >= 0.999, (t, agree)
+        bad = np.nonzero(knn != rknn)[0]
+        if len(bad) > classify_cap:
+            bad = rng.choice(bad, classify_cap, replace=False)
+        sel = np.zeros(n, dtype=bool)
+        sel[bad] = True
+        a_s = np.where(sel, knn, rknn).astype(np.int64)   # only the sampled disagreements remain
+        n_tie, n_flip, unexplained = parity_util.classify_disagreements(xr, prev.centroids, prev.assign.astype(np.int64), a_s, rknn.astype(np.int64), pd, vd, ratios)
+        assert not unexplained, (t, n_tie, n_flip, unexplained[:8])
+        same = knn == rknn
+        assert np.abs(dist[same] - rdist[same]).max() <= 2e-5 * max(1.0, float(rdist.max()))
+        tot, rtot = float(npc.sum()), float(rnp.sum())
+        assert abs(tot - rtot) <= 5e-3 * rtot + 10, (tot, rtot)
+        nd, _ = eng.tune_partial_d(tot, n, k, pd, vd)
+        assert nd == cur.partial_d_next
+    del xr
+
+    # ---- end to end
+    e = skm.Engine(k, d, skm.default_config(False, **kw))
+    e.set_rotation(m)
+    c = e.train(x)
+    es = e.stats(0)
+    assert [r["partial_d"] for r in stats] == [s.partial_d for s in es]
+    ra, a = rk.assignments(), e.assignments()
+    w, rw = _wcss64(x, c, a), _wcss64(x, rc, ra)
+    assert abs(w - rw) <= 1e-4 * rw, (w, rw)
+    agree = float((ra == a).mean())
+    share, rel = _identical_cluster_centroids(e.rotated_centroids(), rk.rotated_centroids(), a, ra, k)
+    print(f"end to end: assignments equal {agree:.5f}, clusters with identical members {share:.4f}, their centroids within {rel:.2e}, wcss rel diff {abs(w - rw) / rw:.2e}")
+    assert rel < 1e-5, rel
+    # A single near-tie that falls the other way changes which clusters are empty or undersized one iteration later,
+    # and the splits spread the difference (the reference run twice with different SIMD widths shows the same); each
+    # iteration on its own is held to 99.9 % above.
+    assert agree >= end_to_end_agree, agree
+    return agree
+
+
+def test_config2_full_size_against_reference(ref):
+    x = datagen.config2()
+    _flat_against_reference(ref, x, 4096, 7, 10, replay=(1, 2, 9), end_to_end_agree=0.99)
+
+
+def test_config3_slice_against_reference(ref):
+    x = datagen.config3(n=1_000_000)
+    _flat_against_reference(ref, x, 10_000, 123, 10, replay=(1, 2, 9), end_to_end_agree=0.97)
+
+
+def test_config4_slice_hierarchical_against_reference(ref):
+    import superkmeans_b200 as skm
+
+    n, d, k, seed = 1_000_000, 768, 16_384, 2024
+    x = datagen.config4(n, d, supers=128, subs=128, seed=seed)
+    kw = dict(early_termination=0, seed=seed)
+    rk = ref.RefKMeans(k, d, ref.default_config(True, **kw), hierarchical=True)
+    rc = rk.train(x)
+    e = skm.Engine(k, d, skm.default_config(True, **kw), hierarchical=True)
+    e.set_rotation(rk.rotation_matrix())
+    c = e.train(x)
+    assert e.n_mesoclusters == rk.n_mesoclusters() == 128
+    for phase in (1, 2, 3):
+        assert len(e.stats(phase)) == len(rk.stats(phase))
+    # mesoclustering record by record
+    for r, s in zip(rk.stats(1), e.stats(1)):
+        assert r["partial_d"] == s.partial_d and r["is_gemm_only"] == bool(s.is_gemm_only)
+        assert abs(r["objective"] - s.objective) <= 1e-4 * r["objective"]
+    ra, a = rk.final_assignments(), e.assignments()
+    w, rw = _wcss64(x, c, a), _wcss64(x, rc, ra)
+    agree = float((ra == a).mean())
+    print(f"hierarchical slice: assignments equal {agree:.5f}, wcss rel diff {abs(w - rw) / rw:.2e}")
+    # a mesocluster whose member list differs by one point draws other starting centroids (hierarchical_superkmeans.h:333-342)
+    # and ends in another local optimum: the objective is the robust gate (the reference's own bar is 5 %)
+    assert abs(w - rw) <= 1e-2 * rw, (w, rw)
+    asg = e.assign(x, c)
+    atp = e.assign_training_points(x, c)
+    assert (atp == asg).mean() >= 0.98
+
+
+@pytest.mark.parametrize("fraction", [0.9, 0.3])
+def test_assign_training_points_of_sampled_models(ref, fraction):
+    """AssignTrainingPoints of a model trained on a sample (superkmeans.h:471-504 size-proportional seeds above 0.8,
+    :505-563 two-level seeds below): against the reference's own answer, and against brute force at the reference's bar
+    (tests/test_assign.cpp:163-201, python/tests/test_superkmeans.py:392-412)."""
+    import superkmeans_b200 as skm
+
+    n, d, k, seed = 40_000, 256, 600, 5
+    x = datagen.gaussian_mixture(n, d, k, 0.3, seed)
+    kw = dict(iters=8, sampling_fraction=fraction, max_points_per_cluster=100_000, early_termination=0, seed=seed, suppress_warnings=1)
+    rk = ref.RefKMeans(k, d, ref.default_config(False, **kw))
+    rc = rk.train(x)
+    e = skm.Engine(k, d, skm.default_config(False, **kw))
+    e.set_rotation(rk.rotation_matrix())
+    c = e.train(x)
+    assert e.n_samples == int(np.floor(np.float32(n) * np.float32(fraction)))
+    assert np.linalg.norm(c - rc) / np.linalg.norm(rc) < 5e-3
+    atp, ratp = e.assign_training_points(x, c), rk.assign_training_points(x, rc)
+    brute, rbrute = e.assign(x, c), rk.assign(x, rc)
+    assert (brute == rbrute).mean() >= 0.999
+    assert (atp == brute).mean() >= 0.95
+    assert (ratp == rbrute).mean() >= 0.95
+    # same seeds, same search: the two fast assignments agree far beyond the 95 % either holds against brute force
+    assert (atp == ratp).mean() >= 0.99, float((atp == ratp).mean())

@@ -43,7 +43,8 @@ def test_rotate_and_unrotate(eng, ref, n, d):
     m = eng.rotation_matrix(d, 3)
     r = eng.rotate(m, x)
     want = x.astype(np.float64) @ m.astype(np.float64).T
-    assert np.abs(r - want).max() < 1e-5 * np.sqrt(d)
+    # fp32 accumulation level: rows have norm sqrt(d), outputs are O(1); a single long chain in tensor memory would be ~1e-5 * sqrt(d) off
+    assert np.abs(r - want).max() < 1e-6 * np.sqrt(d)
     # tests/test_rotation.cpp: norms preserved, Unrotate(Rotate(x)) = x within 1e-4
     assert np.abs(np.linalg.norm(r, axis=1) - np.linalg.norm(x, axis=1)).max() < 1e-4 * np.sqrt(d)
     back = eng.unrotate(m, r)

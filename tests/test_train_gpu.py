@@ -66,10 +66,14 @@ def test_flat_train_gemm_only_matches_reference(ref, n, d, k, seed):
     x = datagen.gaussian_mixture(n, d, k, 0.3, seed)
     rk, rc, e, c = _pair(ref, skm, x, k, iters=6, sampling_fraction=1.0, early_termination=0, seed=seed, use_blas_only=1)
     _check_stats(rk.stats(), e.stats(0))
-    assert _rel_l2(c, rc) < 1e-4
     ra, a = rk.assignments(), e.assignments()
     assert (ra == a).mean() >= 0.999
     assert abs(_wcss64(x, c, a) - _wcss64(x, rc, ra)) <= 1e-4 * _wcss64(x, rc, ra)
+    # Exact iterations: the only differences are fp32 near-ties (the rotation and the products are summed in another
+    # order than OpenBLAS does).  One point that falls the other way moves two centroids by 1 / cluster size, so the
+    # 1e-4 bar holds for the clusters whose members are the same (at 1e-5) and for all centroids when no point differs.
+    assert _centroids_of_identical_clusters(e.rotated_centroids(), rk.rotated_centroids(), a, ra, k) >= 0.98
+    assert _rel_l2(c, rc) < (1e-4 if (ra == a).all() else 5e-3)
 
 
 @pytest.mark.parametrize("n,d,k,seed", [(30000, 256, 600, 4), (20000, 768, 1100, 5), (12000, 130, 520, 6), (90000, 256, 300, 7)])
