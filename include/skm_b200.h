@@ -200,6 +200,14 @@ int skm_get_prune_split(void);
  * a test can watch that path without a fault or a hang.  No counterpart in the reference. */
 skm_status skm_debug_wait_injection(uint64_t wait_limit_cycles, uint32_t producer_stops_after_kblocks);
 
+/* Profiling aid for the chain over gathered centroids (current device): SM cycles its roles spent waiting, summed over
+ * the CTAs of all launches since the last call, then cleared.  out16: [0] MMA thread waiting for the rows to hand an
+ * accumulator back, [1] waiting for a stage, [2] its whole loop; [3] a row warp waiting for an accumulator, [4] fetching
+ * centroid norms, [5] its whole loop, [6] waiting for its partner at chunk ends; [7] a gather thread waiting for a free
+ * stage, [8] for its copies, [9] its whole loop; [10] an X splitter waiting for its tile; [11] the producer waiting for
+ * a free stage; [12] (unit, segment) steps; [13] CTAs.  No counterpart in the reference. */
+skm_status skm_debug_role_cycles(uint64_t* out16);
+
 /* Kernels launched by this library in the calling process so far. */
 uint64_t skm_kernel_launches(void);
 /* Device and pinned-host allocations (cudaMalloc, cudaMallocHost) made by this library in the calling process so

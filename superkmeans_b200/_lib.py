@@ -97,6 +97,7 @@ SIGNATURES = {
     "skm_get_phase_time": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
     "skm_reset_phase_times": (C.c_int, [C.c_void_p]),
     "skm_debug_wait_injection": (C.c_int, [C.c_uint64, C.c_uint32]),
+    "skm_debug_role_cycles": (C.c_int, [C.POINTER(C.c_uint64)]),
     "skm_kernel_launches": (C.c_uint64, []),
     "skm_device_allocations": (C.c_uint64, []),
     "skm_set_prune_split": (None, [C.c_int]),

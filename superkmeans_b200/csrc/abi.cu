@@ -232,6 +232,16 @@ skm_status skm_debug_wait_injection(uint64_t wait_limit_cycles, uint32_t produce
     return guarded(g_op_error, [&] { skmb::tc::set_debug_wait_injection(static_cast<long long>(wait_limit_cycles), producer_stops_after_kblocks); });
 }
 
+skm_status skm_debug_role_cycles(uint64_t* out16) {
+    g_create_error.clear();
+    if (!out16) return SKM_INVALID_ARGUMENT;
+    return guarded(g_op_error, [&] {
+        unsigned long long tmp[16];
+        skmb::tc::role_cycles(tmp);
+        for (int i = 0; i < 16; ++i) out16[i] = tmp[i];
+    });
+}
+
 uint64_t skm_kernel_launches(void) { return skmb::kernel_launch_count(); }
 uint64_t skm_device_allocations(void) { return skmb::device_alloc_count(); }
 

@@ -31,6 +31,11 @@ struct DeviceGuard {
 
 __global__ void u64_to_f64_kernel(const unsigned long long* in, double* out) { *out = static_cast<double>(*in); }
 
+__global__ void widen_u32_kernel(const uint32_t* __restrict__ in, uint64_t* __restrict__ out, size_t n) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = in[i];
+}
+
 // Rows per staging chunk when streaming a host matrix through the GPU.
 size_t chunk_rows_for(size_t d, size_t n) {
     const size_t target_bytes = size_t{256} << 20;
@@ -490,6 +495,10 @@ void run_pruned_pass_sorted(const PrunedParams& p, PrunePassBuffers& b, float ra
     ws.alive_total = b.alive_total.ensure(1);
     ws.ratio_first = ratio_first;
     ws.flag_mult = 22;   // a point is "expensive" from 6 of 128 sampled survivors up
+    uint32_t dense_tile_rows = 16;   // a tile takes the chain when at least this many of its 128 points are expensive
+    // (tuning aids: both thresholds can be overridden from the environment)
+    if (const char* v = std::getenv("SKM_DENSE_FLAG_MULT")) ws.flag_mult = static_cast<uint32_t>(std::max(1, std::atoi(v)));
+    if (const char* v = std::getenv("SKM_DENSE_TILE_ROWS")) dense_tile_rows = static_cast<uint32_t>(std::max(1, std::atoi(v)));
 
     // candidate lists: eight per tile, each with room for an eighth of its pairs (modes 5 / 8: a thirty-second)
     const uint32_t cap_group = static_cast<uint32_t>(std::max<size_t>(128, mode == 8 ? p.k / 2 : p.k * 2));
@@ -544,7 +553,7 @@ void run_pruned_pass_sorted(const PrunedParams& p, PrunePassBuffers& b, float ra
             ws.best = best_b;
             ws.flags = flags_b;
             launch_classify(pb, ws, stream);
-            launch_tile_flags(flags_b, cnt, 16, tile_flags, stream);
+            launch_tile_flags(flags_b, cnt, dense_tile_rows, tile_flags, stream);
             SKM_CUDA(cudaMemcpyAsync(tile_flags_host, tile_flags, sizeof(uint32_t) * n_tiles, cudaMemcpyDeviceToHost, stream));
             SKM_CUDA(cudaStreamSynchronize(stream));
             for (size_t t = 0; t < n_tiles; ++t) {
@@ -1295,21 +1304,31 @@ void Engine::train_hierarchical(const float* data, size_t n, bool on_device, flo
     // the last split, exactly as in the reference; writes that would leave the index array (possible
     // only when that split moved sizes around) are dropped.
     const std::vector<uint32_t> meso_sizes(sizes_host_.begin(), sizes_host_.begin() + n_meso_);
-    std::vector<uint32_t> meso_assign(n_all);
-    SKM_CUDA(cudaMemcpyAsync(meso_assign.data(), assignments_.get(), sizeof(uint32_t) * n_all, cudaMemcpyDeviceToHost, stream_));
-    sync();
-    std::vector<uint64_t> flat(n_all, 0);
     std::vector<size_t> offsets(n_meso_ + 1, 0);
     for (size_t m = 0; m < n_meso_; ++m) offsets[m + 1] = offsets[m] + meso_sizes[m];
-    {
+    meso_indices_dev_.ensure(n_all);
+    if (n_split_ == 0 && offsets[n_meso_] == n_all) {
+        // No split in the last mesoclustering iteration: the sizes are the actual counts, and the partition is the stable
+        // sort of the point indices by mesocluster - on the device, with the update's radix sort.
+        const uint32_t* sorted_keys = nullptr;
+        const uint32_t* order = nullptr;
+        launch_sort_by_key(assignments_.get(), n_all, n_meso_, ws_, &sorted_keys, &order, stream_);
+        widen_u32_kernel<<<static_cast<unsigned>((n_all + 255) / 256), 256, 0, stream_>>>(order, meso_indices_dev_.get(), n_all);
+        note_kernel_launch();
+        SKM_CUDA(cudaGetLastError());
+    } else {
+        std::vector<uint32_t> meso_assign(n_all);
+        SKM_CUDA(cudaMemcpyAsync(meso_assign.data(), assignments_.get(), sizeof(uint32_t) * n_all, cudaMemcpyDeviceToHost, stream_));
+        sync();
+        std::vector<uint64_t> flat(n_all, 0);
         std::vector<size_t> next = offsets;
         for (size_t i = 0; i < n_all; ++i) {
             const size_t pos = next[meso_assign[i]]++;
             if (pos < n_all) flat[pos] = i;
         }
+        SKM_CUDA(cudaMemcpyAsync(meso_indices_dev_.get(), flat.data(), sizeof(uint64_t) * n_all, cudaMemcpyHostToDevice, stream_));
+        sync();
     }
-    SKM_CUDA(cudaMemcpyAsync(meso_indices_dev_.ensure(n_all), flat.data(), sizeof(uint64_t) * n_all, cudaMemcpyHostToDevice, stream_));
-    sync();
 
     // ---- phase 2: fine clustering, one mesocluster after the other (:301-425)
     const std::vector<size_t> fine_nums = arrange_fine_clusters(k_, n_meso_, n_all, meso_sizes);

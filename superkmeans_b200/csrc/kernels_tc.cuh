@@ -61,6 +61,8 @@ void launch_sparse_chain(const float* x, size_t n, size_t k, size_t d, uint32_t 
                          const float* chain_norms_y, const float* ratios, const float* best_in, uint32_t* knn, float* dist, uint32_t* not_pruned, uint2* top2_scratch,
                          const float* y_split, const uint32_t* tile_map, size_t n_tiles, const uint16_t* cols, const uint32_t* col_counts, size_t cols_stride,
                          cudaStream_t stream);
+// Profiling aid: cycles the roles of the gathered chain spent waiting, summed over CTAs since the last call (see kernels_tc_sparse.cu).
+void role_cycles(unsigned long long out[16]);
 // cols / col_counts from union bits: one warp per (tile, chunk); *total_cols += columns listed (rounded up to the 16 the
 // tensor cores process), for work accounting.
 void launch_build_cols(const uint32_t* union_bits, uint32_t union_words, size_t n_tiles, size_t k, uint16_t* cols, uint32_t* col_counts, size_t cols_stride,

@@ -62,6 +62,17 @@ struct SparseParams {
     long long wait_limit;
 };
 
+// Where the roles of sparse_chain_kernel spend their cycles, summed over the CTAs of all launches since the last read
+// (one representative thread per role): see role_cycles().
+__device__ unsigned long long g_role_cycles[16];
+
+__device__ __forceinline__ bool timed_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w, int code, long long& acc) {
+    const long long t0 = clock64();
+    const bool ok = mbar_wait(bar, parity, w, code);
+    acc += clock64() - t0;
+    return ok;
+}
+
 struct SparseMaps {
     CUtensorMap x[3];     // points, visible extent d' / vertical_d / d
 };
@@ -200,11 +211,12 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
         if (lane == 0) {
             uint32_t kbt = 0;
             bool ok = true;
+            long long w_empty = 0;
             SPARSE_FOR_EACH_UNIT_SEGMENT({
                 const CUtensorMap* mx = &maps.x[si.map];
                 for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
                     const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
-                    if (!mbar_wait(&ctrl->empty[s], ph ^ 1u, wctx, 21)) {
+                    if (!timed_wait(&ctrl->empty[s], ph ^ 1u, wctx, 21, w_empty)) {
                         ok = false;
                         break;
                     }
@@ -212,6 +224,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                     tma_load_2d(smem_base + s * STAGE_BYTES + OFF_A_HI, mx, &ctrl->full[s], static_cast<int>(si.x_begin + kb * BK), static_cast<int>(rt * BM));
                 }
             })
+            atomicAdd(&g_role_cycles[11], static_cast<unsigned long long>(w_empty));
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
@@ -219,9 +232,12 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
             uint32_t kbt = 0;
             uint32_t uses[2] = {0, 0};
             bool ok = true;
+            long long w_loaded = 0, w_conv = 0, n_steps = 0;
+            const long long t_begin = clock64();
             SPARSE_FOR_EACH_UNIT_SEGMENT({
+                ++n_steps;
                 // the rows must have read this accumulator's previous checkpoint before it grows (or restarts)
-                if (uses[a] > 0 && !mbar_wait(&ctrl->acc_loaded[a], (uses[a] - 1) & 1u, wctx, 22)) {
+                if (uses[a] > 0 && !timed_wait(&ctrl->acc_loaded[a], (uses[a] - 1) & 1u, wctx, 22, w_loaded)) {
                     ok = false;
                     break;
                 }
@@ -230,7 +246,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                 const uint32_t idesc = make_idesc(nmma);
                 for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
                     const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
-                    if (!mbar_wait(&ctrl->conv[s], ph, wctx, 23)) {
+                    if (!timed_wait(&ctrl->conv[s], ph, wctx, 23, w_conv)) {
                         ok = false;
                         break;
                     }
@@ -251,16 +267,22 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                 if (ok) umma_commit(&ctrl->acc_ready[a]);
                 ++uses[a];
             })
+            atomicAdd(&g_role_cycles[0], static_cast<unsigned long long>(w_loaded));
+            atomicAdd(&g_role_cycles[1], static_cast<unsigned long long>(w_conv));
+            atomicAdd(&g_role_cycles[2], static_cast<unsigned long long>(clock64() - t_begin));
+            atomicAdd(&g_role_cycles[12], static_cast<unsigned long long>(n_steps));
+            atomicAdd(&g_role_cycles[13], 1ull);
         }
     } else if (warp < 4) {
         // ---------------------------------------------------------------- X splitter (warps 2, 3)
         const int cid = threadIdx.x - 64;   // 0 .. 63
         uint32_t kbt = 0;
         bool ok = true;
+        long long w_full = 0;
         SPARSE_FOR_EACH_UNIT_SEGMENT({
             for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
                 const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
-                if (!mbar_wait(&ctrl->full[s], ph, wctx, 24)) {
+                if (!timed_wait(&ctrl->full[s], ph, wctx, 24, w_full)) {
                     ok = false;
                     break;
                 }
@@ -290,6 +312,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                 mbar_arrive(&ctrl->conv[s]);
             }
         })
+        if (cid == 0) atomicAdd(&g_role_cycles[10], static_cast<unsigned long long>(w_full));
     } else if (warp < 6) {
         // ---------------------------------------------------------------- centroid gather (warps 4, 5)
         // Asynchronous 16-byte copies (cp.async) from the pre-split centroid matrix straight into the stage, in the
@@ -302,6 +325,8 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
         uint32_t* rowoff = ctrl->rowoff[0][0];
         uint32_t kbt = 0;
         bool ok = true;
+        long long w_empty = 0, w_group = 0;
+        const long long t_begin = clock64();
         SPARSE_FOR_EACH_UNIT_SEGMENT({
             if (seg == 0) {
                 // element offsets of this thread's centroid rows; rows past the unit's last centroid repeat it (finite
@@ -315,7 +340,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
             for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
                 const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
                 // the MMAs that read this stage four k-blocks ago must be done before it is overwritten
-                if (!mbar_wait(&ctrl->empty[s], ph ^ 1u, wctx, 27)) {
+                if (!timed_wait(&ctrl->empty[s], ph ^ 1u, wctx, 27, w_empty)) {
                     ok = false;
                     break;
                 }
@@ -333,7 +358,9 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                 }
                 cp_async_commit();
                 if (kbt >= 2) {
+                    const long long t0 = clock64();
                     cp_async_wait_group<2>();   // everything but the two newest groups: the stage of two k-blocks ago
+                    w_group += clock64() - t0;
                     fence_proxy_async();
                     mbar_arrive(&ctrl->conv[(kbt - 2) % STAGES]);
                 }
@@ -346,6 +373,11 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
             if (kbt >= 2) mbar_arrive(&ctrl->conv[(kbt - 2) % STAGES]);
             if (kbt >= 1) mbar_arrive(&ctrl->conv[(kbt - 1) % STAGES]);
         }
+        if (gid == 0) {
+            atomicAdd(&g_role_cycles[7], static_cast<unsigned long long>(w_empty));
+            atomicAdd(&g_role_cycles[8], static_cast<unsigned long long>(w_group));
+            atomicAdd(&g_role_cycles[9], static_cast<unsigned long long>(clock64() - t_begin));
+        }
     } else {
         // (warps 6 .. 13)
         // ---------------------------------------------------------------- rows: tests at every checkpoint
@@ -356,6 +388,8 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
         uint32_t uses[2] = {0, 0};
         uint32_t xchg_uses = 0;
         bool ok = true;
+        long long w_ready = 0, w_xchg = 0, t_norms = 0;
+        const long long t_begin = clock64();
         size_t cur_lt = ~size_t{0};
         uint32_t cur_chunk = 0xFFFFFFFFu;
         size_t row = 0;
@@ -388,7 +422,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
             ctrl->xchg[slot][half][row_in_tile] = mine;
             __threadfence_block();
             mbar_arrive(&ctrl->xchg_bar);
-            if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->xchg_bar, xchg_uses & 1u, wctx, 26))) return false;
+            if (!__all_sync(0xffffffffu, timed_wait(&ctrl->xchg_bar, xchg_uses & 1u, wctx, 26, w_xchg))) return false;
             ++xchg_uses;
             const RowPartial other = ctrl->xchg[slot][half ^ 1u][row_in_tile];
             const uint32_t cnt_all = cnt + other.cnt;
@@ -501,6 +535,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
             const float thr = best * ctrl->seg_ratio[seg];
             const float nxv = row_valid ? __ldg(p.chain_norms_x + row * p.n_seg + seg) : 0.f;
             // centroid norms of this warp's share of the unit's columns at this checkpoint
+            const long long t_norms0 = clock64();
             {
                 const float* __restrict__ src = p.chain_norms_y + static_cast<size_t>(seg) * p.k + c0;
                 float cur[HS];
@@ -511,7 +546,8 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                 for (uint32_t q = 0; q < HS; ++q) ny[q * 32 + lane] = cur[q];
                 __syncwarp();
             }
-            if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->acc_ready[a], uses[a] & 1u, wctx, 25))) {
+            t_norms += clock64() - t_norms0;
+            if (!__all_sync(0xffffffffu, timed_wait(&ctrl->acc_ready[a], uses[a] & 1u, wctx, 25, w_ready))) {
                 ok = false;
                 break;
             }
@@ -634,6 +670,12 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
         if (ok && cur_lt != ~size_t{0}) {
             if (close_chunk()) close_row();
         }
+        if (warp == 6 && lane == 0) {
+            atomicAdd(&g_role_cycles[3], static_cast<unsigned long long>(w_ready));
+            atomicAdd(&g_role_cycles[4], static_cast<unsigned long long>(t_norms));
+            atomicAdd(&g_role_cycles[5], static_cast<unsigned long long>(clock64() - t_begin));
+            atomicAdd(&g_role_cycles[6], static_cast<unsigned long long>(w_xchg));
+        }
     }
 #undef SPARSE_FOR_EACH_UNIT_SEGMENT
 
@@ -686,6 +728,17 @@ __global__ void __launch_bounds__(256) build_cols_kernel(const uint32_t* __restr
 }
 
 } // namespace
+
+// Reads and clears the role cycle counters of the current device: [0] MMA thread waiting for the rows to hand an
+// accumulator back, [1] waiting for a stage, [2] its whole loop; [3] a row warp waiting for an accumulator, [4] fetching
+// centroid norms, [5] its whole loop, [6] waiting for its partner at chunk ends; [7] a gather thread waiting for a free
+// stage, [8] for its copies, [9] its whole loop; [10] an X splitter waiting for its tile; [11] the producer waiting for a
+// free stage; [12] (unit, segment) steps; [13] CTAs.
+void role_cycles(unsigned long long out[16]) {
+    SKM_CUDA(cudaMemcpyFromSymbol(out, g_role_cycles, sizeof(unsigned long long) * 16));
+    unsigned long long zero[16] = {};
+    SKM_CUDA(cudaMemcpyToSymbol(g_role_cycles, zero, sizeof(zero)));
+}
 
 void launch_build_cols(const uint32_t* union_bits, uint32_t union_words, size_t n_tiles, size_t k, uint16_t* cols, uint32_t* col_counts, size_t cols_stride,
                        unsigned long long* total_cols, cudaStream_t stream) {
