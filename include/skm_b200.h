@@ -147,10 +147,11 @@ int skm_last_prune_path(const skm_handle* h);
  * (pair, 64-dimension block) steps of the candidate-list walk (each reads 256 bytes of a centroid and of a
  * point), out3[2] rows whose candidate list overflowed and were redone densely.  For roofline accounting. */
 skm_status skm_get_prune_counters(const skm_handle* h, uint64_t* out3);
-/* Work of the chain over gathered centroids (prune path 6) so far: out2[0] rows of the tiles it processed, out2[1]
- * centroid columns its units held (each unit rounded up to a multiple of 16), summed over tiles and 1024-centroid
- * chunks; its tensor-core work is 2 * 128 * out2[1] * d flop, counted once.  For roofline accounting. */
-skm_status skm_get_chain_counters(const skm_handle* h, uint64_t* out2);
+/* Work of the chain over gathered centroids (prune path 6) so far: out3[0] rows of the tiles it processed, out3[1]
+ * centroid columns its units held (each unit rounded up to a multiple of 16), summed over tiles, passes and
+ * units - its tensor-core work is 2 * 128 * out3[1] * d flop, counted once - and out3[2] the points that the
+ * optimistic pass handed to the exact, chunk-by-chunk pass.  For roofline accounting. */
+skm_status skm_get_chain_counters(const skm_handle* h, uint64_t* out3);
 /* Objective of the last iteration accumulated in float64 (the reference sums float32). */
 double skm_last_objective_f64(const skm_handle* h);
 
@@ -188,7 +189,10 @@ int skm_get_tensor_cores(void);
  * order; 5 as 4 with a quarter of the list capacity, so that overflowing lists take their fallback; 6 ordered points,
  * gathered chain for every tile; 7 ordered points, first test + list walk for every tile; 8 as 7 with the small lists
  * of 5; 9 the automatic choice without ordering (dense chain for all points when the sampled survival is high, else
- * first test + list walk with flagged points on the dense chain).  The results do not depend on the choice (up to
+ * first test + list walk with flagged points on the dense chain); 10 ordered points, every tile through the optimistic
+ * chain pass (all thresholds from the distance to the previous centroid, the 1024-centroid chunks ignored) followed by
+ * the exact gathered chain for the points whose best candidate moves - what mode 0 does for the tiles it sends to the
+ * chain, while mode 6 runs the exact gathered chain alone.  The results do not depend on the choice (up to
  * fp32 rounding); it exists for profiling and for testing each kernel on its own.  No counterpart in the reference. */
 void skm_set_prune_split(int mode);
 int skm_get_prune_split(void);

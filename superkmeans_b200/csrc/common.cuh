@@ -179,6 +179,7 @@ void launch_tile_flags(const uint32_t* row_flags, size_t n, uint32_t threshold, 
 void launch_init_chain_rows(const uint32_t* tile_map, size_t n_tiles, size_t n, const uint32_t* prev, const float* best, uint32_t* knn, float* dist, uint32_t* not_pruned,
                             uint2* top2, cudaStream_t stream);
 void launch_classify(const PrunedParams& p, PruneSplitWorkspace& ws, cudaStream_t stream);
+void launch_iota_u32(uint32_t* out, size_t n, cudaStream_t stream);   // out[i] = i
 
 // k nearest rows of y for every row of q by ||q||^2 + ||y||^2 - 2 q.y (BatchComputer::FindKNearestNeighbors,
 // batch_computers.h:191-274): out_idx / out_dist are n_q x k, ascending by (distance, index); dots_scratch needs

@@ -511,14 +511,9 @@ void run_pruned_pass_sorted(const PrunedParams& p, PrunePassBuffers& b, float ra
     b.last_n_hard = 0;
     b.last_n_redo = 0;
 
-    // The chain over the tiles listed in map_host[0 .. n_t) (host) / map_dev (device copy of the same list).
-    auto run_chain_tiles = [&](const uint32_t* map_dev, size_t n_t, size_t rows_in_batch) {
-        if (n_t == 0) return;
-        SubPhase sub(timers, PH_PRUNE_DENSE, stream);
-        float* chain_norms_xb = b.chain_norms_x.ensure(batch * n_ck);
-        // cumulative norms for all rows of the batch are cheap next to what follows, and keep the indexing plain
-        launch_chain_norms(xb, rows_in_batch, p.d, p.partial_d, p.vertical_d, p.horizontal_d, false, chain_norms_xb, stream);
-        launch_init_chain_rows(map_dev, n_t, rows_in_batch, prev_b, best_b, knn_b, dist_b, np_b, top2_b, stream);
+    // The exact chain (chunk by chunk) over the tiles map_dev[0 .. n_t) of the row set (x_rows, n_rows) with its per-row arrays.
+    auto exact_chain = [&](const float* x_rows, size_t n_rows, const uint32_t* map_dev, size_t n_t, const float* nx, const float* best, uint32_t* knn, float* dist, uint32_t* np,
+                           uint2* top2, const float* chain_nx) {
         const size_t per = std::min(n_t, chain_per_launch);
         uint32_t* ubits = b.union_bits.ensure(per * union_words);
         uint16_t* cols = b.cols.ensure(per * cols_stride);
@@ -526,15 +521,78 @@ void run_pruned_pass_sorted(const PrunedParams& p, PrunePassBuffers& b, float ra
         for (size_t t0 = 0; t0 < n_t; t0 += per) {
             const size_t nt = std::min(per, n_t - t0);
             SKM_CUDA(cudaMemsetAsync(ubits, 0, sizeof(uint32_t) * nt * union_words, stream));
-            tc::launch_union(xb, rows_in_batch, p.k, p.d, p.partial_d, nx_b, p.norms_y, best_b, ratio_first, map_dev + t0, nt, ubits, union_words, y_split, stream);
+            tc::launch_union(x_rows, n_rows, p.k, p.d, p.partial_d, nx, p.norms_y, best, ratio_first, map_dev + t0, nt, ubits, union_words, y_split, stream);
             tc::launch_build_cols(ubits, union_words, nt, p.k, cols, counts, cols_stride, sparse_cols, stream);
-            tc::launch_sparse_chain(xb, rows_in_batch, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, chain_norms_xb, chain_norms_y, p.ratios, best_b, knn_b, dist_b, np_b,
-                                    top2_b, y_split, map_dev + t0, nt, cols, counts, cols_stride, stream);
+            tc::launch_sparse_chain(x_rows, n_rows, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, chain_nx, chain_norms_y, p.ratios, best, knn, dist, np, top2, y_split,
+                                    map_dev + t0, nt, cols, counts, cols_stride, stream);
         }
-        tc::launch_refine_chain_tiles(xb, p.y, rows_in_batch, p.k, p.d, top2_b, knn_b, dist_b, map_dev, n_t, stream);
+        tc::launch_refine_chain_tiles(x_rows, p.y, n_rows, p.k, p.d, top2, knn, dist, map_dev, n_t, stream);
+    };
+
+    // The chain over the tiles listed in map_dev[0 .. n_t) of the current batch.  With `optimistic` every tile first takes
+    // the pass that ignores the chunk structure and assumes that no point's best candidate changes; the points for which
+    // that does not hold are gathered (their order kept) and redone exactly.
+    const bool optimistic = (mode == 0 || mode == 10) && p.k <= 65536 && std::getenv("SKM_NO_OPTIMISTIC_CHAIN") == nullptr;
+    auto run_chain_tiles = [&](const uint32_t* map_dev, size_t n_t, size_t rows_in_batch) {
+        if (n_t == 0) return;
+        SubPhase sub(timers, PH_PRUNE_DENSE, stream);
+        float* chain_norms_xb = b.chain_norms_x.ensure(batch * n_ck);
+        // cumulative norms for all rows of the batch are cheap next to what follows, and keep the indexing plain
+        launch_chain_norms(xb, rows_in_batch, p.d, p.partial_d, p.vertical_d, p.horizontal_d, false, chain_norms_xb, stream);
+        launch_init_chain_rows(map_dev, n_t, rows_in_batch, prev_b, best_b, knn_b, dist_b, np_b, top2_b, stream);
         b.total_sparse_rows += n_t * kTileM;
         b.total_dense_rows += n_t * kTileM;
         b.last_n_hard += n_t * kTileM;
+        if (!optimistic) {
+            exact_chain(xb, rows_in_batch, map_dev, n_t, nx_b, best_b, knn_b, dist_b, np_b, top2_b, chain_norms_xb);
+            return;
+        }
+        uint32_t* dirty_b = b.dirty_b.ensure(batch);
+        SKM_CUDA(cudaMemsetAsync(dirty_b, 0, sizeof(uint32_t) * rows_in_batch, stream));
+        {
+            const size_t per = std::min(n_t, chain_per_launch);
+            uint32_t* ubits = b.union_bits.ensure(per * union_words);
+            uint16_t* cols = b.cols.ensure(per * cols_stride);
+            uint32_t* totals = b.col_counts.ensure(per * n_chunks);
+            for (size_t t0 = 0; t0 < n_t; t0 += per) {
+                const size_t nt = std::min(per, n_t - t0);
+                SKM_CUDA(cudaMemsetAsync(ubits, 0, sizeof(uint32_t) * nt * union_words, stream));
+                tc::launch_union(xb, rows_in_batch, p.k, p.d, p.partial_d, nx_b, p.norms_y, best_b, ratio_first, map_dev + t0, nt, ubits, union_words, y_split, stream);
+                tc::launch_build_flat_cols(ubits, union_words, nt, p.k, cols, totals, cols_stride, sparse_cols, stream);
+                tc::launch_sparse_chain(xb, rows_in_batch, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, chain_norms_xb, chain_norms_y, p.ratios, best_b, knn_b, dist_b, np_b,
+                                        top2_b, y_split, map_dev + t0, nt, cols, totals, cols_stride, stream, dirty_b);
+            }
+        }
+        // the points whose best candidate moves: gathered in order, redone chunk by chunk
+        PruneSplitWorkspace cw;
+        cw.positions = b.positions.ensure(prune_split_positions_elems(batch));
+        cw.hard_idx = b.hard_idx.ensure(batch);
+        cw.n_hard_dev = b.n_hard_dev.ensure(1);
+        launch_compact_flags(dirty_b, rows_in_batch, cw, stream);
+        SKM_CUDA(cudaMemcpyAsync(&counters_host[0], cw.n_hard_dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
+        SKM_CUDA(cudaStreamSynchronize(stream));
+        const size_t n_dirty = static_cast<size_t>(counters_host[0] & 0xFFFFFFFFull);
+        b.total_redone_rows += n_dirty;
+        if (n_dirty == 0) return;
+        const size_t nt_d = (n_dirty + kTileM - 1) / kTileM;
+        float* xd = b.listed_x.ensure(n_dirty * p.d);
+        float* best_d = b.listed_best.ensure(n_dirty);
+        uint32_t* knn_d = b.listed_knn.ensure(n_dirty);
+        uint32_t* prev_d = b.redo_prev.ensure(n_dirty);
+        float* dist_d = b.listed_dist.ensure(n_dirty);
+        uint32_t* np_d = b.listed_np.ensure(n_dirty);
+        float* nx_d = b.redo_nx.ensure(n_dirty);
+        uint2* top2_d = b.listed_top2.ensure(n_dirty);
+        float* chain_nd = b.listed_norms.ensure(n_dirty * n_ck);
+        uint32_t* iota = b.tile_iota.ensure(nt_d);
+        launch_gather_listed(xb, best_b, prev_b, cw.hard_idx, n_dirty, p.d, xd, best_d, knn_d, stream);
+        SKM_CUDA(cudaMemcpyAsync(prev_d, knn_d, sizeof(uint32_t) * n_dirty, cudaMemcpyDeviceToDevice, stream));
+        launch_row_sqnorms(xd, n_dirty, p.d, p.partial_d, nx_d, stream);
+        launch_chain_norms(xd, n_dirty, p.d, p.partial_d, p.vertical_d, p.horizontal_d, false, chain_nd, stream);
+        launch_iota_u32(iota, nt_d, stream);
+        launch_init_chain_rows(iota, nt_d, n_dirty, prev_d, best_d, knn_d, dist_d, np_d, top2_d, stream);
+        exact_chain(xd, n_dirty, iota, nt_d, nx_d, best_d, knn_d, dist_d, np_d, top2_d, chain_nd);
+        launch_scatter_listed(cw.hard_idx, n_dirty, knn_d, dist_d, np_d, knn_b, dist_b, np_b, stream);
     };
 
     for (size_t b0 = 0; b0 < p.n; b0 += batch) {
@@ -560,7 +618,7 @@ void run_pruned_pass_sorted(const PrunedParams& p, PrunePassBuffers& b, float ra
                 if (tile_flags_host[t]) map_host[n_dense++] = static_cast<uint32_t>(t);
                 else map_host[batch_tiles + n_lists++] = static_cast<uint32_t>(t);
             }
-        } else if (mode == 6) {
+        } else if (mode == 6 || mode == 10) {
             for (size_t t = 0; t < n_tiles; ++t) map_host[n_dense++] = static_cast<uint32_t>(t);
         } else {
             for (size_t t = 0; t < n_tiles; ++t) map_host[batch_tiles + n_lists++] = static_cast<uint32_t>(t);
@@ -657,11 +715,11 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
     };
     if (p.n == 0) return;
     int mode = g_prune_split_mode;
-    if ((mode == 0 || (mode >= 6 && mode <= 8)) && tc::eligible(p.x, p.d, p.y, p.d)) {
+    if ((mode == 0 || (mode >= 6 && mode <= 8) || mode == 10) && tc::eligible(p.x, p.d, p.y, p.d)) {
         run_pruned_pass_sorted(p, b, ratio_first, device, stream, timers, mode);
         return;
     }
-    if (mode >= 6 && mode <= 8) throw std::invalid_argument("the ordered pruned pass needs 16-byte aligned rows (d % 4 == 0) and the tensor-core kernels switched on");
+    if ((mode >= 6 && mode <= 8) || mode == 10) throw std::invalid_argument("the ordered pruned pass needs 16-byte aligned rows (d % 4 == 0) and the tensor-core kernels switched on");
     if (mode == 9) mode = 0;
     if (b.grid == 0) b.grid = pruned_grid_size(device);
     const uint32_t n_ck = prune_chain_checkpoints(p.partial_d, p.vertical_d, p.horizontal_d);

@@ -141,7 +141,8 @@ struct PrunePassBuffers {
     UpdateWorkspace sort_ws;
     DeviceBuffer<uint32_t> sort_keys_a, sort_keys_b, sort_vals_a, sort_vals_b, sort_table;
     DeviceBuffer<float> xb, best_b, dist_b, nx_b;
-    DeviceBuffer<uint32_t> knn_b, prev_b, np_b, flags_b, tile_flags, tile_map_dense, tile_map_lists, union_bits, col_counts;
+    DeviceBuffer<uint32_t> knn_b, prev_b, np_b, flags_b, tile_flags, tile_map_dense, tile_map_lists, union_bits, col_counts, dirty_b, redo_prev, tile_iota;
+    DeviceBuffer<float> redo_nx;
     DeviceBuffer<uint16_t> cols;
     DeviceBuffer<uint2> top2_b;
     DeviceBuffer<unsigned long long> sparse_cols_dev;
@@ -149,6 +150,7 @@ struct PrunePassBuffers {
     // totals since creation: rows of tiles sent through the gathered chain, centroid columns (rounded to 16) its units
     // held, summed over tiles and chunks - the chain's tensor-core work is 2 * 128 * columns * d flop (counted once)
     unsigned long long total_sparse_rows = 0, total_sparse_cols = 0;
+    unsigned long long total_redone_rows = 0;   // points of the optimistic chain pass that had to be redone exactly
 };
 // mode: 0 = automatic: with rows that TMA can address, the points are taken in the order of their previous centroid and
 // every tile of 128 goes either through the first test + list walk or, when many of its points keep a large share of
@@ -158,7 +160,9 @@ struct PrunePassBuffers {
 // to a quarter so that the overflow route runs, 6 = ordered points, gathered chain for every tile, 7 = ordered points,
 // first test + list walk for every tile (overflowing tiles through the gathered chain), 8 = as 7 with the small lists
 // of mode 5, 9 = the automatic choice without ordering (dense chain for all points when the sampled survival rate is
-// high, else first test + list walk with flagged points on the dense chain).
+// high, else first test + list walk with flagged points on the dense chain), 10 = ordered points, every tile through
+// the optimistic chain pass with the exact gathered chain for the points it flags (mode 0 does the same for the tiles
+// it sends to the chain; mode 6 uses the exact gathered chain alone).
 void set_prune_split_mode(int mode);
 int prune_split_mode();
 void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, int device, cudaStream_t stream, PhaseTimers* timers = nullptr);
@@ -196,9 +200,10 @@ class Engine {
         out[1] = prune_bufs_.total_pair_steps;
         out[2] = prune_bufs_.total_redo_rows;
     }
-    void chain_counters(uint64_t out[2]) const {
+    void chain_counters(uint64_t out[3]) const {
         out[0] = prune_bufs_.total_sparse_rows;
         out[1] = prune_bufs_.total_sparse_cols;
+        out[2] = prune_bufs_.total_redone_rows;
     }
     const std::vector<skm_iter_stats>& stats(int phase) const;
     int device() const { return device_; }

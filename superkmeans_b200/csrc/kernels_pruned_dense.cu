@@ -481,6 +481,17 @@ void launch_classify(const PrunedParams& p, PruneSplitWorkspace& ws, cudaStream_
     SKM_LAUNCH_CHECK();
 }
 
+__global__ void iota_u32_kernel(uint32_t* __restrict__ out, size_t n) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = static_cast<uint32_t>(i);
+}
+
+void launch_iota_u32(uint32_t* out, size_t n, cudaStream_t stream) {
+    if (n == 0) return;
+    iota_u32_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(out, n);
+    SKM_LAUNCH_CHECK();
+}
+
 void launch_compact_flags(const uint32_t* flags, size_t n, PruneSplitWorkspace& ws, cudaStream_t stream) {
     if (n == 0) return;
     copy_u32_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(flags, ws.positions, n);

@@ -60,7 +60,14 @@ void launch_union(const float* x, size_t n, size_t k, size_t d, uint32_t partial
 void launch_sparse_chain(const float* x, size_t n, size_t k, size_t d, uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d, const float* chain_norms_x,
                          const float* chain_norms_y, const float* ratios, const float* best_in, uint32_t* knn, float* dist, uint32_t* not_pruned, uint2* top2_scratch,
                          const float* y_split, const uint32_t* tile_map, size_t n_tiles, const uint16_t* cols, const uint32_t* col_counts, size_t cols_stride,
-                         cudaStream_t stream);
+                         cudaStream_t stream, uint32_t* dirty = nullptr);
+// With `dirty` the call is the OPTIMISTIC pass instead: cols holds ONE ascending list of global centroid indices per tile
+// (launch_build_flat_cols; col_counts = the list lengths, cols_stride >= k <= 65536) and every threshold comes from
+// best_in alone, as if no point's best candidate changed during the search.  Written: not_pruned (first-test survivors)
+// and dirty (1 = some centroid other than the previous one survived every test and ended below best_in; such a point
+// must be redone by the exact call, all others keep their assignment and distance).  knn is only read.
+void launch_build_flat_cols(const uint32_t* union_bits, uint32_t union_words, size_t n_tiles, size_t k, uint16_t* cols, uint32_t* totals, size_t cols_stride,
+                            unsigned long long* total_cols, cudaStream_t stream);
 // Profiling aid: cycles the roles of the gathered chain spent waiting, summed over CTAs since the last call (see kernels_tc_sparse.cu).
 void role_cycles(unsigned long long out[16]);
 // cols / col_counts from union bits: one warp per (tile, chunk); *total_cols += columns listed (rounded up to the 16 the

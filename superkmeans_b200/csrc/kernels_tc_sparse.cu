@@ -51,6 +51,7 @@ struct SparseParams {
     float* dist;
     uint32_t* not_pruned;
     uint2* top2;                    // out: the two smallest final distances seen by the chain, per point
+    uint32_t* dirty;                // optimistic pass only, out: 1 = the point has to be redone by the exact chain
     const float* y_hi;              // k x d, tf32 hi parts of the centroids
     const float* y_lo;              // k x d, tf32 lo parts
     const uint32_t* tile_map;       // n_tiles row-tile indices
@@ -69,6 +70,13 @@ __device__ unsigned long long g_role_cycles[16];
 __device__ __forceinline__ bool timed_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w, int code, long long& acc) {
     const long long t0 = clock64();
     const bool ok = mbar_wait(bar, parity, w, code);
+    acc += clock64() - t0;
+    return ok;
+}
+// for the roles that run ahead of the tensor pipe (TMA producer, X splitter, centroid gather)
+__device__ __forceinline__ bool timed_wait_relaxed(uint64_t* bar, uint32_t parity, const WaitCtx& w, int code, long long& acc) {
+    const long long t0 = clock64();
+    const bool ok = mbar_wait_relaxed(bar, parity, w, code);
     acc += clock64() - t0;
     return ok;
 }
@@ -173,6 +181,9 @@ constexpr int SPARSE_THREADS = 448;
         }                                                                                                 \
     }
 
+// MERGED = false: the exact chain, chunk by chunk.  MERGED = true: the optimistic pass (see merged_rows below): the
+// lists are one per tile (n_chunks = 1, global centroid indices), and the rows' threads only count and look for a winner.
+template <bool MERGED>
 __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const __grid_constant__ SparseMaps maps, const SparseParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
@@ -216,7 +227,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                 const CUtensorMap* mx = &maps.x[si.map];
                 for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
                     const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
-                    if (!timed_wait(&ctrl->empty[s], ph ^ 1u, wctx, 21, w_empty)) {
+                    if (!timed_wait_relaxed(&ctrl->empty[s], ph ^ 1u, wctx, 21, w_empty)) {
                         ok = false;
                         break;
                     }
@@ -282,7 +293,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
         SPARSE_FOR_EACH_UNIT_SEGMENT({
             for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
                 const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
-                if (!timed_wait(&ctrl->full[s], ph, wctx, 24, w_full)) {
+                if (!timed_wait_relaxed(&ctrl->full[s], ph, wctx, 24, w_full)) {
                     ok = false;
                     break;
                 }
@@ -340,7 +351,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
             for (uint32_t kb = 0; kb < si.n_kb; ++kb, ++kbt) {
                 const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
                 // the MMAs that read this stage four k-blocks ago must be done before it is overwritten
-                if (!timed_wait(&ctrl->empty[s], ph ^ 1u, wctx, 27, w_empty)) {
+                if (!timed_wait_relaxed(&ctrl->empty[s], ph ^ 1u, wctx, 27, w_empty)) {
                     ok = false;
                     break;
                 }
@@ -377,6 +388,189 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
             atomicAdd(&g_role_cycles[7], static_cast<unsigned long long>(w_empty));
             atomicAdd(&g_role_cycles[8], static_cast<unsigned long long>(w_group));
             atomicAdd(&g_role_cycles[9], static_cast<unsigned long long>(clock64() - t_begin));
+        }
+    } else if (MERGED) {
+        // (warps 6 .. 13)
+        // ---------------------------------------------------------------- rows, optimistic pass
+        // The chain is run once over ALL the centroids a tile can still reach, in units that ignore the 1024-centroid
+        // chunks, with every threshold taken from the distance to the previous centroid.  That is exactly what the
+        // chunk-by-chunk search does for a point whose `best` never changes on the way - the common case once the
+        // clustering settles.  A point for which some other centroid survives every test and ends below that distance
+        // would have had its `best` lowered at that centroid's chunk, and its later chunks tested more strictly: it is
+        // flagged (`dirty`) and redone by the exact kernel; for all others the survivor count and the (unchanged)
+        // assignment are final.
+        const uint32_t half = static_cast<uint32_t>(warp - 6) >> 2;
+        const uint32_t quarter = static_cast<uint32_t>(warp) & 3u;
+        const uint32_t lane_base = 32u * quarter;
+        const uint32_t row_in_tile = lane_base + lane;
+        uint32_t uses[2] = {0, 0};
+        uint32_t xchg_uses = 0;
+        bool ok = true;
+        long long w_ready = 0, w_xchg = 0, t_norms = 0;
+        const long long t_begin = clock64();
+        size_t cur_lt = ~size_t{0};
+        size_t row = 0;
+        bool row_valid = false;
+        float best = -1.f;
+        uint32_t prev = 0xFFFFFFFFu, cnt = 0, dirty = 0;
+        constexpr int HS = BN / 64;
+        uint32_t alive0[HS], alive1[HS];
+#pragma unroll
+        for (int q = 0; q < HS; ++q) alive0[q] = alive1[q] = 0;
+        float* ny = ctrl->ny[warp - 6];
+        auto close_row = [&]() -> bool {
+            RowPartial mine{};
+            mine.cnt = cnt;
+            mine.prev_first = dirty;
+            const uint32_t slot = xchg_uses & 1u;
+            ctrl->xchg[slot][half][row_in_tile] = mine;
+            __threadfence_block();
+            mbar_arrive(&ctrl->xchg_bar);
+            if (!__all_sync(0xffffffffu, timed_wait(&ctrl->xchg_bar, xchg_uses & 1u, wctx, 26, w_xchg))) return false;
+            ++xchg_uses;
+            if (row_valid && half == 0) {
+                const RowPartial other = ctrl->xchg[slot][1][row_in_tile];
+                p.not_pruned[row] = cnt + other.cnt;
+                p.dirty[row] = (dirty | other.prev_first) ? 1u : 0u;
+            }
+            return true;
+        };
+        SPARSE_FOR_EACH_UNIT_SEGMENT({
+            if (lt != cur_lt) {
+                if (cur_lt != ~size_t{0} && !close_row()) {
+                    ok = false;
+                    break;
+                }
+                cur_lt = lt;
+                row = rt * BM + row_in_tile;
+                row_valid = row < p.n;
+                best = row_valid ? p.best_in[row] : -1.f;
+                prev = row_valid ? p.knn[row] : 0xFFFFFFFFu;
+                cnt = 0;
+                dirty = 0;
+            }
+            const bool first = seg == 0, last = (seg + 1 == p.n_seg);
+            const uint32_t hw = ((nu + 63u) >> 6) << 5;
+            const uint32_t hb = half * hw;
+            const uint32_t my_cols = nu > hb ? min(hw, nu - hb) : 0u;
+            const uint32_t n_sl = (my_cols + 31u) >> 5;
+            uint16_t* colid = ctrl->colid[warp - 6][a];
+            uint32_t cidx[HS];
+            if (first) {
+#pragma unroll
+                for (uint32_t q = 0; q < HS; ++q) {
+                    const uint32_t j = q * 32 + lane;
+                    cidx[q] = j < my_cols ? static_cast<uint32_t>(__ldg(unit_cols + hb + j)) : 0u;
+                    colid[j] = static_cast<uint16_t>(cidx[q]);
+                }
+                __syncwarp();
+            } else {
+#pragma unroll
+                for (uint32_t q = 0; q < HS; ++q) cidx[q] = colid[q * 32 + lane];
+            }
+            const float thr = best * ctrl->seg_ratio[seg];
+            const float nxv = row_valid ? __ldg(p.chain_norms_x + row * p.n_seg + seg) : 0.f;
+            const long long t_norms0 = clock64();
+            {
+                const float* __restrict__ src = p.chain_norms_y + static_cast<size_t>(seg) * p.k;
+                float cur[HS];
+#pragma unroll
+                for (uint32_t q = 0; q < HS; ++q) cur[q] = (q * 32 + lane < my_cols) ? __ldg(src + cidx[q]) : 0.f;
+                __syncwarp();
+#pragma unroll
+                for (uint32_t q = 0; q < HS; ++q) ny[q * 32 + lane] = cur[q];
+                __syncwarp();
+            }
+            t_norms += clock64() - t_norms0;
+            if (!__all_sync(0xffffffffu, timed_wait(&ctrl->acc_ready[a], uses[a] & 1u, wctx, 25, w_ready))) {
+                ok = false;
+                break;
+            }
+            ++uses[a];
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + (lane_base << 16) + a * BN + hb;
+            uint32_t alive[HS];
+#pragma unroll
+            for (int q = 0; q < HS; ++q) alive[q] = a ? alive1[q] : alive0[q];
+            auto test_slice = [&](const uint32_t sl, const uint32_t (&r)[32], uint32_t& alive_ch) {
+                const uint32_t cb0 = sl * 32;
+                uint32_t w = 0;
+#pragma unroll
+                for (uint32_t j = 0; j < 32; j += 4) {
+                    const float4 nyv = *reinterpret_cast<const float4*>(ny + cb0 + j);
+                    const float p0 = fmaf(-2.0f, __uint_as_float(r[j + 0]), nxv) + nyv.x;
+                    const float p1 = fmaf(-2.0f, __uint_as_float(r[j + 1]), nxv) + nyv.y;
+                    const float p2 = fmaf(-2.0f, __uint_as_float(r[j + 2]), nxv) + nyv.z;
+                    const float p3 = fmaf(-2.0f, __uint_as_float(r[j + 3]), nxv) + nyv.w;
+                    w |= (p0 < thr ? (1u << j) : 0u) | (p1 < thr ? (2u << j) : 0u) | (p2 < thr ? (4u << j) : 0u) | (p3 < thr ? (8u << j) : 0u);
+                }
+                if (first) {
+                    const uint32_t lo = sl * 32;
+                    const uint32_t valid = (my_cols >= lo + 32) ? 0xFFFFFFFFu : (my_cols > lo ? ((1u << (my_cols - lo)) - 1u) : 0u);
+                    alive_ch = w & valid;
+                    cnt += __popc(alive_ch);
+                } else {
+                    alive_ch &= w;
+                }
+                if (last) {
+                    // survivors of every test, the last one being "below the distance to the previous centroid" (ratio[d] == 1):
+                    // any of them other than the previous centroid itself means `best` would have moved
+                    uint32_t m = alive_ch;
+                    while (m) {
+                        const uint32_t j = __ffs(m) - 1;
+                        m &= m - 1;
+                        if (static_cast<uint32_t>(colid[cb0 + j]) != prev) dirty = 1u;
+                    }
+                }
+            };
+            uint32_t ra[32], rb[32];
+            if (n_sl <= 2) {
+                if (n_sl > 0) tmem_ld32_issue(taddr, ra);
+                if (n_sl > 1) tmem_ld32_issue(taddr + 32, rb);
+                if (n_sl > 0) tmem_ld_wait(ra);
+                if (n_sl > 1) tmem_ld_wait(rb);
+                tc_fence_before();
+                mbar_arrive(&ctrl->acc_loaded[a]);
+                if (n_sl > 0) test_slice(0, ra, alive[0]);
+                if (n_sl > 1) test_slice(1, rb, alive[1]);
+            } else {
+                tmem_ld32_issue(taddr, ra);
+                tmem_ld_wait(ra);
+                bool handed_back = false;
+#pragma unroll 1
+                for (uint32_t ch = 0; ch < HS; ch += 2) {
+                    const bool has0 = ch < n_sl, has1 = ch + 1 < n_sl, has2 = ch + 2 < n_sl;
+                    if (has1) tmem_ld32_issue(taddr + (ch + 1) * 32, rb);
+                    if (has0) test_slice(ch, ra, alive[0]);
+                    if (has1) tmem_ld_wait(rb);
+                    if (has2) {
+                        tmem_ld32_issue(taddr + (ch + 2) * 32, ra);
+                    } else if (!handed_back) {
+                        tc_fence_before();
+                        mbar_arrive(&ctrl->acc_loaded[a]);
+                        handed_back = true;
+                    }
+                    if (has1) test_slice(ch + 1, rb, alive[1]);
+                    if (has2) tmem_ld_wait(ra);
+                    const uint32_t m0 = alive[0], m1 = alive[1];
+#pragma unroll
+                    for (int q = 0; q < HS - 2; ++q) alive[q] = alive[q + 2];
+                    alive[HS - 2] = m0;
+                    alive[HS - 1] = m1;
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < HS; ++q) {
+                if (a) alive1[q] = alive[q];
+                else alive0[q] = alive[q];
+            }
+        })
+        if (ok && cur_lt != ~size_t{0}) close_row();
+        if (warp == 6 && lane == 0) {
+            atomicAdd(&g_role_cycles[3], static_cast<unsigned long long>(w_ready));
+            atomicAdd(&g_role_cycles[4], static_cast<unsigned long long>(t_norms));
+            atomicAdd(&g_role_cycles[5], static_cast<unsigned long long>(clock64() - t_begin));
+            atomicAdd(&g_role_cycles[6], static_cast<unsigned long long>(w_xchg));
         }
     } else {
         // (warps 6 .. 13)
@@ -753,7 +947,7 @@ void launch_build_cols(const uint32_t* union_bits, uint32_t union_words, size_t 
 void launch_sparse_chain(const float* x, size_t n, size_t k, size_t d, uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d, const float* chain_norms_x,
                          const float* chain_norms_y, const float* ratios, const float* best_in, uint32_t* knn, float* dist, uint32_t* not_pruned, uint2* top2_scratch,
                          const float* y_split, const uint32_t* tile_map, size_t n_tiles, const uint16_t* cols, const uint32_t* col_counts, size_t cols_stride,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, uint32_t* dirty) {
     if (n_tiles == 0 || n == 0 || k == 0) return;
     if (k * d >= (size_t{1} << 32)) throw std::invalid_argument("centroid matrix too large for the gathered chain (k * d must stay below 2^32)");
     int device = 0;
@@ -788,11 +982,70 @@ void launch_sparse_chain(const float* x, size_t n, size_t k, size_t d, uint32_t 
     p.cols_stride = cols_stride;
     p.error = error_word();
     p.wait_limit = wait_limit();
-    SKM_CUDA(cudaFuncSetAttribute(sparse_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S_SMEM_BYTES)));
     int sms = 0;
     SKM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
     const int grid = static_cast<int>(std::min<size_t>(n_tiles, static_cast<size_t>(sms)));
-    sparse_chain_kernel<<<grid, SPARSE_THREADS, S_SMEM_BYTES, stream>>>(maps, p);
+    if (dirty) {
+        // optimistic pass: one list per tile, global indices
+        if (k > 65536) throw std::invalid_argument("the optimistic chain pass indexes centroids with 16 bits (k <= 65536)");
+        p.n_chunks = 1;
+        p.dirty = dirty;
+        SKM_CUDA(cudaFuncSetAttribute(sparse_chain_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S_SMEM_BYTES)));
+        sparse_chain_kernel<true><<<grid, SPARSE_THREADS, S_SMEM_BYTES, stream>>>(maps, p);
+    } else {
+        SKM_CUDA(cudaFuncSetAttribute(sparse_chain_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S_SMEM_BYTES)));
+        sparse_chain_kernel<false><<<grid, SPARSE_THREADS, S_SMEM_BYTES, stream>>>(maps, p);
+    }
+    note_kernel_launch();
+    SKM_CUDA(cudaGetLastError());
+}
+
+// One warp per tile: all set bits of the tile's union words as ascending global centroid indices, and their number.
+__global__ void __launch_bounds__(256) build_flat_cols_kernel(const uint32_t* __restrict__ union_bits, uint32_t union_words, size_t n_tiles, size_t k,
+                                                              uint16_t* __restrict__ cols, uint32_t* __restrict__ totals, size_t cols_stride,
+                                                              unsigned long long* __restrict__ total_cols) {
+    const size_t t = static_cast<size_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (t >= n_tiles) return;
+    uint32_t base = 0;
+    uint16_t* out_tile = cols + t * cols_stride;
+    for (uint32_t w0 = 0; w0 < union_words; w0 += 32) {
+        const uint32_t word = w0 + lane;
+        uint32_t bits = word < union_words ? union_bits[t * union_words + word] : 0u;
+        const size_t first = static_cast<size_t>(word) * 32;
+        if (first + 32 > k) bits &= first >= k ? 0u : ((1u << (k - first)) - 1u);
+        const uint32_t c = __popc(bits);
+        uint32_t incl = c;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t v = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) incl += v;
+        }
+        uint16_t* out = out_tile + base + (incl - c);
+        uint32_t m = bits;
+        while (m) {
+            const uint32_t b = __ffs(m) - 1;
+            m &= m - 1;
+            *out++ = static_cast<uint16_t>(first + b);
+        }
+        base += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) {
+        totals[t] = base;
+        if (total_cols && base) {
+            const uint32_t n_units = base <= 16u ? 1u : max(2u, (base + BN - 1) / BN);
+            const uint32_t unit_w = (((base + n_units - 1) / n_units) + 15u) & ~15u;
+            unsigned long long cols16 = 0;
+            for (uint32_t u = 0; u * unit_w < base; ++u) cols16 += (min(unit_w, base - u * unit_w) + 15u) & ~15u;
+            atomicAdd(total_cols, cols16);
+        }
+    }
+}
+
+void launch_build_flat_cols(const uint32_t* union_bits, uint32_t union_words, size_t n_tiles, size_t k, uint16_t* cols, uint32_t* totals, size_t cols_stride,
+                            unsigned long long* total_cols, cudaStream_t stream) {
+    if (n_tiles == 0 || k == 0) return;
+    build_flat_cols_kernel<<<static_cast<unsigned>((n_tiles + 7) / 8), 256, 0, stream>>>(union_bits, union_words, n_tiles, k, cols, totals, cols_stride, total_cols);
     note_kernel_launch();
     SKM_CUDA(cudaGetLastError());
 }

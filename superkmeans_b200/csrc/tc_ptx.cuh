@@ -92,6 +92,25 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     return true;
 }
 
+// The same wait for roles that are not on the critical path (producers running ahead): between polls the warp sleeps a
+// few dozen nanoseconds, which leaves the issue slots of its scheduler to the warps that do the arithmetic.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, const WaitCtx& w, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(48);
+        if ((++spins & 255u) == 0) {
+            if (*reinterpret_cast<volatile int*>(w.error) != 0) return false;
+            if (clock64() - t0 > w.limit) {
+                atomicCAS(w.error, 0, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* tmap, uint64_t* bar, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_dst),
                  "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y)

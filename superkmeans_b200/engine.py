@@ -149,9 +149,9 @@ class Engine:
 
     def chain_counters(self) -> dict:
         """Work of the chain over gathered centroids so far: rows of its tiles, centroid columns of its units (see skm_get_chain_counters)."""
-        out = (C.c_uint64 * 2)()
+        out = (C.c_uint64 * 3)()
         check(lib.skm_get_chain_counters(self._h, out), self._h)
-        return {"rows": int(out[0]), "columns": int(out[1])}
+        return {"rows": int(out[0]), "columns": int(out[1]), "redone_rows": int(out[2])}
 
     @property
     def last_objective_f64(self) -> float:
@@ -277,7 +277,7 @@ def tensor_cores_enabled() -> bool:
 def set_prune_split(mode: int) -> None:
     """0 = automatic (ordered points, per-tile route), 1 = SIMT candidate lists, 2 = dense SIMT chain, 3 = dense tensor-core chain, 4 = tensor-core first
     test + list walk, 5 = as 4 with small lists, 6 = ordered points + gathered chain, 7 = ordered points + lists, 8 = as 7 with small lists, 9 = automatic
-    without ordering (see skm_set_prune_split)."""
+    without ordering, 10 = ordered points + optimistic chain pass with exact redo (see skm_set_prune_split)."""
     lib.skm_set_prune_split(int(mode))
 
 

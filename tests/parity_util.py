@@ -10,7 +10,11 @@ that search can legitimately differ on a point in exactly two ways:
   * threshold flip: the better answer sat within fp32 rounding of one of its thresholds, so one side dropped it
     (an ADSampling false prune) and the other kept it.
 Everything else would be a bug.  `classify_disagreements` replays the search of the affected points in float64 and
-returns the points that fit neither case."""
+returns the points that fit neither case.  Points that the quick check (was the better answer itself near one of its
+thresholds?) does not explain get the full treatment: `reachable_answers` replays the whole search and follows BOTH
+outcomes of every test that is within rounding of its threshold (an earlier candidate that one side kept and the other
+dropped changes `best`, and with it every later threshold); the disagreement is explained when both answers can be
+reached that way."""
 from __future__ import annotations
 
 import numpy as np
@@ -29,6 +33,69 @@ def _checkpoints(d, partial_d, vertical_d):
     if partial_d < vertical_d:
         segs.append((np.arange(partial_d, vertical_d), d))
     return segs
+
+
+def reachable_answers(xi, y64, prev_i, segs, r, thr_tol, tie_abs, max_states=64):
+    """Final answers (centroid indices) that the chunk-by-chunk search can end with when every test whose partial
+    distance is within thr_tol * (|x|^2 + |c|^2 over the dimensions seen) of its threshold, and every final comparison
+    within tie_abs of `best`, may fall either way.  Follows the reference's order: `best` is fixed inside a chunk of
+    1024 centroids and lowered at its end (pdxearch.h:290-324); the previous centroid as the only survivor of the first
+    test leaves it untouched (:140-143)."""
+    k = y64.shape[0]
+    best0 = float(((xi - y64[prev_i]) ** 2).sum())
+    states = {(best0, int(prev_i))}
+    for lo in range(0, k, CHUNK):
+        hi = min(lo + CHUNK, k)
+        yc = y64[lo:hi]
+        diff2 = (xi[None, :] - yc) ** 2
+        x2, y2 = xi ** 2, yc ** 2
+        pds, scales = [], []
+        pd = np.zeros(hi - lo)
+        sc = np.zeros(hi - lo)
+        for dims, seen in segs:
+            pd = pd + diff2[:, dims].sum(1)
+            sc = sc + x2[dims].sum() + y2[:, dims].sum(1)
+            pds.append(pd)
+            scales.append(sc)
+        nxt = set()
+        for best, bidx in states:
+            sure = np.ones(hi - lo, dtype=bool)      # passes every test beyond doubt
+            maybe = np.ones(hi - lo, dtype=bool)     # passes every test when the doubtful ones fall its way
+            for s, (dims, seen) in enumerate(segs):
+                thr = best * r[seen]
+                slack = thr_tol * scales[s]
+                sure &= pds[s] < thr - slack
+                maybe &= pds[s] < thr + slack
+                if s == 0:
+                    first_sure, first_maybe = sure.copy(), maybe.copy()
+            final = pds[-1]
+            win_sure = sure & (final < best - tie_abs)
+            win_maybe = maybe & (final < best + tie_abs)
+            # the rule for "the previous centroid is the only survivor of the first test": may apply when the counts allow it
+            p_in = lo <= prev_i < hi
+            only_prev_possible = p_in and first_maybe[prev_i - lo] and int(first_sure.sum() - (1 if first_sure[prev_i - lo] else 0)) == 0
+            only_prev_certain = p_in and first_sure[prev_i - lo] and int(first_maybe.sum()) == 1
+            outcomes = set()
+            if only_prev_possible or not win_maybe.any():
+                outcomes.add((best, bidx))
+            if not only_prev_certain and win_maybe.any():
+                idx = np.nonzero(win_maybe)[0]
+                floor = final[win_sure].min() if win_sure.any() else np.inf
+                if win_sure.any():
+                    j = idx[np.argmin(np.where(win_sure[idx], final[idx], np.inf))]
+                    outcomes.add((float(final[j]), int(lo + j)))
+                else:
+                    outcomes.add((best, bidx))   # none of the doubtful ones made it
+                for j in idx:
+                    if not win_sure[j] and final[j] <= floor + tie_abs:
+                        outcomes.add((float(final[j]), int(lo + j)))
+                    elif win_sure[j] and final[j] <= floor + tie_abs:
+                        outcomes.add((float(final[j]), int(lo + j)))
+            nxt |= outcomes
+        if len(nxt) > max_states:
+            nxt = set(sorted(nxt)[:max_states])
+        states = nxt
+    return {b for _, b in states}
 
 
 def classify_disagreements(x, y, prev, a, b, partial_d, vertical_d, ratios, tie_rel=1e-5, tie_norm=1e-6, thr_tol=2e-5, margins=None):
@@ -86,6 +153,10 @@ def classify_disagreements(x, y, prev, a, b, partial_d, vertical_d, ratios, tie_
         if margins is not None:
             margins.append(closest)
         if closest <= thr_tol:
+            n_flip += 1
+            continue
+        reach = reachable_answers(xi, y64, int(prev[i]), segs, r, thr_tol, tie_rel * min(da, db) + tie_norm * norms)
+        if int(a[i]) in reach and int(b[i]) in reach:
             n_flip += 1
         else:
             bad.append(int(i))

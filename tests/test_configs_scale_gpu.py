@@ -128,6 +128,7 @@ def test_config4_slice_hierarchical_against_reference(ref):
     for phase in (1, 2, 3):
         assert len(e.stats(phase)) == len(rk.stats(phase))
     # mesoclustering record by record
+    print("mesoclustering (reference objective, engine objective, split):", [(r["objective"], s.objective, r["split"], s.split) for r, s in zip(rk.stats(1), e.stats(1))])
     for r, s in zip(rk.stats(1), e.stats(1)):
         assert r["partial_d"] == s.partial_d and r["is_gemm_only"] == bool(s.is_gemm_only)
         assert abs(r["objective"] - s.objective) <= 1e-4 * r["objective"]
