@@ -390,7 +390,8 @@ def main():
         barrier()
         t0 = time.perf_counter()
         if kind == "assign":
-            res = e.assign(data, cent_dev if on_device else cent_host, n=n_local, on_device=on_device, out=out_dev if on_device else None)
+            # row shards, replicated centroids, no exchange on the data path (the ranks' answers stay on their GPUs / hosts)
+            res = skd.assign_sharded(e, data, cent_dev if on_device else cent_host, n_local, n, on_device=on_device, out=out_dev if on_device else None)
         else:
             res = e.train(data, n=n_local, on_device=on_device)
         torch.cuda.synchronize(device)

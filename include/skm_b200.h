@@ -181,19 +181,22 @@ skm_status skm_reset_phase_times(skm_handle* h);
  * No counterpart in the reference (it delegates to whatever BLAS is linked). */
 void skm_set_tensor_cores(int enabled);
 int skm_get_tensor_cores(void);
-/* Which kernels a pruned assignment pass uses.  0 (default): with rows that TMA can address (d % 4 == 0) the points are
- * taken in the order of their previous centroid and every tile of 128 goes through the tensor-core first test + list
- * walk or, when many of its points keep a large share of the centroids alive, through the tensor-core chain over the
- * centroids its rows can still reach; SIMT candidate lists otherwise.  1 SIMT candidate lists for all points; 2 dense
- * SIMT chain for all; 3 dense tensor-core chain for all; 4 tensor-core first test + list walk for all, original
- * order; 5 as 4 with a quarter of the list capacity, so that overflowing lists take their fallback; 6 ordered points,
+/* Which kernels a pruned assignment pass uses.  0 (default): with rows that TMA can address (d % 4 == 0) the share of
+ * pairs that survive the first test is estimated on 128 sampled centroids; below 1.5 % every point takes the
+ * tensor-core first test + list walk in the original order (points that keep many centroids alive go through the dense
+ * chain instead: the choice of 9), from 1.5 % up (and k <= 65536) the points are taken in the order of their previous
+ * centroid and every tile of 128 goes through the chain over the centroids its rows can still reach (the choice of
+ * 10); SIMT candidate lists when TMA cannot address the rows.  1 SIMT candidate lists for all points; 2 dense SIMT
+ * chain for all; 3 dense tensor-core chain for all; 4 tensor-core first test + list walk for all, original order; 5 as
+ * 4 with a quarter of the list capacity, so that overflowing lists take their fallback; 6 ordered points, exact
  * gathered chain for every tile; 7 ordered points, first test + list walk for every tile; 8 as 7 with the small lists
- * of 5; 9 the automatic choice without ordering (dense chain for all points when the sampled survival is high, else
- * first test + list walk with flagged points on the dense chain); 10 ordered points, every tile through the optimistic
- * chain pass (all thresholds from the distance to the previous centroid, the 1024-centroid chunks ignored) followed by
- * the exact gathered chain for the points whose best candidate moves - what mode 0 does for the tiles it sends to the
- * chain, while mode 6 runs the exact gathered chain alone.  The results do not depend on the choice (up to
- * fp32 rounding); it exists for profiling and for testing each kernel on its own.  No counterpart in the reference. */
+ * of 5; 9 unordered: dense chain for all points when the sampled survival is high, else first test + list walk with
+ * flagged points on the dense chain; 10 ordered points, every tile through the optimistic chain pass (all thresholds
+ * from the distance to the previous centroid, the 1024-centroid chunks ignored) followed by the exact gathered chain
+ * for the points whose best candidate moves; 11 ordered points, per tile either first test + list walk or (tiles with
+ * many expensive points, and tiles whose lists overflow) the chain as in 10.  The results do not depend on the choice
+ * (up to fp32 rounding); it exists for profiling and for testing each kernel on its own.  No counterpart in the
+ * reference. */
 void skm_set_prune_split(int mode);
 int skm_get_prune_split(void);
 /* Test hook for the failure path of the tensor-core kernels (current device).  Every wait inside those kernels is

@@ -439,7 +439,7 @@ size_t sorted_batch_rows(size_t n, size_t d) {
     return std::min(rows, ((n + kTileM - 1) / kTileM) * kTileM);
 }
 
-// The pruned pass over the points in the order of their previous centroid (modes 0, 6, 7, 8).  Points that share a
+// The pruned pass over the points in the order of their previous centroid (modes 6, 7, 8, 10, 11, and 0 when it picks it).  Points that share a
 // previous centroid have nearly the same thresholds and the same neighbourhood of centroids, so a tile of 128 of them
 // either has short candidate lists (first test + list walk) or keeps a common, limited set of centroids alive (chain
 // over the centroids named by the tile's union bits).  The order changes where work is done, not what is computed.
@@ -532,7 +532,7 @@ void run_pruned_pass_sorted(const PrunedParams& p, PrunePassBuffers& b, float ra
     // The chain over the tiles listed in map_dev[0 .. n_t) of the current batch.  With `optimistic` every tile first takes
     // the pass that ignores the chunk structure and assumes that no point's best candidate changes; the points for which
     // that does not hold are gathered (their order kept) and redone exactly.
-    const bool optimistic = (mode == 0 || mode == 10) && p.k <= 65536 && std::getenv("SKM_NO_OPTIMISTIC_CHAIN") == nullptr;
+    const bool optimistic = (mode == 11 || mode == 10) && p.k <= 65536 && std::getenv("SKM_NO_OPTIMISTIC_CHAIN") == nullptr;
     auto run_chain_tiles = [&](const uint32_t* map_dev, size_t n_t, size_t rows_in_batch) {
         if (n_t == 0) return;
         SubPhase sub(timers, PH_PRUNE_DENSE, stream);
@@ -603,7 +603,7 @@ void run_pruned_pass_sorted(const PrunedParams& p, PrunePassBuffers& b, float ra
 
         // ---- which tiles take which route
         size_t n_dense = 0, n_lists = 0;
-        if (mode == 0) {
+        if (mode == 11) {
             PrunedParams pb = p;
             pb.x = xb;
             pb.n = cnt;
@@ -702,6 +702,13 @@ void run_pruned_pass_sorted(const PrunedParams& p, PrunePassBuffers& b, float ra
 
 } // namespace
 
+// Share of (point, sampled centroid) pairs passing the first test from which the automatic choice takes the ordered chain
+// (a tuning aid: SKM_AUTO_CHAIN_SURVIVAL overrides it).
+static double auto_chain_survival() {
+    if (const char* v = std::getenv("SKM_AUTO_CHAIN_SURVIVAL")) return std::atof(v);
+    return 0.015;
+}
+
 void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, int device, cudaStream_t stream, PhaseTimers* timers) {
     struct Sub {
         PhaseTimers* t;
@@ -715,11 +722,12 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
     };
     if (p.n == 0) return;
     int mode = g_prune_split_mode;
-    if ((mode == 0 || (mode >= 6 && mode <= 8) || mode == 10) && tc::eligible(p.x, p.d, p.y, p.d)) {
+    const bool auto_mode = mode == 0;
+    if (((mode >= 6 && mode <= 8) || mode == 10 || mode == 11) && tc::eligible(p.x, p.d, p.y, p.d)) {
         run_pruned_pass_sorted(p, b, ratio_first, device, stream, timers, mode);
         return;
     }
-    if ((mode >= 6 && mode <= 8) || mode == 10) throw std::invalid_argument("the ordered pruned pass needs 16-byte aligned rows (d % 4 == 0) and the tensor-core kernels switched on");
+    if ((mode >= 6 && mode <= 8) || mode == 10 || mode == 11) throw std::invalid_argument("the ordered pruned pass needs 16-byte aligned rows (d % 4 == 0) and the tensor-core kernels switched on");
     if (mode == 9) mode = 0;
     if (b.grid == 0) b.grid = pruned_grid_size(device);
     const uint32_t n_ck = prune_chain_checkpoints(p.partial_d, p.vertical_d, p.horizontal_d);
@@ -752,6 +760,15 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
         // Candidate lists cost one gathered block per surviving pair and step; the tensor-core chain costs a
         // full product whatever survives.  Past roughly 0.8 % of surviving pairs the chain is cheaper.
         const double survival = static_cast<double>(host[0]) / (static_cast<double>(p.n) * n_sample);
+        b.last_survival = survival;
+        // Which family of routes: candidate lists cost one gathered 64-dimension block per surviving pair and step, so
+        // they win while few pairs survive the first test; past ~1.5 % of surviving pairs the points go, in the order
+        // of their previous centroid, through the chain over each tile's reachable centroids (whose cost follows the
+        // union of the tile's survivors, not their number).
+        if (auto_mode && tc_ok && p.k <= 65536 && survival >= auto_chain_survival()) {
+            run_pruned_pass_sorted(p, b, ratio_first, device, stream, timers, 10);
+            return;
+        }
         // The chain costs a full product whatever survives; lists cost a partial product plus one gathered
         // block per surviving pair and step, and their capacity is an eighth of all pairs.
         use_chain = tc_ok && (survival > 0.08 || n_hard * 2 > p.n);
@@ -1302,6 +1319,9 @@ void Engine::train_hierarchical(const float* data, size_t n, bool on_device, flo
     final_centroids_.ensure(k_ * d_);
     x_rot_.ensure(n_all * d_);
     SKM_CUDA(cudaMemsetAsync(assignments_.get(), 0, sizeof(uint32_t) * n, stream_));
+    // Points that no mesocluster's index range covers (possible only when the last mesoclustering iteration split clusters,
+    // see the partition below) keep cluster 0, as with the reference's freshly mapped array (hierarchical_superkmeans.h:121).
+    SKM_CUDA(cudaMemsetAsync(final_assignments_.get(), 0, sizeof(uint32_t) * n_all, stream_));
     prepare_update_workspace(n_all, k_);
 
     // ---- phase 1: mesoclustering (:161-257)

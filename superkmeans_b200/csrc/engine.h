@@ -129,6 +129,7 @@ struct PrunePassBuffers {
     DeviceBuffer<float> listed_x, listed_best, listed_dist, listed_norms, y_split;
     DeviceBuffer<unsigned long long> alive_total;
     PinnedBuffer<unsigned long long> counters_host;
+    double last_survival = 0;   // share of sampled (point, centroid) pairs that passed the first test in the last automatic choice
     int last_path = 0;   // 1 lists (+ dense for flagged points), 3 tensor-core chain, 4 tensor-core first test + list walk
     int grid = 0;
     size_t last_n_hard = 0;

@@ -72,3 +72,47 @@ def train_sharded(engine, local_rows, n_local: int, n_global: int, row_offset: i
     else:
         engine.set_shard(n_global, row_offset, make_allreduce(device, group))
     return engine.train(local_rows, n=n_local, on_device=on_device)
+
+
+def gather_rows(local, n_global: int, group=None, dst=None):
+    """Concatenates the ranks' contiguous shards (split as `shard_bounds`) of a per-row result in rank order.  `local` is
+    a 1-d numpy array or torch tensor (host or device); the result has `n_global` entries and lives where `local` does.
+    With `dst` only that rank receives it (the others get None).  Shards differ by at most one row, so every rank sends
+    `ceil(n_global / world)` entries and the padding is cut on arrival."""
+    import torch
+    import torch.distributed as dist
+
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    lo, hi = shard_bounds(n_global, rank, world)
+    as_numpy = isinstance(local, np.ndarray)
+    np_dtype = local.dtype if as_numpy else None
+    if as_numpy and np_dtype == np.uint32:   # carried as int32: the collectives have no unsigned 32-bit type
+        local = local.view(np.int32)
+    t = torch.from_numpy(np.ascontiguousarray(local)) if as_numpy else local.contiguous()
+    if t.dim() != 1 or t.shape[0] != hi - lo:
+        raise ValueError(f"rank {rank} holds rows [{lo}, {hi}) but passed {tuple(t.shape)} entries")
+    width = -(-n_global // world)
+    send = torch.zeros(width, dtype=t.dtype, device=t.device)
+    send[: hi - lo] = t
+    if dst is None:
+        parts = [torch.empty_like(send) for _ in range(world)]
+        dist.all_gather(parts, send, group=group)
+    else:
+        parts = [torch.empty_like(send) for _ in range(world)] if rank == dst else None
+        dist.gather(send, parts, dst=dist.get_global_rank(group, dst) if group is not None else dst, group=group)
+        if rank != dst:
+            return None
+    sizes = [shard_bounds(n_global, r, world) for r in range(world)]
+    out = torch.cat([p[: b - a] for p, (a, b) in zip(parts, sizes)])
+    return out.numpy().view(np_dtype) if as_numpy else out
+
+
+def assign_sharded(engine, local_rows, centroids, n_local: int, n_global: int, on_device: bool = True, out=None, gather: bool = False, dst=None,
+                   group=None):
+    """Assign over row shards: every rank assigns its own rows to the (replicated) centroids - no exchange on the data
+    path, the ranks run independently.  Returns this rank's assignments, or with `gather` the assignments of all
+    `n_global` rows in row order (on every rank, or on `dst` only)."""
+    res = engine.assign(local_rows, centroids, n=n_local, on_device=on_device, out=out)
+    if not gather:
+        return res
+    return gather_rows(res, n_global, group=group, dst=dst)

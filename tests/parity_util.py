@@ -161,3 +161,40 @@ def classify_disagreements(x, y, prev, a, b, partial_d, vertical_d, ratios, tie_
         else:
             bad.append(int(i))
     return n_tie, n_flip, bad
+
+
+def coincident_centroids(y, rel=1e-11):
+    """Representative (smallest index) of every group of centroids that coincide: squared distance <= rel * squared norm.
+
+    Such groups are left by SplitClusters (superkmeans.h:890-928) when one cluster is the source of several splits in one
+    call: the source is scaled by (1 - e s) each time and the copy by (1 + e s) (e = 1/1024, s = +-1 alternating over the
+    dimensions), so a copy that is itself split later returns to (1 + e s)(1 - e s) = 1 - e^2 times the original, the same
+    vector as the copy made right after the source's first scaling, up to the rounding of the products.  A point near such
+    a pair sees two distances that differ by ~1e-8 relative: which one an fp32 search reports is rounding, in the
+    reference as much as here, so parity is counted up to these groups."""
+    y64 = np.asarray(y, dtype=np.float64)
+    k = y64.shape[0]
+    nn = (y64 ** 2).sum(1)
+    proj = y64 @ np.random.default_rng(0).standard_normal(y64.shape[1])
+    order = np.argsort(proj, kind="stable")
+    parent = np.arange(k)
+
+    def find(i):
+        while parent[i] != i:
+            parent[i] = parent[parent[i]]
+            i = parent[i]
+        return i
+
+    sp = proj[order]
+    scale = np.sqrt(nn[order]) + 1e-30
+    for a in range(k - 1):
+        b = a + 1
+        # |projection difference| <= |r| * |difference|: a generous window, the exact check decides
+        while b < k and sp[b] - sp[a] <= 1e-3 * scale[a]:
+            i, j = order[a], order[b]
+            if ((y64[i] - y64[j]) ** 2).sum() <= rel * max(nn[i], nn[j]):
+                ri, rj = find(i), find(j)
+                if ri != rj:
+                    parent[max(ri, rj)] = min(ri, rj)
+            b += 1
+    return np.array([find(i) for i in range(k)])

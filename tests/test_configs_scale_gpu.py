@@ -7,8 +7,9 @@
 
 Each flat configuration is checked twice:
   step-wise  - pruned iterations replayed from the reference's own state (its rotated points, centroids, previous
-               assignment and d'): >= 99.9 % identical assignments, every sampled disagreement explained as a near-tie
-               or a threshold flip, not-pruned totals and the next d' as the reference's;
+               assignment and d'): >= 99.9 % identical assignments (centroids that coincide to rounding, which repeated
+               splits of one cluster leave behind, counted as one cluster), every sampled disagreement explained as a
+               near-tie or a threshold flip, not-pruned totals and the next d' as the reference's;
   end to end - same d' schedule, centroids of clusters with identical members within 1e-5, WCSS within 2e-3 and a
                floor on the share of identical assignments (both reported; single near-tie flips are amplified by
                the cluster splits at these sizes, see the comment at the gates).
@@ -61,8 +62,12 @@ def _flat_against_reference(ref, x, k, seed, iters, replay, end_to_end_agree, cl
         pd = st["partial_d"]
         rknn, rdist, rnp = ref.find_nearest_pruned(xr, prev.centroids, prev.assign, pd)
         knn, dist, npc = eng.find_nearest_pruned(xr, prev.centroids, prev.assign, pd)
-        agree = float((knn == rknn).mean())
-        assert agree >= 0.999, (t, agree)
+        # centroids that coincide up to rounding (several splits of one cluster in one call) count as one cluster
+        rep = parity_util.coincident_centroids(prev.centroids)
+        raw = float((knn == rknn).mean())
+        agree = float((rep[knn] == rep[rknn]).mean())
+        print(f"iteration {t + 1}: assignments equal {raw:.5f}, up to {int((rep != np.arange(k)).sum())} coincident centroids {agree:.5f}")
+        assert agree >= 0.999, (t, agree, raw)
         bad = np.nonzero(knn != rknn)[0]
         if len(bad) > classify_cap:
             bad = rng.choice(bad, classify_cap, replace=False)

@@ -120,9 +120,9 @@ def _trace(ref, n, d, k, iters, seed, hier=False, centers=None, **kw):
     return _TRACES[key]
 
 
-@pytest.mark.parametrize("split_mode", [0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10],
+@pytest.mark.parametrize("split_mode", [0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11],
                          ids=["auto", "lists_only", "dense_simt_only", "tensor_core_chain", "tensor_core_lists", "tensor_core_lists_overflowing", "ordered_gathered_chain",
-                              "ordered_lists", "ordered_lists_overflowing", "auto_unordered", "ordered_optimistic_chain"])
+                              "ordered_lists", "ordered_lists_overflowing", "unordered_lists_and_chain", "ordered_optimistic_chain", "ordered_route_per_tile"])
 @pytest.mark.parametrize("n,d,k", [(20000, 256, 512), (12000, 768, 1500), (6000, 130, 1030), (9000, 1024, 2100)])
 def test_pruned_step_matches_reference_teacher_forced(eng, ref, n, d, k, split_mode):
     """Every pruned iteration of a reference run, replayed from the reference's own inputs, with the
@@ -133,7 +133,7 @@ def test_pruned_step_matches_reference_teacher_forced(eng, ref, n, d, k, split_m
     try:
         # the tensor-memory accumulator truncates: partial distances sit ~1e-5 (relative to the dot product)
         # high, which moves a few more pairs across the thresholds than fp32 rounding does
-        _pruned_step_check(eng, ref, n, d, k, count_tol=5e-3 if split_mode in (0, 3, 4, 5, 6, 7, 8, 9, 10) else 1e-3)
+        _pruned_step_check(eng, ref, n, d, k, count_tol=5e-3 if split_mode in (0, 3, 4, 5, 6, 7, 8, 9, 10, 11) else 1e-3)
     finally:
         eng.set_prune_split(0)
 

@@ -68,6 +68,34 @@ def test_sharded_protocol_matches_single_process(tmp_path, world):
     assert np.linalg.norm(ranks[0]["cent"] - cent1) <= 1e-4 * np.linalg.norm(cent1)
 
 
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_assign_gathers_rows_in_order(tmp_path, world):
+    """Assign over row shards (n not a multiple of the world size): the gathered result, on every rank or on one, is the
+    single-process assignment."""
+    from oracle import restate
+    from tests import datagen
+
+    n, d, k, seed = 5003, 64, 97, 21
+    x = datagen.gaussian_mixture(n, d, k, 0.3, seed)
+    c = x[np.random.default_rng(seed).choice(n, k, replace=False)].copy()
+    base = str(tmp_path / "assign")
+    np.save(base + ".centroids.npy", c)
+    want, _ = restate.find_nearest(x, c)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           os.path.join(ROOT, "tests", "_gloo_assign_worker.py"), base, str(n), str(d), str(k), str(seed)]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, OMP_NUM_THREADS="2"), cwd=ROOT)
+    assert res.returncode == 0, res.stderr[-2000:]
+    ranks = [np.load(f"{base}.rank{r}.npz") for r in range(world)]
+    for r, z in enumerate(ranks):
+        lo, hi = skd.shard_bounds(n, r, world)
+        assert (int(z["lo"]), int(z["hi"])) == (lo, hi)
+        np.testing.assert_array_equal(z["mine"], want[lo:hi])
+        assert z["everywhere"].dtype == np.uint32
+        np.testing.assert_array_equal(z["everywhere"], want)
+        assert len(z["on_last"]) == (n if r == world - 1 else 0)
+    np.testing.assert_array_equal(ranks[-1]["on_last"], want)
+
+
 def test_allreduce_callback_through_the_c_callback_type():
     """The closure the engine calls (ptr, count, dtype) sums a host buffer in place; single rank."""
     import ctypes as C
