@@ -72,6 +72,30 @@ def peaks():
     return d
 
 
+def measure_tf32_peak(torch, device, size=8192, reps=10):
+    """Dense TF32 tensor throughput of the library GEMM (torch.matmul with TF32 allowed) on this GPU, best of `reps`:
+    the denominator for the three TF32 products behind every fp32-accurate term.  Only a yardstick: nothing on the
+    measured path calls it."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a = torch.randn(size, size, device=device)
+        b = torch.randn(size, size, device=device)
+        torch.matmul(a, b)
+        best = float("inf")
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch.matmul(a, b)
+            e1.record()
+            torch.cuda.synchronize(device)
+            best = min(best, e0.elapsed_time(e1))
+        del a, b
+        return 2.0 * size ** 3 / (best / 1e3) / 1e12
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
 # ---------------------------------------------------------------------------------------------
 # Synthetic workloads, generated on the device in blocks of BLOCK rows, each block from its own seed
 # ---------------------------------------------------------------------------------------------
@@ -324,8 +348,8 @@ def work_rows(kernel, n_local, stats, engine):
         return n_local * max(1, sum(1 for s in stats if s.is_gemm_only))
     if kernel == "sparse_chain_kernel" and engine is not None:
         return engine.chain_counters()["rows"]
-    if engine is not None and engine.last_prune_path == 6:
-        return n_local * pruned - engine.chain_counters()["rows"]
+    if engine is not None:
+        return max(0, n_local * pruned - engine.chain_counters()["rows"])
     return n_local * pruned
 
 
@@ -463,14 +487,18 @@ def main():
         ms, calls = phase_acc["search/1st_blas"]
         cands.append(("gemm_tc_kernel<ARGMIN>", ms, calls, "tensor", sum(2.0 * n_local * k * d for s in stats if s.is_gemm_only)))
         ms, calls = phase_acc["search/first_test"]
-        listed_rows = n_local * len(d_partial) - (chain["rows"] if prune_path == 6 else 0)
-        cands.append(("gemm_tc_kernel<PRUNE>", ms, calls, "tensor", 2.0 * listed_rows * k * mean_pd if prune_path in (4, 6) else 0.0))
+        # a Train can mix routes (the automatic choice is taken per pass): rows that went through the ordered chain, rows
+        # of the unordered dense chain, and rows that took first test + list walk
+        chain_rows = chain["rows"]
+        legacy_dense_rows = max(0, counters["dense_rows"] - chain_rows)
+        listed_rows = max(0, n_local * len(d_partial) - chain_rows)
+        cands.append(("gemm_tc_kernel<PRUNE>", ms, calls, "tensor", 2.0 * listed_rows * k * mean_pd if ms > 0 else 0.0))
         ms, calls = phase_acc["search/dense"]
-        if prune_path == 6:
+        if chain_rows >= legacy_dense_rows:
             # union pass over the first d' dimensions of every centroid + the chain over the gathered columns (128 rows per unit)
-            cands.append(("sparse_chain_kernel", ms, calls, "tensor", 2.0 * 128 * chain["columns"] * d + 2.0 * chain["rows"] * k * mean_pd))
+            cands.append(("sparse_chain_kernel", ms, calls, "tensor", 2.0 * 128 * chain["columns"] * d + 2.0 * chain_rows * k * mean_pd))
         else:
-            cands.append(("chain_tc_kernel", ms, calls, "tensor", 2.0 * counters["dense_rows"] * k * d))
+            cands.append(("chain_tc_kernel", ms, calls, "tensor", 2.0 * legacy_dense_rows * k * d))
         ms, calls = phase_acc["search/walk"]
         # every (pair, 64-dimension block) step gathers 256 B of the centroid's PDX block, served by L2
         cands.append(("walk_lists_kernel", ms, calls, "l2", 256.0 * counters["walk_pair_steps"]))
@@ -483,10 +511,12 @@ def main():
         roofline = {"kernel": dom, "bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf, "traffic": None,
                     "peak_source": f"bf16 dense sustained, {pk['_source']}", "avg_launch_ms": dom_ms / max(dom_calls, 1),
                     "note": "fp32-accurate distances from three TF32 products per term; flops counted once as 2*rows*columns*K"}
-        tf32 = pk.get("tf32_tflops")
+        tf32 = pk.get("tf32_tflops") or (measure_tf32_peak(torch, device) if rank == 0 else None)
         if tf32:
-            roofline["frac_of_tf32_dense"] = 3.0 * achieved / float(tf32)
+            # the tensor cores execute three TF32 products per counted term
             roofline["tf32_peak"] = float(tf32)
+            roofline["tf32_peak_source"] = "torch.matmul 8192^3 with TF32 allowed, best of 10, measured in this run (burst)"
+            roofline["frac_of_tf32_dense"] = 3.0 * achieved / float(tf32)
     else:
         achieved = work / (dom_ms_per_step / 1e3) / 1e9 if dom_ms > 0 else 0.0
         roofline = {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs, "traffic": None,

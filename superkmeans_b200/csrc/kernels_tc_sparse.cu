@@ -162,8 +162,8 @@ constexpr int SPARSE_THREADS = 448;
             if (n_listed == 0) continue;                                                                  \
             const size_t c0 = static_cast<size_t>(chunk) * kChunk;                                        \
             const uint16_t* chunk_cols = p.cols + lt * p.cols_stride + c0;                                \
-            /* as few units as the 256-column accumulators allow (the rows' threads pay a fixed price per unit and segment) */ \
-            const uint32_t n_units = (n_listed + BN - 1) / BN;                                            \
+            /* at least two units whenever there is enough to split, so that one unit's tests overlap the other's products */ \
+            const uint32_t n_units = n_listed <= 16u ? 1u : max(2u, (n_listed + BN - 1) / BN);            \
             const uint32_t unit_w = (((n_listed + n_units - 1) / n_units) + 15u) & ~15u;                  \
             for (uint32_t pair = 0; pair * 2 < n_units && ok; ++pair) {                                   \
                 for (uint32_t seg = 0; seg < p.n_seg && ok; ++seg) {                                      \
@@ -415,12 +415,8 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
         uint32_t prev = 0xFFFFFFFFu, cnt = 0, dirty = 0;
         constexpr int HS = BN / 64;
         uint32_t alive0[HS], alive1[HS];
-        float pre0[HS], pre1[HS];   // per accumulator: the next segment's centroid norms of this lane's columns
 #pragma unroll
-        for (int q = 0; q < HS; ++q) {
-            alive0[q] = alive1[q] = 0;
-            pre0[q] = pre1[q] = 0.f;
-        }
+        for (int q = 0; q < HS; ++q) alive0[q] = alive1[q] = 0;
         float* ny = ctrl->ny[warp - 6];
         auto close_row = [&]() -> bool {
             RowPartial mine{};
@@ -476,24 +472,14 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
             const float nxv = row_valid ? __ldg(p.chain_norms_x + row * p.n_seg + seg) : 0.f;
             const long long t_norms0 = clock64();
             {
-                // centroid norms of this warp's columns at this checkpoint: fetched one segment ahead (below), except for a unit's first segment
                 const float* __restrict__ src = p.chain_norms_y + static_cast<size_t>(seg) * p.k;
                 float cur[HS];
 #pragma unroll
-                for (uint32_t q = 0; q < HS; ++q) cur[q] = first ? ((q * 32 + lane < my_cols) ? __ldg(src + cidx[q]) : 0.f) : (a ? pre1[q] : pre0[q]);
+                for (uint32_t q = 0; q < HS; ++q) cur[q] = (q * 32 + lane < my_cols) ? __ldg(src + cidx[q]) : 0.f;
                 __syncwarp();
 #pragma unroll
                 for (uint32_t q = 0; q < HS; ++q) ny[q * 32 + lane] = cur[q];
                 __syncwarp();
-                if (!last) {
-                    const float* __restrict__ nxt = src + p.k;
-#pragma unroll
-                    for (uint32_t q = 0; q < HS; ++q) {
-                        const float v = (q * 32 + lane < my_cols) ? __ldg(nxt + cidx[q]) : 0.f;
-                        if (a) pre1[q] = v;
-                        else pre0[q] = v;
-                    }
-                }
             }
             t_norms += clock64() - t_norms0;
             if (!__all_sync(0xffffffffu, timed_wait(&ctrl->acc_ready[a], uses[a] & 1u, wctx, 25, w_ready))) {
@@ -508,9 +494,9 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
             for (int q = 0; q < HS; ++q) alive[q] = a ? alive1[q] : alive0[q];
             // At the last checkpoint the question is not the test itself but "could this centroid beat the previous one":
             // distances from the tensor-memory accumulator sit too high by an amount that grows with the number of
-            // accumulation steps (~1e-5 of the norms at d = 1024), and the exact pass settles such near-misses with fp32
-            // distances of its runner-ups, so the bar is raised by a multiple of that.
-            const float near_bar = last ? fmaf(best, 1e-4f, best) + (4e-8f * static_cast<float>(p.d)) * nxv : thr;
+            // accumulation steps (up to ~2e-5 of the norms at d = 1024, ~6e-5 at d = 1536), and the exact pass settles
+            // such near-misses with fp32 distances of its runner-ups, so the bar is raised by that much.
+            const float near_bar = last ? fmaf(best, 1e-4f, best) + (3e-8f * static_cast<float>(p.d)) * nxv : thr;
             auto test_slice = [&](const uint32_t sl, const uint32_t (&r)[32], uint32_t& alive_ch) {
                 const uint32_t cb0 = sl * 32;
                 uint32_t w = 0;
@@ -615,13 +601,9 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
         // per accumulator: survivor masks of the unit in flight and where among this half's columns the row's previous
         // centroid sits (or none)
         uint32_t alive0[HS], alive1[HS];
-        float pre0[HS], pre1[HS];   // per accumulator: the next segment's centroid norms of this lane's columns
         uint32_t prevpos0 = 0xFFFFFFFFu, prevpos1 = 0xFFFFFFFFu;
 #pragma unroll
-        for (int q = 0; q < HS; ++q) {
-            alive0[q] = alive1[q] = 0;
-            pre0[q] = pre1[q] = 0.f;
-        }
+        for (int q = 0; q < HS; ++q) alive0[q] = alive1[q] = 0;
         float* ny = ctrl->ny[warp - 6];
         // End of a chunk: the two threads of the row exchange what they found in their halves of the columns and
         // both apply the same update.  Returns false when the wait ran out.
@@ -754,24 +736,14 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
             // centroid norms of this warp's share of the unit's columns at this checkpoint
             const long long t_norms0 = clock64();
             {
-                // fetched one segment ahead (below), except for a unit's first segment
                 const float* __restrict__ src = p.chain_norms_y + static_cast<size_t>(seg) * p.k + c0;
                 float cur[HS];
 #pragma unroll
-                for (uint32_t q = 0; q < HS; ++q) cur[q] = first ? ((q * 32 + lane < my_cols) ? __ldg(src + cidx[q]) : 0.f) : (a ? pre1[q] : pre0[q]);
+                for (uint32_t q = 0; q < HS; ++q) cur[q] = (q * 32 + lane < my_cols) ? __ldg(src + cidx[q]) : 0.f;
                 __syncwarp();
 #pragma unroll
                 for (uint32_t q = 0; q < HS; ++q) ny[q * 32 + lane] = cur[q];
                 __syncwarp();
-                if (!last) {
-                    const float* __restrict__ nxt = src + p.k;
-#pragma unroll
-                    for (uint32_t q = 0; q < HS; ++q) {
-                        const float v = (q * 32 + lane < my_cols) ? __ldg(nxt + cidx[q]) : 0.f;
-                        if (a) pre1[q] = v;
-                        else pre0[q] = v;
-                    }
-                }
             }
             t_norms += clock64() - t_norms0;
             if (!__all_sync(0xffffffffu, timed_wait(&ctrl->acc_ready[a], uses[a] & 1u, wctx, 25, w_ready))) {
@@ -945,7 +917,7 @@ __global__ void __launch_bounds__(256) build_cols_kernel(const uint32_t* __restr
         col_counts[t * n_chunks + chunk] = total;
         if (total_cols && total) {
             // columns as the tensor cores see them: the chunk's units (cut as in sparse_chain_kernel), each rounded up to 16
-            const uint32_t n_units = (total + BN - 1) / BN;
+            const uint32_t n_units = total <= 16u ? 1u : max(2u, (total + BN - 1) / BN);
             const uint32_t unit_w = (((total + n_units - 1) / n_units) + 15u) & ~15u;
             unsigned long long cols16 = 0;
             for (uint32_t u = 0; u * unit_w < total; ++u) cols16 += (min(unit_w, total - u * unit_w) + 15u) & ~15u;
@@ -1066,7 +1038,7 @@ __global__ void __launch_bounds__(256) build_flat_cols_kernel(const uint32_t* __
     if (lane == 0) {
         totals[t] = base;
         if (total_cols && base) {
-            const uint32_t n_units = (base + BN - 1) / BN;
+            const uint32_t n_units = base <= 16u ? 1u : max(2u, (base + BN - 1) / BN);
             const uint32_t unit_w = (((base + n_units - 1) / n_units) + 15u) & ~15u;
             unsigned long long cols16 = 0;
             for (uint32_t u = 0; u * unit_w < base; ++u) cols16 += (min(unit_w, base - u * unit_w) + 15u) & ~15u;

@@ -7,9 +7,10 @@
 
 Each flat configuration is checked twice:
   step-wise  - pruned iterations replayed from the reference's own state (its rotated points, centroids, previous
-               assignment and d'): >= 99.9 % identical assignments (centroids that coincide to rounding, which repeated
-               splits of one cluster leave behind, counted as one cluster), every sampled disagreement explained as a
-               near-tie or a threshold flip, not-pruned totals and the next d' as the reference's;
+               assignment and d'): >= 99.9 % identical assignments (answers that tie within the rounding of the reference's
+               own fp32 distances counted as equal; nearly all of them lie between centroids that coincide to rounding,
+               which repeated splits of one cluster leave behind), every sampled disagreement explained as a near-tie
+               or a threshold flip, not-pruned totals and the next d' as the reference's;
   end to end - same d' schedule, centroids of clusters with identical members within 1e-5, WCSS within 2e-3 and a
                floor on the share of identical assignments (both reported; single near-tie flips are amplified by
                the cluster splits at these sizes, see the comment at the gates).
@@ -31,13 +32,20 @@ def _wcss64(x, c, a, block=200_000):
 
 
 def _identical_cluster_centroids(c, rc, a, ra, k):
+    """Share of clusters with the same (non-empty) member set in both runs, and the largest relative centroid difference
+    among them, leaving out clusters that differ by no more than the 1/1024 scaling of a split (the last consolidation
+    may draw other clusters to split once the runs differ anywhere); their number is returned as well."""
     same = np.ones(k, dtype=bool)
     diff = a != ra
     same[a[diff]] = False
     same[ra[diff]] = False
+    same &= np.bincount(a, minlength=k) > 0
     num = np.linalg.norm(c[same].astype(np.float64) - rc[same].astype(np.float64), axis=1)
     den = np.linalg.norm(rc[same].astype(np.float64), axis=1) + 1e-30
-    return float(same.mean()), float((num / den).max()) if same.any() else 0.0
+    rel = num / den
+    split_like = (rel >= 1e-5) & (rel < 2.5e-3)
+    rest = rel[~split_like]
+    return float(same.mean()), float(rest.max()) if rest.size else 0.0, int(split_like.sum())
 
 
 def _flat_against_reference(ref, x, k, seed, iters, replay, end_to_end_agree, classify_cap=150):
@@ -62,12 +70,23 @@ def _flat_against_reference(ref, x, k, seed, iters, replay, end_to_end_agree, cl
         pd = st["partial_d"]
         rknn, rdist, rnp = ref.find_nearest_pruned(xr, prev.centroids, prev.assign, pd)
         knn, dist, npc = eng.find_nearest_pruned(xr, prev.centroids, prev.assign, pd)
-        # centroids that coincide up to rounding (several splits of one cluster in one call) count as one cluster
+        # Answers that tie within the rounding of the reference's own distances count as equal: the reference forms
+        # ||x||^2 + ||c||^2 - 2 x.c in fp32 (batch_computers.h:152-163), which is only good to ~1e-7 of the norms (its
+        # reported distances differ from float64 ones by up to 1e-7 on unit rows).  Nearly all such ties are between
+        # centroids that coincide to rounding, which several splits of one cluster in one call leave behind
+        # (parity_util.coincident_centroids); their count is reported.
         rep = parity_util.coincident_centroids(prev.centroids)
         raw = float((knn == rknn).mean())
-        agree = float((rep[knn] == rep[rknn]).mean())
-        print(f"iteration {t + 1}: assignments equal {raw:.5f}, up to {int((rep != np.arange(k)).sum())} coincident centroids {agree:.5f}")
+        differ = np.nonzero(knn != rknn)[0]
+        xs = xr[differ].astype(np.float64)
+        ca, cb = prev.centroids[knn[differ]].astype(np.float64), prev.centroids[rknn[differ]].astype(np.float64)
+        gap = np.abs(((xs - ca) ** 2).sum(1) - ((xs - cb) ** 2).sum(1))
+        tied = gap <= 1e-7 * ((xs ** 2).sum(1) + np.maximum((ca ** 2).sum(1), (cb ** 2).sum(1)))
+        agree = 1.0 - float((~tied).sum()) / n
+        print(f"iteration {t + 1}: assignments equal {raw:.5f}; {int(tied.sum())} of {len(differ)} differences are ties at the reference's own rounding "
+              f"({int((rep[knn[differ]] == rep[rknn[differ]]).sum())} between coincident centroids, {int((rep != np.arange(k)).sum())} such centroids); equal up to ties {agree:.5f}")
         assert agree >= 0.999, (t, agree, raw)
+        del xs, ca, cb
         bad = np.nonzero(knn != rknn)[0]
         if len(bad) > classify_cap:
             bad = rng.choice(bad, classify_cap, replace=False)
@@ -93,11 +112,12 @@ def _flat_against_reference(ref, x, k, seed, iters, replay, end_to_end_agree, cl
     ra, a = rk.assignments(), e.assignments()
     w, rw = _wcss64(x, c, a), _wcss64(x, rc, ra)
     agree = float((ra == a).mean())
-    share, rel = _identical_cluster_centroids(e.rotated_centroids(), rk.rotated_centroids(), a, ra, k)
+    share, rel, n_split_like = _identical_cluster_centroids(e.rotated_centroids(), rk.rotated_centroids(), a, ra, k)
     splits = [(r["split"], s.split) for r, s in zip(stats, es)]
-    print(f"end to end: assignments equal {agree:.5f}, clusters with identical members {share:.4f}, their centroids within {rel:.2e}, "
+    print(f"end to end: assignments equal {agree:.5f}, clusters with identical members {share:.4f}, their centroids within {rel:.2e} ({n_split_like} apart by a split's scaling), "
           f"wcss rel diff {abs(w - rw) / rw:.2e}, splits (reference, engine) per iteration {splits}")
     assert rel < 1e-5, rel
+    assert n_split_like <= 2 * max(1, int(stats[-1]["split"]) + int(es[-1].split)), n_split_like
     # At this size hundreds of clusters are empty after the first iterations (as many centres as clusters, Forgy start):
     # SplitClusters re-seeds them from clusters chosen by size, so one point that falls the other way at a near-tie
     # changes which clusters are split an iteration later, and the runs separate (the reference's own pruned and
@@ -142,7 +162,16 @@ def test_config4_slice_hierarchical_against_reference(ref):
         assert r["split"] == s.split
         assert abs(r["objective"] - s.objective) <= 2e-3 * r["objective"]
     ra, a = rk.final_assignments(), e.assignments()
-    w, rw = _wcss64(x, c, a), _wcss64(x, rc, ra)
+    # When the last mesoclustering iteration split clusters, the sizes that lay out the mesoclusters' index ranges no longer
+    # match the members (hierarchical_superkmeans.h:260-286), some points fall in no range, and the reference leaves their
+    # entries of its freshly allocated array unwritten (:121): whatever the heap held.  The engine reports cluster 0 there.
+    covered = ra < k
+    print(f"hierarchical slice: {int((~covered).sum())} points outside every mesocluster's range (reference entries unwritten)")
+    assert (~covered).sum() <= n // 100
+    assert a.max() < k
+    xc, ra, a = x[covered], ra[covered], a[covered]
+    w, rw = _wcss64(xc, c, a), _wcss64(xc, rc, ra)
+    del xc
     agree = float((ra == a).mean())
     print(f"hierarchical slice: assignments equal {agree:.5f}, wcss rel diff {abs(w - rw) / rw:.2e}")
     # a mesocluster whose member list differs by one point draws other starting centroids (hierarchical_superkmeans.h:333-342)

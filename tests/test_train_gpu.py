@@ -46,15 +46,22 @@ def _check_stats(rs, es, rel=1e-4, strict=True):
 
 
 def _centroids_of_identical_clusters(c, rc, a, ra, k):
-    """Clusters whose member sets are the same in both runs must have the same centroid (1e-5 relative);
-    returns the fraction of such clusters."""
+    """Clusters whose (non-empty) member sets are the same in both runs must have the same centroid (1e-5 relative);
+    returns the fraction of such clusters.  When the runs differ somewhere, the last consolidation may have drawn other
+    clusters to split (SplitClusters walks the sizes with the seeded generator, superkmeans.h:890-928): a source cluster
+    is then scaled by 1 +- 1/1024 per dimension in one run only, which is the one deviation tolerated here, for as many
+    clusters as could have been touched (two per differing point at the very most)."""
     same = np.ones(k, dtype=bool)
     diff = a != ra
     same[a[diff]] = False
     same[ra[diff]] = False
+    same &= np.bincount(a, minlength=k) > 0      # an empty cluster's centroid is a copy of whichever cluster the split drew
     num = np.linalg.norm(c[same].astype(np.float64) - rc[same].astype(np.float64), axis=1)
     den = np.linalg.norm(rc[same].astype(np.float64), axis=1) + 1e-30
-    assert (num / den).max() < 1e-5, float((num / den).max())
+    rel = num / den
+    off = rel >= 1e-5
+    assert off.sum() <= 2 * int(diff.sum()), (int(off.sum()), int(diff.sum()))
+    assert (rel[off] < 2.5e-3).all(), float(rel.max())
     return float(same.mean())
 
 
