@@ -147,11 +147,13 @@ int skm_last_prune_path(const skm_handle* h);
  * (pair, 64-dimension block) steps of the candidate-list walk (each reads 256 bytes of a centroid and of a
  * point), out3[2] rows whose candidate list overflowed and were redone densely.  For roofline accounting. */
 skm_status skm_get_prune_counters(const skm_handle* h, uint64_t* out3);
-/* Work of the chain over gathered centroids (prune path 6) so far: out3[0] rows of the tiles it processed, out3[1]
+/* Work of the chain over gathered centroids (prune path 6) so far: out4[0] rows of the tiles it processed, out4[1]
  * centroid columns its units held (each unit rounded up to a multiple of 16), summed over tiles, passes and
- * units - its tensor-core work is 2 * 128 * out3[1] * d flop, counted once - and out3[2] the points that the
- * optimistic pass handed to the exact, chunk-by-chunk pass.  For roofline accounting. */
-skm_status skm_get_chain_counters(const skm_handle* h, uint64_t* out3);
+ * units - its tensor-core work is 2 * 128 * out4[1] * d flop, counted once -, out4[2] the points that the
+ * optimistic pass flagged (their best candidate can move; they are settled by replaying the search over the
+ * candidates the pass recorded) and out4[3] those of them whose candidate lists overflowed and that went through the
+ * exact, chunk-by-chunk chain pass instead.  For roofline accounting. */
+skm_status skm_get_chain_counters(const skm_handle* h, uint64_t* out4);
 /* Objective of the last iteration accumulated in float64 (the reference sums float32). */
 double skm_last_objective_f64(const skm_handle* h);
 

@@ -13,7 +13,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJDIR = os.path.join(HERE, "build")
-SOURCES = ["kernels.cu", "kernels_pruned_dense.cu", "kernels_tc.cu", "kernels_tc_sparse.cu", "kernels_tc_rotate.cu", "kernels_walk.cu", "kernels_topk.cu", "kernels_group.cu", "engine.cu",
+SOURCES = ["kernels.cu", "kernels_pruned_dense.cu", "kernels_tc.cu", "kernels_tc_sparse.cu", "kernels_tc_rotate.cu", "kernels_walk.cu", "kernels_topk.cu", "kernels_replay.cu", "engine.cu",
            "comm_nccl.cu", "noalloc.cu", "abi.cu"]
 HEADERS = ["common.cuh", "device_utils.cuh", "gemm_simt.cuh", "tc_ptx.cuh", "kernels_tc.cuh", "noalloc.h", "engine.h", "host_logic.h", "comm_nccl.h",
            os.path.join("..", "..", "include", "skm_b200.h")]

@@ -151,10 +151,10 @@ skm_status skm_get_prune_counters(const skm_handle* h, uint64_t* out3) {
     h->engine->prune_counters(out3);
     return SKM_OK;
 }
-skm_status skm_get_chain_counters(const skm_handle* h, uint64_t* out3) {
+skm_status skm_get_chain_counters(const skm_handle* h, uint64_t* out4) {
     SKM_NEED(h);
-    if (!out3) return SKM_INVALID_ARGUMENT;
-    h->engine->chain_counters(out3);
+    if (!out4) return SKM_INVALID_ARGUMENT;
+    h->engine->chain_counters(out4);
     return SKM_OK;
 }
 double skm_last_objective_f64(const skm_handle* h) { return (h && h->engine) ? h->engine->last_objective_f64() : 0.0; }

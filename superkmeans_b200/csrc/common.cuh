@@ -131,6 +131,33 @@ void launch_pruned_prepare(const PrunedParams& p, PruneSplitWorkspace& ws, cudaS
 // Runs the dense chain for the n_hard points listed in ws.hard_idx.
 void launch_assign_pruned_dense(const PrunedParams& p, PruneSplitWorkspace& ws, size_t n_hard, cudaStream_t stream);
 
+// Replay of the pruned search for the points listed in idx[0 .. n_listed) (rows of x) from the candidates the optimistic
+// chain pass recorded for them (kernels_replay.cu).
+struct ReplayParams {
+    const float* x;              // rows, row-major, d floats each
+    const float* y;              // row-major centroids
+    const float* ratios;
+    const float* best_in;        // per row: exact distance to the previous centroid
+    const uint32_t* prev;        // per row: previous centroid
+    const uint32_t* idx;         // listed rows
+    const uint32_t* cand;        // per row two lists of `cap` centroid indices
+    const uint32_t* meta;        // per row: list lengths (bits 0..7, 8..15) and the overflow bit (16)
+    uint32_t* knn;               // per row, written when the point moves
+    float* dist;
+    float* thr;                  // per listed point and chunk of 1024 centroids: best at the chunk's start * ratio[partial_d]
+    uint32_t* overflow;          // per listed point: 1 when its lists overflowed (nothing else is decided for it)
+    size_t n_listed;
+    size_t k;
+    uint32_t d;
+    uint32_t partial_d;
+    uint32_t vertical_d;
+    uint32_t horizontal_d;
+    uint32_t cap;
+};
+void launch_replay_candidates(const ReplayParams& p, cudaStream_t stream);
+void launch_scatter_u32(const uint32_t* idx, const uint32_t* in, uint32_t* out, size_t n, cudaStream_t stream);       // out[idx[i]] = in[i]
+void launch_compose_u32(const uint32_t* outer, const uint32_t* inner, uint32_t* out, size_t n, cudaStream_t stream);  // out[i] = outer[inner[i]]
+
 // Pruned assignment with candidate lists made by the tensor-core first test (kernels_tc.cu) and walked by
 // walk_lists_kernel (kernels_walk.cu), for the row tiles [tile0, tile0 + n_tiles) of 128 points.
 struct WalkParams {

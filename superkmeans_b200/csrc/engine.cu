@@ -549,6 +549,11 @@ void run_pruned_pass_sorted(const PrunedParams& p, PrunePassBuffers& b, float ra
         }
         uint32_t* dirty_b = b.dirty_b.ensure(batch);
         SKM_CUDA(cudaMemsetAsync(dirty_b, 0, sizeof(uint32_t) * rows_in_batch, stream));
+        // candidates of the flagged points, for the replay: two lists of kCandCap per point
+        constexpr uint32_t kCandCap = 16;
+        const bool replay = std::getenv("SKM_NO_CANDIDATE_REPLAY") == nullptr;
+        uint32_t* cand_b = replay ? b.cand.ensure(batch * 2 * kCandCap) : nullptr;
+        uint32_t* meta_b = replay ? b.cand_meta.ensure(batch) : nullptr;
         {
             const size_t per = std::min(n_t, chain_per_launch);
             uint32_t* ubits = b.union_bits.ensure(per * union_words);
@@ -560,10 +565,10 @@ void run_pruned_pass_sorted(const PrunedParams& p, PrunePassBuffers& b, float ra
                 tc::launch_union(xb, rows_in_batch, p.k, p.d, p.partial_d, nx_b, p.norms_y, best_b, ratio_first, map_dev + t0, nt, ubits, union_words, y_split, stream);
                 tc::launch_build_flat_cols(ubits, union_words, nt, p.k, cols, totals, cols_stride, sparse_cols, stream);
                 tc::launch_sparse_chain(xb, rows_in_batch, p.k, p.d, p.partial_d, p.vertical_d, p.horizontal_d, chain_norms_xb, chain_norms_y, p.ratios, best_b, knn_b, dist_b, np_b,
-                                        top2_b, y_split, map_dev + t0, nt, cols, totals, cols_stride, stream, dirty_b);
+                                        top2_b, y_split, map_dev + t0, nt, cols, totals, cols_stride, stream, dirty_b, cand_b, meta_b, kCandCap);
             }
         }
-        // the points whose best candidate moves: gathered in order, redone chunk by chunk
+        // the points whose best candidate can move, in order
         PruneSplitWorkspace cw;
         cw.positions = b.positions.ensure(prune_split_positions_elems(batch));
         cw.hard_idx = b.hard_idx.ensure(batch);
@@ -574,25 +579,86 @@ void run_pruned_pass_sorted(const PrunedParams& p, PrunePassBuffers& b, float ra
         const size_t n_dirty = static_cast<size_t>(counters_host[0] & 0xFFFFFFFFull);
         b.total_redone_rows += n_dirty;
         if (n_dirty == 0) return;
-        const size_t nt_d = (n_dirty + kTileM - 1) / kTileM;
-        float* xd = b.listed_x.ensure(n_dirty * p.d);
-        float* best_d = b.listed_best.ensure(n_dirty);
-        uint32_t* knn_d = b.listed_knn.ensure(n_dirty);
-        uint32_t* prev_d = b.redo_prev.ensure(n_dirty);
-        float* dist_d = b.listed_dist.ensure(n_dirty);
-        uint32_t* np_d = b.listed_np.ensure(n_dirty);
-        float* nx_d = b.redo_nx.ensure(n_dirty);
-        uint2* top2_d = b.listed_top2.ensure(n_dirty);
-        float* chain_nd = b.listed_norms.ensure(n_dirty * n_ck);
-        uint32_t* iota = b.tile_iota.ensure(nt_d);
-        launch_gather_listed(xb, best_b, prev_b, cw.hard_idx, n_dirty, p.d, xd, best_d, knn_d, stream);
-        SKM_CUDA(cudaMemcpyAsync(prev_d, knn_d, sizeof(uint32_t) * n_dirty, cudaMemcpyDeviceToDevice, stream));
-        launch_row_sqnorms(xd, n_dirty, p.d, p.partial_d, nx_d, stream);
-        launch_chain_norms(xd, n_dirty, p.d, p.partial_d, p.vertical_d, p.horizontal_d, false, chain_nd, stream);
-        launch_iota_u32(iota, nt_d, stream);
-        launch_init_chain_rows(iota, nt_d, n_dirty, prev_d, best_d, knn_d, dist_d, np_d, top2_d, stream);
-        exact_chain(xd, n_dirty, iota, nt_d, nx_d, best_d, knn_d, dist_d, np_d, top2_d, chain_nd);
-        launch_scatter_listed(cw.hard_idx, n_dirty, knn_d, dist_d, np_d, knn_b, dist_b, np_b, stream);
+
+        // The exact chain, chunk by chunk, for the points idx[0 .. cnt) of the batch (gathered, their order kept).
+        auto exact_redo = [&](const uint32_t* idx, size_t cnt) {
+            const size_t nt_d = (cnt + kTileM - 1) / kTileM;
+            float* xd = b.listed_x.ensure(cnt * p.d);
+            float* best_d = b.listed_best.ensure(cnt);
+            uint32_t* knn_d = b.listed_knn.ensure(cnt);
+            uint32_t* prev_d = b.redo_prev.ensure(cnt);
+            float* dist_d = b.listed_dist.ensure(cnt);
+            uint32_t* np_d = b.listed_np.ensure(cnt);
+            float* nx_d = b.redo_nx.ensure(cnt);
+            uint2* top2_d = b.listed_top2.ensure(cnt);
+            float* chain_nd = b.listed_norms.ensure(cnt * n_ck);
+            uint32_t* iota = b.tile_iota.ensure(nt_d);
+            launch_gather_listed(xb, best_b, prev_b, idx, cnt, p.d, xd, best_d, knn_d, stream);
+            SKM_CUDA(cudaMemcpyAsync(prev_d, knn_d, sizeof(uint32_t) * cnt, cudaMemcpyDeviceToDevice, stream));
+            launch_row_sqnorms(xd, cnt, p.d, p.partial_d, nx_d, stream);
+            launch_chain_norms(xd, cnt, p.d, p.partial_d, p.vertical_d, p.horizontal_d, false, chain_nd, stream);
+            launch_iota_u32(iota, nt_d, stream);
+            launch_init_chain_rows(iota, nt_d, cnt, prev_d, best_d, knn_d, dist_d, np_d, top2_d, stream);
+            exact_chain(xd, cnt, iota, nt_d, nx_d, best_d, knn_d, dist_d, np_d, top2_d, chain_nd);
+            launch_scatter_listed(idx, cnt, knn_d, dist_d, np_d, knn_b, dist_b, np_b, stream);
+        };
+        if (!replay) {
+            b.total_fallback_rows += n_dirty;
+            exact_redo(cw.hard_idx, n_dirty);
+            return;
+        }
+        // Replay of the search over the recorded candidates (assignment, distance, per-chunk thresholds), then the
+        // not-pruned counts from a first test with those thresholds.
+        const uint32_t n_chunks32 = static_cast<uint32_t>(n_chunks);
+        float* thr = b.replay_thr.ensure(n_dirty * n_chunks);
+        uint32_t* ovf = b.replay_ovf.ensure(n_dirty);
+        ReplayParams rp{};
+        rp.x = xb;
+        rp.y = p.y;
+        rp.ratios = p.ratios;
+        rp.best_in = best_b;
+        rp.prev = prev_b;
+        rp.idx = cw.hard_idx;
+        rp.cand = cand_b;
+        rp.meta = meta_b;
+        rp.knn = knn_b;
+        rp.dist = dist_b;
+        rp.thr = thr;
+        rp.overflow = ovf;
+        rp.n_listed = n_dirty;
+        rp.k = p.k;
+        rp.d = static_cast<uint32_t>(p.d);
+        rp.partial_d = p.partial_d;
+        rp.vertical_d = p.vertical_d;
+        rp.horizontal_d = p.horizontal_d;
+        rp.cap = kCandCap;
+        launch_replay_candidates(rp, stream);
+        {
+            float* xd = b.listed_x.ensure(n_dirty * p.d);
+            float* best_d = b.listed_best.ensure(n_dirty);
+            uint32_t* knn_d = b.listed_knn.ensure(n_dirty);
+            float* nx_d = b.redo_nx.ensure(n_dirty);
+            uint32_t* np_d = b.replay_np.ensure(n_dirty);
+            launch_gather_listed(xb, best_b, prev_b, cw.hard_idx, n_dirty, p.d, xd, best_d, knn_d, stream);
+            launch_row_sqnorms(xd, n_dirty, p.d, p.partial_d, nx_d, stream);
+            tc::launch_count_first_test(xd, n_dirty, p.k, p.d, p.partial_d, nx_d, p.norms_y, thr, n_chunks32, np_d, y_split, stream);
+            launch_scatter_u32(cw.hard_idx, np_d, np_b, n_dirty, stream);
+        }
+        // points with more candidates than the lists hold
+        PruneSplitWorkspace cw2;
+        cw2.positions = b.positions2.ensure(prune_split_positions_elems(n_dirty));
+        cw2.hard_idx = b.hard_idx2.ensure(n_dirty);
+        cw2.n_hard_dev = b.n_hard_dev2.ensure(1);
+        launch_compact_flags(ovf, n_dirty, cw2, stream);
+        SKM_CUDA(cudaMemcpyAsync(&counters_host[0], cw2.n_hard_dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
+        SKM_CUDA(cudaStreamSynchronize(stream));
+        const size_t n_over = static_cast<size_t>(counters_host[0] & 0xFFFFFFFFull);
+        if (n_over == 0) return;
+        b.total_fallback_rows += n_over;
+        uint32_t* over_rows = b.hard_idx3.ensure(n_over);
+        launch_compose_u32(cw.hard_idx, cw2.hard_idx, over_rows, n_over, stream);
+        // their state is still the starting one: the replay leaves such points alone
+        exact_redo(over_rows, n_over);
     };
 
     for (size_t b0 = 0; b0 < p.n; b0 += batch) {

@@ -151,7 +151,10 @@ struct PrunePassBuffers {
     // totals since creation: rows of tiles sent through the gathered chain, centroid columns (rounded to 16) its units
     // held, summed over tiles and chunks - the chain's tensor-core work is 2 * 128 * columns * d flop (counted once)
     unsigned long long total_sparse_rows = 0, total_sparse_cols = 0;
-    unsigned long long total_redone_rows = 0;   // points of the optimistic chain pass that had to be redone exactly
+    unsigned long long total_redone_rows = 0;   // points the optimistic chain pass flagged (settled by the candidate replay)
+    unsigned long long total_fallback_rows = 0; // ... of which the candidate lists overflowed: redone by the exact chain pass
+    DeviceBuffer<uint32_t> cand, cand_meta, replay_ovf, replay_np, positions2, hard_idx2, hard_idx3, n_hard_dev2;
+    DeviceBuffer<float> replay_thr;
 };
 // mode: 0 = automatic: with rows that TMA can address, the points are taken in the order of their previous centroid and
 // every tile of 128 goes either through the first test + list walk or, when many of its points keep a large share of
@@ -201,10 +204,11 @@ class Engine {
         out[1] = prune_bufs_.total_pair_steps;
         out[2] = prune_bufs_.total_redo_rows;
     }
-    void chain_counters(uint64_t out[3]) const {
+    void chain_counters(uint64_t out[4]) const {
         out[0] = prune_bufs_.total_sparse_rows;
         out[1] = prune_bufs_.total_sparse_cols;
         out[2] = prune_bufs_.total_redone_rows;
+        out[3] = prune_bufs_.total_fallback_rows;
     }
     const std::vector<skm_iter_stats>& stats(int phase) const;
     int device() const { return device_; }

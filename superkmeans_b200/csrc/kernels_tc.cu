@@ -71,6 +71,11 @@ struct Params {
     // tile passes the (slightly widened) first test against centroid c
     uint32_t* union_bits;
     uint32_t union_words;
+    // counting epilogue (MODE_COUNT): count_out[row] += number of centroids whose partial distance over the first kdim
+    // dimensions is below thr_rows[row * thr_chunks + chunk of 1024 the centroid lies in]
+    const float* thr_rows;
+    uint32_t thr_chunks;
+    uint32_t* count_out;
     // Y arrives already split: tmap_y covers the hi parts, tmap_ylo the lo parts, and the splitter warps
     // only treat X
     bool y_presplit;
@@ -79,7 +84,7 @@ struct Params {
     uint32_t debug_producer_stop;
 };
 
-enum { MODE_ARGMIN = 0, MODE_STORE = 1, MODE_PRUNE = 2, MODE_UNION = 3 };
+enum { MODE_ARGMIN = 0, MODE_STORE = 1, MODE_PRUNE = 2, MODE_UNION = 3, MODE_COUNT = 4 };
 constexpr float kUnionSlack = 1.0f / 512.0f;   // see the union epilogue
 
 template <int MODE>
@@ -102,7 +107,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&ctrl->tmem_full[b], 1);
-            mbar_init(&ctrl->tmem_empty[b], (MODE == MODE_PRUNE || MODE == MODE_UNION) ? 256 : 128);
+            mbar_init(&ctrl->tmem_empty[b], (MODE == MODE_PRUNE || MODE == MODE_UNION || MODE == MODE_COUNT) ? 256 : 128);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
@@ -113,7 +118,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
     tc_fence_after();
     const uint32_t tmem_base = ctrl->tmem_base;
 
-    constexpr bool kTiled = (MODE == MODE_PRUNE || MODE == MODE_UNION);   // works on a given range / list of row tiles
+    constexpr bool kTiled = (MODE == MODE_PRUNE || MODE == MODE_UNION || MODE == MODE_COUNT);   // works on a given range / list of row tiles
     const size_t rt_begin = kTiled ? p.tile0 : 0;
     const size_t n_row_tiles = kTiled ? p.tile0 + p.n_tiles : (p.n + BM - 1) / BM;
     // row tile that entry rt of the loops below stands for
@@ -270,11 +275,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                     thr = fmaf(t0, 1e-4f, t0) + (kUnionSlack + 1e-6f) * nx;
                 }
             }
+            uint32_t counted = 0;   // MODE_COUNT
             for (uint32_t nt = 0; nt < n_col_tiles && ok; ++nt, ++t) {
                 const uint32_t b = t & 1u, tph = (t >> 1) & 1u;
                 const size_t col0 = static_cast<size_t>(nt) * BN;
                 float* ny = ctrl->ny[warp & 3][b];
                 if (MODE == MODE_PRUNE && (nt & 3u) == 0 && lane == 0) my_offs[nt >> 2] = filled;
+                if (MODE == MODE_COUNT && (nt & 3u) == 0) thr = row_valid ? __ldg(p.thr_rows + row * p.thr_chunks + (nt >> 2)) : -FLT_MAX;
                 if (MODE == MODE_ARGMIN) {
                     // each warp keeps its own copy, so no cross-warp barrier is needed
                     for (int j = lane; j < BN; j += 32) ny[j] = (col0 + j < p.k) ? __ldg(p.norms_y + col0 + j) : 0.f;
@@ -335,6 +342,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
                         mask &= n_valid >= 32u ? 0xFFFFFFFFu : ((1u << n_valid) - 1u);
                         const uint32_t any = __reduce_or_sync(0xffffffffu, mask);
                         if (any != 0 && lane == 0) atomicOr(my_union + (first >> 5), any);
+                    } else if (MODE == MODE_COUNT) {
+                        uint32_t mask = 0;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 nyv = *reinterpret_cast<const float4*>(ny + ch * 32 + j);
+                            const float p0 = fmaf(-2.0f, __uint_as_float(r[j + 0]), nx) + nyv.x;
+                            const float p1 = fmaf(-2.0f, __uint_as_float(r[j + 1]), nx) + nyv.y;
+                            const float p2 = fmaf(-2.0f, __uint_as_float(r[j + 2]), nx) + nyv.z;
+                            const float p3 = fmaf(-2.0f, __uint_as_float(r[j + 3]), nx) + nyv.w;
+                            mask |= (p0 < thr ? (1u << j) : 0u) | (p1 < thr ? (2u << j) : 0u) | (p2 < thr ? (4u << j) : 0u) | (p3 < thr ? (8u << j) : 0u);
+                        }
+                        const size_t first = col0 + static_cast<size_t>(ch) * 32;
+                        const uint32_t n_valid = first >= p.k ? 0u : static_cast<uint32_t>(min(static_cast<size_t>(32), p.k - first));
+                        mask &= n_valid >= 32u ? 0xFFFFFFFFu : ((1u << n_valid) - 1u);
+                        counted += __popc(mask);
                     } else if (MODE == MODE_PRUNE) {
                         // test of the first checkpoint for 32 centroids, then a warp scan places every row's
                         // survivors behind those of the lower lanes
@@ -435,6 +457,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const __grid_co
             }
             if (MODE == MODE_ARGMIN && ok && row_valid) p.out_top2[row] = make_uint2(i1, i2);
             if (MODE == MODE_PRUNE && ok && lane == 0) my_offs[(n_col_tiles + 3) / 4] = filled;
+            if (MODE == MODE_COUNT && ok && row_valid && counted != 0) atomicAdd(p.count_out + row, counted);   // the row's other half adds its own
         }
     }
 
@@ -1259,6 +1282,36 @@ void launch_first_test(const float* x, const float* y, size_t n, size_t k, size_
     SKM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<MODE_PRUNE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES)));
     const int grid = static_cast<int>(std::min<size_t>(n_tiles, static_cast<size_t>(sm_count(device))));
     gemm_tc_kernel<MODE_PRUNE><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, ty, tylo, p);
+    note_kernel_launch();
+    SKM_CUDA(cudaGetLastError());
+}
+
+void launch_count_first_test(const float* x, size_t n, size_t k, size_t d, uint32_t partial_d, const float* norms_x, const float* norms_y, const float* thr_rows,
+                             uint32_t thr_chunks, uint32_t* count_out, const float* y_split, cudaStream_t stream) {
+    if (n == 0 || k == 0) return;
+    int device = 0;
+    SKM_CUDA(cudaGetDevice(&device));
+    const CUtensorMap tx = make_tmap(x, partial_d, n, d, BM);
+    const CUtensorMap ty = make_tmap(y_split, partial_d, k, d, BN);
+    const CUtensorMap tylo = make_tmap(y_split + k * d, partial_d, k, d, BN);
+    Params p{};
+    p.y_presplit = true;
+    p.n = n;
+    p.k = k;
+    p.kdim = partial_d;
+    p.norms_x = norms_x;
+    p.norms_y = norms_y;
+    p.error = error_flag(device);
+    p.wait_limit = g_wait_limit;
+    p.tile0 = 0;
+    p.n_tiles = (n + BM - 1) / BM;
+    p.thr_rows = thr_rows;
+    p.thr_chunks = thr_chunks;
+    p.count_out = count_out;
+    SKM_CUDA(cudaMemsetAsync(count_out, 0, sizeof(uint32_t) * n, stream));
+    SKM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<MODE_COUNT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES)));
+    const int grid = static_cast<int>(std::min<size_t>(p.n_tiles, static_cast<size_t>(sm_count(device))));
+    gemm_tc_kernel<MODE_COUNT><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, ty, tylo, p);
     note_kernel_launch();
     SKM_CUDA(cudaGetLastError());
 }

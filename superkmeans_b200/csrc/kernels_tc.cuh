@@ -48,6 +48,12 @@ void launch_first_test(const float* x, const float* y, size_t n, size_t k, size_
 // The same first test (threshold widened by 1e-4 relative) for the row tiles tile_map[0 .. n_tiles), keeping only its
 // footprint: bit c of union_bits[t * union_words + c / 32] is set (atomic OR into zeroed memory) when some row of tile t
 // passes the test against centroid c.  y_split: the centroids split by launch_presplit.
+// Counts, for every row of x (n x d, only the first partial_d dimensions are read), the centroids whose partial distance
+// is below thr_rows[row * thr_chunks + chunk], chunk = the centroid's block of 1024: the first ADSampling test with a
+// threshold per point and chunk.  count_out is zeroed by the call.
+void launch_count_first_test(const float* x, size_t n, size_t k, size_t d, uint32_t partial_d, const float* norms_x, const float* norms_y, const float* thr_rows,
+                             uint32_t thr_chunks, uint32_t* count_out, const float* y_split, cudaStream_t stream);
+
 void launch_union(const float* x, size_t n, size_t k, size_t d, uint32_t partial_d, const float* norms_x, const float* norms_y, const float* best_in, float ratio_first,
                   const uint32_t* tile_map, size_t n_tiles, uint32_t* union_bits, uint32_t union_words, const float* y_split, cudaStream_t stream);
 
@@ -60,7 +66,7 @@ void launch_union(const float* x, size_t n, size_t k, size_t d, uint32_t partial
 void launch_sparse_chain(const float* x, size_t n, size_t k, size_t d, uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d, const float* chain_norms_x,
                          const float* chain_norms_y, const float* ratios, const float* best_in, uint32_t* knn, float* dist, uint32_t* not_pruned, uint2* top2_scratch,
                          const float* y_split, const uint32_t* tile_map, size_t n_tiles, const uint16_t* cols, const uint32_t* col_counts, size_t cols_stride,
-                         cudaStream_t stream, uint32_t* dirty = nullptr);
+                         cudaStream_t stream, uint32_t* dirty = nullptr, uint32_t* cand = nullptr, uint32_t* cand_meta = nullptr, uint32_t cand_cap = 0);
 // With `dirty` the call is the OPTIMISTIC pass instead: cols holds ONE ascending list of global centroid indices per tile
 // (launch_build_flat_cols; col_counts = the list lengths, cols_stride >= k <= 65536) and every threshold comes from
 // best_in alone, as if no point's best candidate changed during the search.  Written: not_pruned (first-test survivors)

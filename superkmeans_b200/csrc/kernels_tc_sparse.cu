@@ -51,7 +51,10 @@ struct SparseParams {
     float* dist;
     uint32_t* not_pruned;
     uint2* top2;                    // out: the two smallest final distances seen by the chain, per point
-    uint32_t* dirty;                // optimistic pass only, out: 1 = the point has to be redone by the exact chain
+    uint32_t* dirty;                // optimistic pass only, out: 1 = the point's best candidate can move
+    uint32_t* cand;                 // optimistic pass only, out: per point two lists (one per thread of the row) of cand_cap centroid indices
+    uint32_t* cand_meta;            //   list lengths in bits 0..7 and 8..15, bit 16 = a list overflowed
+    uint32_t cand_cap;
     const float* y_hi;              // k x d, tf32 hi parts of the centroids
     const float* y_lo;              // k x d, tf32 lo parts
     const uint32_t* tile_map;       // n_tiles row-tile indices
@@ -242,15 +245,19 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
         if (lane == 0) {
             uint32_t kbt = 0;
             uint32_t uses[2] = {0, 0};
+            bool unread[2] = {false, false};   // accumulator a was handed to the rows and they have not confirmed reading it
             bool ok = true;
             long long w_loaded = 0, w_conv = 0, n_steps = 0;
             const long long t_begin = clock64();
             SPARSE_FOR_EACH_UNIT_SEGMENT({
                 ++n_steps;
                 // the rows must have read this accumulator's previous checkpoint before it grows (or restarts)
-                if (uses[a] > 0 && !timed_wait(&ctrl->acc_loaded[a], (uses[a] - 1) & 1u, wctx, 22, w_loaded)) {
-                    ok = false;
-                    break;
+                if (unread[a]) {
+                    if (!timed_wait(&ctrl->acc_loaded[a], (uses[a] - 1) & 1u, wctx, 22, w_loaded)) {
+                        ok = false;
+                        break;
+                    }
+                    unread[a] = false;
                 }
                 tc_fence_after();
                 const uint32_t acc = tmem_base + a * BN;
@@ -275,8 +282,14 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                     }
                     umma_commit(&ctrl->empty[s]);
                 }
-                if (ok) umma_commit(&ctrl->acc_ready[a]);
-                ++uses[a];
+                // The optimistic pass looks at the accumulator after the first segment (first test, counts) and after the
+                // last one (could another centroid win) only: a test in between can only clear a row that the last one
+                // would flag, never the other way round, so the segments in between accumulate without a hand-over.
+                if (!MERGED || seg == 0 || seg + 1 == p.n_seg) {
+                    if (ok) umma_commit(&ctrl->acc_ready[a]);
+                    ++uses[a];
+                    unread[a] = true;
+                }
             })
             atomicAdd(&g_role_cycles[0], static_cast<unsigned long long>(w_loaded));
             atomicAdd(&g_role_cycles[1], static_cast<unsigned long long>(w_conv));
@@ -398,7 +411,11 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
         // clustering settles.  A point for which some other centroid survives every test and ends below that distance
         // would have had its `best` lowered at that centroid's chunk, and its later chunks tested more strictly: it is
         // flagged (`dirty`) and redone by the exact kernel; for all others the survivor count and the (unchanged)
-        // assignment are final.
+        // assignment are final.  Only two checkpoints are looked at: the first (survivor count, survivor mask) and the
+        // last (does a first-test survivor other than the previous centroid end below the bar).  The tests in between could
+        // only take candidates away, i.e. clear a flag, and they rarely do (a candidate that ends below `best` yet fails
+        // a test on the way is an ADSampling false prune); leaving them out flags a few more rows and saves the rows'
+        // threads twelve of fourteen passes over the accumulator at d = 1024.
         const uint32_t half = static_cast<uint32_t>(warp - 6) >> 2;
         const uint32_t quarter = static_cast<uint32_t>(warp) & 3u;
         const uint32_t lane_base = 32u * quarter;
@@ -418,10 +435,12 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
 #pragma unroll
         for (int q = 0; q < HS; ++q) alive0[q] = alive1[q] = 0;
         float* ny = ctrl->ny[warp - 6];
+        uint32_t ncand = 0;   // competitors this thread found for its row in the current tile
         auto close_row = [&]() -> bool {
             RowPartial mine{};
             mine.cnt = cnt;
             mine.prev_first = dirty;
+            mine.cbi = ncand;
             const uint32_t slot = xchg_uses & 1u;
             ctrl->xchg[slot][half][row_in_tile] = mine;
             __threadfence_block();
@@ -432,6 +451,10 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                 const RowPartial other = ctrl->xchg[slot][1][row_in_tile];
                 p.not_pruned[row] = cnt + other.cnt;
                 p.dirty[row] = (dirty | other.prev_first) ? 1u : 0u;
+                if (p.cand_meta) {
+                    const uint32_t over = (ncand > p.cand_cap || other.cbi > p.cand_cap) ? 1u : 0u;
+                    p.cand_meta[row] = min(ncand, p.cand_cap) | (min(other.cbi, p.cand_cap) << 8) | (over << 16);
+                }
             }
             return true;
         };
@@ -448,8 +471,10 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                 prev = row_valid ? p.knn[row] : 0xFFFFFFFFu;
                 cnt = 0;
                 dirty = 0;
+                ncand = 0;
             }
             const bool first = seg == 0, last = (seg + 1 == p.n_seg);
+            if (!first && !last) continue;   // no hand-over in between (see the MMA warp)
             const uint32_t hw = ((nu + 63u) >> 6) << 5;
             const uint32_t hb = half * hw;
             const uint32_t my_cols = nu > hb ? min(hw, nu - hb) : 0u;
@@ -524,7 +549,12 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                     while (m) {
                         const uint32_t j = __ffs(m) - 1;
                         m &= m - 1;
-                        if (static_cast<uint32_t>(colid[cb0 + j]) != prev) dirty = 1u;
+                        const uint32_t col = colid[cb0 + j];
+                        if (col != prev) {
+                            dirty = 1u;
+                            if (p.cand && ncand < p.cand_cap) p.cand[(row * 2 + half) * p.cand_cap + ncand] = col;
+                            ++ncand;
+                        }
                     }
                 }
             };
@@ -952,7 +982,7 @@ void launch_build_cols(const uint32_t* union_bits, uint32_t union_words, size_t 
 void launch_sparse_chain(const float* x, size_t n, size_t k, size_t d, uint32_t partial_d, uint32_t vertical_d, uint32_t horizontal_d, const float* chain_norms_x,
                          const float* chain_norms_y, const float* ratios, const float* best_in, uint32_t* knn, float* dist, uint32_t* not_pruned, uint2* top2_scratch,
                          const float* y_split, const uint32_t* tile_map, size_t n_tiles, const uint16_t* cols, const uint32_t* col_counts, size_t cols_stride,
-                         cudaStream_t stream, uint32_t* dirty) {
+                         cudaStream_t stream, uint32_t* dirty, uint32_t* cand, uint32_t* cand_meta, uint32_t cand_cap) {
     if (n_tiles == 0 || n == 0 || k == 0) return;
     if (k * d >= (size_t{1} << 32)) throw std::invalid_argument("centroid matrix too large for the gathered chain (k * d must stay below 2^32)");
     int device = 0;
@@ -995,6 +1025,9 @@ void launch_sparse_chain(const float* x, size_t n, size_t k, size_t d, uint32_t 
         if (k > 65536) throw std::invalid_argument("the optimistic chain pass indexes centroids with 16 bits (k <= 65536)");
         p.n_chunks = 1;
         p.dirty = dirty;
+        p.cand = cand;
+        p.cand_meta = cand_meta;
+        p.cand_cap = cand_cap;
         SKM_CUDA(cudaFuncSetAttribute(sparse_chain_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S_SMEM_BYTES)));
         sparse_chain_kernel<true><<<grid, SPARSE_THREADS, S_SMEM_BYTES, stream>>>(maps, p);
     } else {

@@ -149,9 +149,9 @@ class Engine:
 
     def chain_counters(self) -> dict:
         """Work of the chain over gathered centroids so far: rows of its tiles, centroid columns of its units (see skm_get_chain_counters)."""
-        out = (C.c_uint64 * 3)()
+        out = (C.c_uint64 * 4)()
         check(lib.skm_get_chain_counters(self._h, out), self._h)
-        return {"rows": int(out[0]), "columns": int(out[1]), "redone_rows": int(out[2])}
+        return {"rows": int(out[0]), "columns": int(out[1]), "redone_rows": int(out[2]), "fallback_rows": int(out[3])}
 
     @property
     def last_objective_f64(self) -> float:
