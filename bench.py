@@ -57,6 +57,7 @@ def parse_args():
     p.add_argument("--no-pageable", action="store_true", help="skip the end-to-end figure from pageable host memory")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-cache", action="store_true", help="do not keep device buffers between Train calls")
+    p.add_argument("--prune-split", type=int, default=0, help="force one route of the pruned pass (skm_set_prune_split; 0 = automatic), for profiling")
     return p.parse_args()
 
 
@@ -384,6 +385,8 @@ def main():
             comm = skd.make_comm(local_rank)   # the per-iteration sums run inside the library, on the engine's stream
     if not args.no_cache:
         eng.set_workspace_cache(True)
+    if args.prune_split:
+        eng.set_prune_split(args.prune_split)
 
     d, k, kind = spec["d"], spec["k"], spec["kind"]
     metric, unit = unit_of(spec)
@@ -435,6 +438,8 @@ def main():
     for _ in range(args.warmup):
         one_pass(x, True)
     sampler = ClockSampler(local_rank)
+    if kind == "flat":
+        eng.chain_role_cycles()   # clear the role counters of the warm-up steps
     launches0 = eng.kernel_launches()
     if rank == 0:
         sampler.start()
@@ -524,6 +529,10 @@ def main():
                     "note": ("gathered 256-byte centroid blocks served by L2, not HBM: the fraction is against the HBM copy peak for scale only" if bound == "l2"
                              else "rows read once per iteration")}
     roofline["kernels_ms_per_step"] = {c[0]: round(c[1] / args.steps, 3) for c in cands}
+    if kind == "flat":
+        roles = eng.chain_role_cycles()   # of the timed steps (and whatever ran after them)
+        if roles["steps"]:
+            roofline["chain_role_cycles_per_step"] = roles
     traffic = TRAFFIC_PER_ROW.get((dom, d, k))
     if traffic is not None and dom_calls:
         rows_per_launch = work_rows(dom, n_local, stats, e if kind == "flat" else None) * args.steps / dom_calls
@@ -647,7 +656,9 @@ def main():
                   "sums_across_shards": "NCCL group on the engine's stream" if comm is not None else None}
         if kind == "flat":
             config.update({"partial_d": [int(s.partial_d) for s in stats], "not_pruned_pct": [round(float(s.not_pruned_pct), 6) for s in stats],
-                           "objective": float(stats[-1].objective), "prune_path": prune_path})
+                           "objective": float(stats[-1].objective), "prune_path": prune_path, "chain": e.chain_counters()})
+            if args.prune_split:
+                config["prune_split_forced"] = args.prune_split
         line = {
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "seconds_per_step": ms_per_step / 1e3, "wall_ms_per_step": float(np.mean(walls)), "higher_is_better": True,

@@ -286,6 +286,22 @@ def kernel_launches() -> int:
     return int(lib.skm_kernel_launches())
 
 
+_ROLE_NAMES = ("mma_wait_rows", "mma_wait_operands", "mma_total", "rows_wait_accumulator", "rows_norms", "rows_total", "rows_wait_partner", "gather_wait_stage",
+               "gather_wait_copies", "gather_total", "splitter_wait_tile", "producer_wait_stage")
+
+
+def chain_role_cycles() -> dict:
+    """SM cycles the roles of the chain over gathered centroids spent, per (unit, segment) step and averaged over the CTAs of
+    all launches since the last call (skm_debug_role_cycles; the counters are cleared by the call)."""
+    buf = (C.c_uint64 * 16)()
+    check(lib.skm_debug_role_cycles(buf))
+    steps = max(int(buf[12]), 1)
+    out = {name: round(int(buf[i]) / steps, 1) for i, name in enumerate(_ROLE_NAMES)}
+    out["steps"] = int(buf[12])
+    out["ctas"] = int(buf[13])
+    return out
+
+
 def device_allocations() -> int:
     """cudaMalloc / cudaMallocHost calls made by the library in this process so far."""
     return int(lib.skm_device_allocations())

@@ -48,7 +48,19 @@ def _identical_cluster_centroids(c, rc, a, ra, k):
     return float(same.mean()), float(rest.max()) if rest.size else 0.0, int(split_like.sum())
 
 
-def _flat_against_reference(ref, x, k, seed, iters, replay, end_to_end_agree, classify_cap=150):
+def _equal_up_to_ties(xr, centroids, knn, rknn):
+    """Share of points with the same answer, two answers counting as the same when their float64 distances differ by no
+    more than the rounding of the reference's own fp32 formula ||x||^2 + ||c||^2 - 2 x.c (1e-7 of the norms); also the
+    raw share and the mask of tied differences."""
+    differ = np.nonzero(knn != rknn)[0]
+    xs = xr[differ].astype(np.float64)
+    ca, cb = centroids[knn[differ]].astype(np.float64), centroids[rknn[differ]].astype(np.float64)
+    gap = np.abs(((xs - ca) ** 2).sum(1) - ((xs - cb) ** 2).sum(1))
+    tied = gap <= 1e-7 * ((xs ** 2).sum(1) + np.maximum((ca ** 2).sum(1), (cb ** 2).sum(1)))
+    return 1.0 - float((~tied).sum()) / len(knn), 1.0 - len(differ) / len(knn), differ, tied
+
+
+def _flat_against_reference(ref, x, k, seed, iters, replay, end_to_end_agree, classify_cap=150, other_routes=(10,)):
     import superkmeans_b200 as skm
     from superkmeans_b200 import engine as eng
 
@@ -76,17 +88,25 @@ def _flat_against_reference(ref, x, k, seed, iters, replay, end_to_end_agree, cl
         # centroids that coincide to rounding, which several splits of one cluster in one call leave behind
         # (parity_util.coincident_centroids); their count is reported.
         rep = parity_util.coincident_centroids(prev.centroids)
-        raw = float((knn == rknn).mean())
-        differ = np.nonzero(knn != rknn)[0]
-        xs = xr[differ].astype(np.float64)
-        ca, cb = prev.centroids[knn[differ]].astype(np.float64), prev.centroids[rknn[differ]].astype(np.float64)
-        gap = np.abs(((xs - ca) ** 2).sum(1) - ((xs - cb) ** 2).sum(1))
-        tied = gap <= 1e-7 * ((xs ** 2).sum(1) + np.maximum((ca ** 2).sum(1), (cb ** 2).sum(1)))
-        agree = 1.0 - float((~tied).sum()) / n
+        agree, raw, differ, tied = _equal_up_to_ties(xr, prev.centroids, knn, rknn)
         print(f"iteration {t + 1}: assignments equal {raw:.5f}; {int(tied.sum())} of {len(differ)} differences are ties at the reference's own rounding "
               f"({int((rep[knn[differ]] == rep[rknn[differ]]).sum())} between coincident centroids, {int((rep != np.arange(k)).sum())} such centroids); equal up to ties {agree:.5f}")
         assert agree >= 0.999, (t, agree, raw)
-        del xs, ca, cb
+        # the same step through the kernels the automatic choice did not take here (the ordered chain with its candidate
+        # replay is what the headline workload runs)
+        for route in other_routes:
+            eng.set_prune_split(route)
+            try:
+                knn_o, dist_o, npc_o = eng.find_nearest_pruned(xr, prev.centroids, prev.assign, pd)
+            finally:
+                eng.set_prune_split(0)
+            agree_o, raw_o, _, _ = _equal_up_to_ties(xr, prev.centroids, knn_o, rknn)
+            tot_o, rtot = float(npc_o.sum()), float(rnp.sum())
+            print(f"iteration {t + 1}, route {route}: assignments equal {raw_o:.5f}, up to ties {agree_o:.5f}, not-pruned total off by {abs(tot_o - rtot) / rtot:.2e}")
+            assert agree_o >= 0.999, (t, route, agree_o, raw_o)
+            assert abs(tot_o - rtot) <= 5e-3 * rtot + 10, (t, route, tot_o, rtot)
+            same_o = knn_o == rknn
+            assert np.abs(dist_o[same_o] - rdist[same_o]).max() <= 2e-5 * max(1.0, float(rdist.max()))
         bad = np.nonzero(knn != rknn)[0]
         if len(bad) > classify_cap:
             bad = rng.choice(bad, classify_cap, replace=False)
