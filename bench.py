@@ -52,6 +52,7 @@ def parse_args():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     p.add_argument("--n", type=int, default=0, help="override the number of rows (0 = the workload's)")
+    p.add_argument("--iters", type=int, default=0, help="override the iterations of a flat workload (0 = the workload's), for short profiling runs")
     p.add_argument("--cpu-sample", type=int, default=1_000_000, help="rows of the workload given to the CPU reference by the cpu_baseline leg")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-pageable", action="store_true", help="skip the end-to-end figure from pageable host memory")
@@ -358,6 +359,9 @@ def main():
     args = parse_args()
     spec = dict(WORKLOADS[args.workload])
     n = args.n or spec["n"]
+    if args.iters and spec["kind"] == "flat":
+        spec["iters"] = args.iters
+        spec["text"] += f" [iterations overridden: {args.iters}]"
     if args.impl == "reference":
         run_reference_arm(args, spec, n)
         return
@@ -441,6 +445,7 @@ def main():
     if kind == "flat":
         eng.chain_role_cycles()   # clear the role counters of the warm-up steps
     launches0 = eng.kernel_launches()
+    allocs0 = eng.device_allocations()
     if rank == 0:
         sampler.start()
     dev_ms, walls, phase_acc, stats, prune_path = [], [], {}, [], 0
@@ -459,6 +464,7 @@ def main():
         prune_path = e.last_prune_path
     clocks = sampler.stop() if rank == 0 else None
     launches = eng.kernel_launches() - launches0
+    allocs = eng.device_allocations() - allocs0
     n_it = len(stats) if kind == "flat" else spec["iters"]
     ms_per_step = float(np.mean(dev_ms))
     value = n * n_it / (ms_per_step / 1e3)
@@ -665,7 +671,7 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
             "phases_ms_per_step": {name: round(v, 3) for name, v in phases.items()},
             "after_train": extra_calls, "roofline": roofline, "cpu_baseline": cpu_baseline, "parity_on_sample": parity, "sharded_parity": sharded_parity, "e2e": e2e, "e2e_pageable": e2e_pageable,
-            "gpu_launches": int(launches), "clocks": clocks,
+            "gpu_launches": int(launches), "device_allocations_in_timed_region": int(allocs), "clocks": clocks,
         }
         print(json.dumps(line))
     if world > 1:

@@ -15,6 +15,7 @@
 #include <cfloat>
 #include <chrono>
 #include <mutex>
+#include <unordered_map>
 #include <vector>
 
 namespace skmb {
@@ -36,8 +37,18 @@ struct CachedBlock {
 };
 std::mutex g_cache_mu;
 std::vector<CachedBlock> g_cache;
+std::unordered_map<void*, size_t> g_block_bytes;   // true size of every live block that was allocated through the cache path
 bool g_cache_on = false;
-constexpr size_t kCacheMinBytes = size_t{32} << 20;
+constexpr size_t kCacheMinBytes = size_t{64} << 10;
+
+// Sizes are rounded up to one of eight steps per power of two, so that requests that differ a little from call to call
+// (buffers sized by a count that the data decide) land on the same block sizes and find each other in the cache.
+size_t cache_bucket(size_t bytes) {
+    size_t p2 = size_t{1} << 16;
+    while (p2 * 2 <= bytes) p2 *= 2;
+    const size_t step = p2 / 8;
+    return (bytes + step - 1) / step * step;
+}
 thread_local double g_alloc_ms = 0.0;
 
 struct AllocClock {
@@ -61,7 +72,9 @@ void* device_alloc(size_t bytes) {
     AllocClock clock;
     int device = 0;
     SKM_CUDA(cudaGetDevice(&device));
-    if (g_cache_on && bytes >= kCacheMinBytes) {
+    const bool cached_path = g_cache_on && bytes >= kCacheMinBytes;
+    if (cached_path) {
+        bytes = cache_bucket(bytes);
         std::lock_guard<std::mutex> lock(g_cache_mu);
         size_t best = g_cache.size();
         for (size_t i = 0; i < g_cache.size(); ++i) {
@@ -70,6 +83,7 @@ void* device_alloc(size_t bytes) {
         }
         if (best != g_cache.size()) {
             void* p = g_cache[best].p;
+            g_block_bytes[p] = g_cache[best].bytes;
             g_cache.erase(g_cache.begin() + static_cast<long>(best));
             return p;
         }
@@ -87,12 +101,24 @@ void* device_alloc(size_t bytes) {
         e = cudaMalloc(&p, bytes);
     }
     cuda_check(e, "cudaMalloc", __FILE__, __LINE__);
+    if (cached_path) {
+        std::lock_guard<std::mutex> lock(g_cache_mu);
+        g_block_bytes[p] = bytes;
+    }
     return p;
 }
 
 void device_free(void* p, size_t bytes) {
     if (!p) return;
     AllocClock clock;
+    {
+        std::lock_guard<std::mutex> lock(g_cache_mu);
+        const auto it = g_block_bytes.find(p);
+        if (it != g_block_bytes.end()) {
+            bytes = it->second;   // the block's true (rounded-up) size
+            g_block_bytes.erase(it);
+        }
+    }
     if (g_cache_on && bytes >= kCacheMinBytes) {
         int device = 0;
         if (cudaGetDevice(&device) == cudaSuccess) {
