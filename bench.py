@@ -340,6 +340,9 @@ TRAFFIC_PER_ROW = {
     ("gemm_tc_kernel<ARGMIN>", 1024, 10_000): 3.59e9 / 4e5,
     ("gemm_tc_kernel<PRUNE>", 1024, 10_000): 0.377e9 / 4e5,
     ("walk_lists_kernel", 1024, 10_000): 5.86e9 / 4e5,
+    # optimistic chain pass, captured at n = 1 000 000 in the first pruned iteration (the one with the longest centroid
+    # lists: an upper figure for the later ones)
+    ("sparse_chain_kernel", 1024, 10_000): 137.9e9 / 1e6,
 }
 
 
@@ -543,7 +546,7 @@ def main():
     if traffic is not None and dom_calls:
         rows_per_launch = work_rows(dom, n_local, stats, e if kind == "flat" else None) * args.steps / dom_calls
         roofline["traffic"] = traffic * rows_per_launch
-        roofline["traffic_note"] = "dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture at n = 400000 (same d and k), per row, times the rows one launch covers"
+        roofline["traffic_note"] = "DRAM bytes of an ncu capture of this kernel on a slice of the workload (same d and k; profiles/), per row, times the rows one launch covers"
 
     # ---- the configurations that say "Train + Assign": Assign and AssignTrainingPoints of the training rows, device-resident
     extra_calls = None

@@ -135,17 +135,23 @@ struct SplitOp {
 inline size_t split_clusters_flat(std::vector<uint32_t>& sizes, size_t n_samples, size_t n_clusters, uint32_t seed, std::vector<SplitOp>& ops) {
     size_t n_split = 0;
     std::mt19937 rng(seed);
+    // The walk below draws ~n_clusters numbers per empty cluster (tens of millions when a thousand clusters are empty), so
+    // the acceptance probabilities are tabulated - with the reference's own expression, double division rounded to
+    // float - and refreshed for the two clusters a split changes; the draws and comparisons are the reference's.
+    const float denom = (float) (n_samples - n_clusters);
+    auto prob = [&](size_t c) -> float { return (sizes[c] - 1.0) / denom; };
+    std::vector<float> p(n_clusters);
+    for (size_t c = 0; c < n_clusters; ++c) p[c] = prob(c);
+    std::uniform_real_distribution<float> uniform(0, 1);   // stateless: one object draws what a fresh one per call would
     for (size_t ci = 0; ci < n_clusters; ci++) {
         if (sizes[ci] == 0) {
-            size_t cj;
-            for (cj = 0; true; cj = (cj + 1) % n_clusters) {
-                float p = (sizes[cj] - 1.0) / (float) (n_samples - n_clusters);
-                float r = std::uniform_real_distribution<float>(0, 1)(rng);
-                if (r < p) break;
-            }
+            size_t cj = 0;
+            while (!(uniform(rng) < p[cj])) cj = (cj + 1 == n_clusters) ? 0 : cj + 1;
             ops.push_back({static_cast<uint32_t>(ci), static_cast<uint32_t>(cj), 0u, 0.0f});
             sizes[ci] = sizes[cj] / 2;
             sizes[cj] -= sizes[ci];
+            p[ci] = prob(ci);
+            p[cj] = prob(cj);
             n_split++;
         }
     }
@@ -162,18 +168,24 @@ inline size_t split_clusters_hierarchical(std::vector<uint32_t>& sizes, size_t n
     std::mt19937 rng(seed);
     const size_t average_size = n_samples / n_clusters;
     const size_t threshold_size = static_cast<size_t>(static_cast<float>(average_size) * kBalancingThreshold);
-    for (size_t ci = 0; ci < n_clusters; ci++) {
-        if (sizes[ci] == 0) {
-            size_t cj;
-            for (cj = 0; true; cj = (cj + 1) % n_clusters) {
-                float p = (sizes[cj] - 1.0f) / static_cast<float>(n_samples - n_clusters);
-                float r = std::uniform_real_distribution<float>(0, 1)(rng);
-                if (r < p) break;
+    {
+        // tabulated acceptance probabilities, as in split_clusters_flat (here the reference divides in float)
+        const float denom = static_cast<float>(n_samples - n_clusters);
+        auto prob = [&](size_t c) -> float { return (sizes[c] - 1.0f) / denom; };
+        std::vector<float> p(n_clusters);
+        for (size_t c = 0; c < n_clusters; ++c) p[c] = prob(c);
+        std::uniform_real_distribution<float> uniform(0, 1);
+        for (size_t ci = 0; ci < n_clusters; ci++) {
+            if (sizes[ci] == 0) {
+                size_t cj = 0;
+                while (!(uniform(rng) < p[cj])) cj = (cj + 1 == n_clusters) ? 0 : cj + 1;
+                ops.push_back({static_cast<uint32_t>(ci), static_cast<uint32_t>(cj), 0u, 0.0f});
+                sizes[ci] = sizes[cj] / 2;
+                sizes[cj] -= sizes[ci];
+                p[ci] = prob(ci);
+                p[cj] = prob(cj);
+                n_split++;
             }
-            ops.push_back({static_cast<uint32_t>(ci), static_cast<uint32_t>(cj), 0u, 0.0f});
-            sizes[ci] = sizes[cj] / 2;
-            sizes[cj] -= sizes[ci];
-            n_split++;
         }
     }
     for (size_t ci = 0; ci < n_clusters; ci++) {

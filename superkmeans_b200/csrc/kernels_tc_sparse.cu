@@ -13,15 +13,15 @@
 //      in units of up to 256 of them.  A centroid that is not listed fails the first test for every row of the tile,
 //      so leaving it out changes neither the survivor counts nor the winners.
 //
-// Kernel roles (448 threads, one persistent CTA per SM), stage layout and accumulators are those of the dense chain:
+// Kernel roles (512 threads, one persistent CTA per SM), stage layout and accumulators are those of the dense chain:
 //   warp 0      TMA producer of the X tile (128 points x 16 dimensions per stage);
 //   warp 1      MMA issuer: tcgen05.mma kind::tf32, M = 128, N = the unit's column count rounded up to 16;
 //   warps 2-3   split the X tile into tf32 hi / lo parts in place;
-//   warps 4-5   gather the unit's centroid rows: asynchronous 16-byte copies (cp.async) of the hi and lo parts from the
+//   warps 4-7   gather the unit's centroid rows: asynchronous 16-byte copies (cp.async) of the hi and lo parts from the
 //               pre-split centroid matrix (global memory, L2 resident) into the stage, in the 64-byte swizzled layout
 //               the MMA descriptors expect (16-byte unit u of row r at unit u ^ ((r >> 1) & 3)); up to three stages
 //               of copies are in flight, and a stage is announced once its copies have landed;
-//   warps 6-13  the rows' threads: two per point (columns 0-127 and 128-255 of a unit); tests after every segment,
+//   warps 8-15  the rows' threads: two per point (columns 0-127 and 128-255 of a unit); tests after every segment,
 //               merge at chunk ends, as in the dense chain.
 // Every wait is bounded; on expiry the kernel records a code, every role leaves its loops, tensor memory is released
 // and the kernel returns.
@@ -151,7 +151,10 @@ static_assert(sizeof(SparseCtrl) <= S_CTRL_BYTES, "control block too large");
 constexpr uint32_t S_SMEM_BYTES = STAGES * STAGE_BYTES + S_CTRL_BYTES + 1024;
 static_assert(S_SMEM_BYTES <= 232448, "over the shared memory of one CTA");
 constexpr uint32_t SPARSE_MAX_SEGMENTS = 64;
-constexpr int SPARSE_THREADS = 448;
+constexpr int SPARSE_THREADS = 512;
+// warps: 0 TMA producer, 1 MMA issuer, 2-3 X splitter, 4-7 centroid gather, 8-15 rows
+constexpr int kGatherThreads = 128;
+constexpr int kRowWarp0 = 8;
 
 // Order of work shared by all roles: listed tile, chunk of 1024 centroids (skipped when it lists nothing), pair of
 // units, segment, unit of the pair.  A chunk's listed centroids are cut into units of equal width (a multiple of 16, at
@@ -200,7 +203,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&ctrl->full[s], 1);
-            mbar_init(&ctrl->conv[s], 128);   // 64 X-splitter threads + 64 gather threads
+            mbar_init(&ctrl->conv[s], 64 + kGatherThreads);   // 64 X-splitter threads + the gather threads
             mbar_init(&ctrl->empty[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -337,15 +340,17 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
             }
         })
         if (cid == 0) atomicAdd(&g_role_cycles[10], static_cast<unsigned long long>(w_full));
-    } else if (warp < 6) {
-        // ---------------------------------------------------------------- centroid gather (warps 4, 5)
+    } else if (warp < kRowWarp0) {
+        // ---------------------------------------------------------------- centroid gather (warps 4 .. 7)
         // Asynchronous 16-byte copies (cp.async) from the pre-split centroid matrix straight into the stage, in the
         // swizzled layout; no registers are tied up, so the copies of up to three stages are in flight per thread.  A
-        // thread copies unit c16 of the hi and of the lo part of rows r0, r0 + 16, ..., r0 + 240.  A stage is announced
+        // thread copies unit c16 of the hi and of the lo part of rows r0, r0 + 32, ..., r0 + 224 (four warps: the copies
+        // issue rate, ~50 cycles per warp instruction of 32 scattered 16-byte pieces, was the kernel's limit with two).
+        // A stage is announced
         // to the MMA warp two stages after its copies were issued, once cp.async.wait_group says they have landed.
-        const uint32_t gid = threadIdx.x - 128u;   // 0 .. 63
+        const uint32_t gid = threadIdx.x - 128u;   // 0 .. kGatherThreads - 1
         const uint32_t c16 = gid & 3u;
-        const uint32_t r0 = gid >> 2;              // 0 .. 15
+        const uint32_t r0 = gid >> 2;              // 0 .. kGatherThreads / 4 - 1
         uint32_t* rowoff = ctrl->rowoff[0][0];
         uint32_t kbt = 0;
         bool ok = true;
@@ -356,8 +361,8 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                 // element offsets of this thread's centroid rows; rows past the unit's last centroid repeat it (finite
                 // values; their columns are never tested).  Entry r is written and read by this thread only.
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const uint32_t r = r0 + 16u * i;
+                for (int i = 0; i < static_cast<int>(BN * 4 / kGatherThreads); ++i) {
+                    const uint32_t r = r0 + static_cast<uint32_t>(kGatherThreads / 4) * i;
                     if (r < nmma) rowoff[a * BN + r] = (static_cast<uint32_t>(c0) + __ldg(unit_cols + min(r, nu - 1u))) * p.d;
                 }
             }
@@ -371,8 +376,8 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
                 const uint32_t xc = si.x_begin + kb * BK + c16 * 4u;
                 const uint32_t st = smem_base + s * STAGE_BYTES;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const uint32_t r = r0 + 16u * i;
+                for (int i = 0; i < static_cast<int>(BN * 4 / kGatherThreads); ++i) {
+                    const uint32_t r = r0 + static_cast<uint32_t>(kGatherThreads / 4) * i;
                     if (r < nmma) {
                         const uint32_t off = rowoff[a * BN + r] + xc;
                         const uint32_t slot = (r * 4u + (c16 ^ ((r >> 1) & 3u))) * 16u;
@@ -403,7 +408,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
             atomicAdd(&g_role_cycles[9], static_cast<unsigned long long>(clock64() - t_begin));
         }
     } else if (MERGED) {
-        // (warps 6 .. 13)
+        // (warps 8 .. 15)
         // ---------------------------------------------------------------- rows, optimistic pass
         // The chain is run once over ALL the centroids a tile can still reach, in units that ignore the 1024-centroid
         // chunks, with every threshold taken from the distance to the previous centroid.  That is exactly what the
@@ -416,7 +421,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
         // only take candidates away, i.e. clear a flag, and they rarely do (a candidate that ends below `best` yet fails
         // a test on the way is an ADSampling false prune); leaving them out flags a few more rows and saves the rows'
         // threads twelve of fourteen passes over the accumulator at d = 1024.
-        const uint32_t half = static_cast<uint32_t>(warp - 6) >> 2;
+        const uint32_t half = static_cast<uint32_t>(warp - kRowWarp0) >> 2;
         const uint32_t quarter = static_cast<uint32_t>(warp) & 3u;
         const uint32_t lane_base = 32u * quarter;
         const uint32_t row_in_tile = lane_base + lane;
@@ -434,7 +439,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
         uint32_t alive0[HS], alive1[HS];
 #pragma unroll
         for (int q = 0; q < HS; ++q) alive0[q] = alive1[q] = 0;
-        float* ny = ctrl->ny[warp - 6];
+        float* ny = ctrl->ny[warp - kRowWarp0];
         uint32_t ncand = 0;   // competitors this thread found for its row in the current tile
         auto close_row = [&]() -> bool {
             RowPartial mine{};
@@ -479,7 +484,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
             const uint32_t hb = half * hw;
             const uint32_t my_cols = nu > hb ? min(hw, nu - hb) : 0u;
             const uint32_t n_sl = (my_cols + 31u) >> 5;
-            uint16_t* colid = ctrl->colid[warp - 6][a];
+            uint16_t* colid = ctrl->colid[warp - kRowWarp0][a];
             uint32_t cidx[HS];
             if (first) {
 #pragma unroll
@@ -601,16 +606,16 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
             }
         })
         if (ok && cur_lt != ~size_t{0}) close_row();
-        if (warp == 6 && lane == 0) {
+        if (warp == kRowWarp0 && lane == 0) {
             atomicAdd(&g_role_cycles[3], static_cast<unsigned long long>(w_ready));
             atomicAdd(&g_role_cycles[4], static_cast<unsigned long long>(t_norms));
             atomicAdd(&g_role_cycles[5], static_cast<unsigned long long>(clock64() - t_begin));
             atomicAdd(&g_role_cycles[6], static_cast<unsigned long long>(w_xchg));
         }
     } else {
-        // (warps 6 .. 13)
+        // (warps 8 .. 15)
         // ---------------------------------------------------------------- rows: tests at every checkpoint
-        const uint32_t half = static_cast<uint32_t>(warp - 6) >> 2;   // which 128 of a unit's 256 columns
+        const uint32_t half = static_cast<uint32_t>(warp - kRowWarp0) >> 2;   // which 128 of a unit's 256 columns
         const uint32_t quarter = static_cast<uint32_t>(warp) & 3u;
         const uint32_t lane_base = 32u * quarter;
         const uint32_t row_in_tile = lane_base + lane;
@@ -634,7 +639,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
         uint32_t prevpos0 = 0xFFFFFFFFu, prevpos1 = 0xFFFFFFFFu;
 #pragma unroll
         for (int q = 0; q < HS; ++q) alive0[q] = alive1[q] = 0;
-        float* ny = ctrl->ny[warp - 6];
+        float* ny = ctrl->ny[warp - kRowWarp0];
         // End of a chunk: the two threads of the row exchange what they found in their halves of the columns and
         // both apply the same update.  Returns false when the wait ran out.
         auto close_chunk = [&]() -> bool {
@@ -728,7 +733,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
             const uint32_t hb = half * hw;   // first column of this thread's share
             const uint32_t my_cols = nu > hb ? min(hw, nu - hb) : 0u;
             const uint32_t n_sl = (my_cols + 31u) >> 5;
-            uint16_t* colid = ctrl->colid[warp - 6][a];
+            uint16_t* colid = ctrl->colid[warp - kRowWarp0][a];
             uint32_t cidx[HS];
             uint32_t prevpos;
             if (first) {
@@ -899,7 +904,7 @@ __global__ void __launch_bounds__(SPARSE_THREADS, 1) sparse_chain_kernel(const _
         if (ok && cur_lt != ~size_t{0}) {
             if (close_chunk()) close_row();
         }
-        if (warp == 6 && lane == 0) {
+        if (warp == kRowWarp0 && lane == 0) {
             atomicAdd(&g_role_cycles[3], static_cast<unsigned long long>(w_ready));
             atomicAdd(&g_role_cycles[4], static_cast<unsigned long long>(t_norms));
             atomicAdd(&g_role_cycles[5], static_cast<unsigned long long>(clock64() - t_begin));
