@@ -546,7 +546,7 @@ def main():
     if traffic is not None and dom_calls:
         rows_per_launch = work_rows(dom, n_local, stats, e if kind == "flat" else None) * args.steps / dom_calls
         roofline["traffic"] = traffic * rows_per_launch
-        roofline["traffic_note"] = "DRAM bytes of an ncu capture of this kernel on a slice of the workload (same d and k; profiles/), per row, times the rows one launch covers"
+        roofline["traffic_note"] = "DRAM bytes of an ncu capture of this kernel on a slice of the workload (same d and k), per row, times the rows one launch covers"
 
     # ---- the configurations that say "Train + Assign": Assign and AssignTrainingPoints of the training rows, device-resident
     extra_calls = None
