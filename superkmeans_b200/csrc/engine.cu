@@ -9,6 +9,8 @@
 #include <cmath>
 #include <cstring>
 #include <future>
+#include <thread>
+#include <atomic>
 #include <iostream>
 #include <numeric>
 #include <random>
@@ -367,8 +369,10 @@ void Engine::generate_centroids_from_host(const float* data, bool on_device, siz
 
 // Fine-clustering variant (hierarchical_superkmeans.h:333-342): rows of an already rotated device
 // buffer, no rotation.
-void Engine::generate_centroids_from_device_rows(const float* dev_rows, size_t n_points, size_t k_cur) {
-    const std::vector<size_t> idx = forgy_indices(n_points, k_cur, cfg_.seed);
+void Engine::generate_centroids_from_device_rows(const float* dev_rows, size_t n_points, size_t k_cur, const std::vector<size_t>* precomputed) {
+    std::vector<size_t> own;
+    if (!precomputed) own = forgy_indices(n_points, k_cur, cfg_.seed);
+    const std::vector<size_t>& idx = precomputed ? *precomputed : own;
     std::vector<uint64_t> idx64(idx.begin(), idx.end());
     DeviceBuffer<uint64_t> idx_dev;
     SKM_CUDA(cudaMemcpyAsync(idx_dev.ensure(k_cur), idx64.data(), sizeof(uint64_t) * k_cur, cudaMemcpyHostToDevice, stream_));
@@ -1481,12 +1485,28 @@ void Engine::train_hierarchical(const float* data, size_t n, bool on_device, flo
     const size_t max_meso = *std::max_element(meso_sizes.begin(), meso_sizes.end());
     meso_buffer_.ensure(std::max<size_t>(max_meso, 1) * d_);
     meso_norms_.ensure(std::max<size_t>(max_meso, 1));
+    // The Forgy rows of every mesocluster (a shuffle of its member positions each) are drawn ahead by a host thread.
+    auto meso_rows = [&](size_t m) { return std::min<size_t>(meso_sizes[m], n_all - std::min(offsets[m], n_all)); };
+    std::vector<std::vector<size_t>> forgy(n_meso_);
+    std::atomic<size_t> forgy_done{0};
+    std::thread forgy_thread([&, seed = cfg_.seed] {
+        for (size_t m = 0; m < n_meso_; ++m) {
+            if (fine_nums[m] != 0) forgy[m] = forgy_indices(meso_rows(m), fine_nums[m], seed);
+            forgy_done.store(m + 1, std::memory_order_release);
+        }
+    });
+    struct Joiner {
+        std::thread& t;
+        ~Joiner() {
+            if (t.joinable()) t.join();
+        }
+    } joiner{forgy_thread};
     size_t fine_offset = 0;
     for (size_t m = 0; m < n_meso_; ++m) {
         const size_t n_fine = fine_nums[m];
         if (n_fine == 0) continue;
         partial_d_ = initial_pd;
-        const size_t msize = std::min<size_t>(meso_sizes[m], n_all - std::min(offsets[m], n_all));
+        const size_t msize = meso_rows(m);
         n_samples_ = msize;
         if (msize < n_fine) {
             throw std::runtime_error("a mesocluster holds fewer points than the fine clusters allotted to it");
@@ -1494,7 +1514,8 @@ void Engine::train_hierarchical(const float* data, size_t n, bool on_device, flo
         const uint64_t* idx = meso_indices_dev_.get() + offsets[m];
         launch_gather_rows(x_rot_.get(), idx, meso_buffer_.get(), msize, d_, stream_);      // CompactMesoclusterToBuffer (:685-704)
         launch_gather_f32(full_norms_.get(), idx, meso_norms_.get(), msize, stream_);
-        generate_centroids_from_device_rows(meso_buffer_.get(), msize, n_fine);
+        while (forgy_done.load(std::memory_order_acquire) <= m) std::this_thread::yield();
+        generate_centroids_from_device_rows(meso_buffer_.get(), msize, n_fine, &forgy[m]);
 
         const bool always_gemm_only = d_ < kDimensionThresholdForPruning || cfg_.use_blas_only || n_fine <= kNClustersThresholdForPruning;
         bool partial_norms_computed = false;

@@ -257,7 +257,7 @@ class Engine {
     // `precomputed`: the Forgy indices when the caller has already drawn them (on another thread, while buffers were allocated)
     void generate_centroids_from_host(const float* data, bool on_device, size_t n_points_global, size_t k_cur, bool rotate, const std::vector<size_t>* precomputed = nullptr);
     bool sharded_() const { return allreduce_fn_ != nullptr || comm_ != nullptr; }
-    void generate_centroids_from_device_rows(const float* dev_rows, size_t n_points, size_t k_cur);
+    void generate_centroids_from_device_rows(const float* dev_rows, size_t n_points, size_t k_cur, const std::vector<size_t>* precomputed = nullptr);
     void train_flat(const float* data, size_t n, bool on_device, const float* queries, size_t n_queries, float* centroids_out);
     void prepare_recall(const float* queries, size_t n_queries, bool rotate);
     float compute_recall(size_t k_cur);

