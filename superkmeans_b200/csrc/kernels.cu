@@ -1002,106 +1002,11 @@ void launch_sort_by_key(const uint32_t* keys, size_t n, size_t k, UpdateWorkspac
     *order_out = vin;
 }
 
-// Update of a small problem in one launch (the fine clusterings of the hierarchical variant run thousands of them, and the
-// sort-based path above costs eleven launches each).  Block c < k owns cluster c: it scans the assignments in index
-// order, 256 at a time, compacts the members of its cluster (order kept) and adds their rows dimension by dimension -
-// one fixed order of additions, so the result is reproducible.  Block k reduces the distances (float64) and the
-// not-pruned counts.
-constexpr int kSmallUpdateDimsPerThread = 16;   // d <= 4096
-__global__ void __launch_bounds__(256) small_update_kernel(const float* __restrict__ x, const uint32_t* __restrict__ assign, const float* __restrict__ dist,
-                                                           const uint32_t* __restrict__ np, size_t n, size_t k, size_t d, float* __restrict__ sums,
-                                                           uint32_t* __restrict__ counts, double* __restrict__ wcss, unsigned long long* __restrict__ np_total) {
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (blockIdx.x == k) {
-        __shared__ double sd[256];
-        __shared__ unsigned long long su[256];
-        double a = 0.0;
-        unsigned long long b = 0;
-        for (size_t i = tid; i < n; i += 256) {
-            if (dist) a += static_cast<double>(dist[i]);
-            if (np) b += np[i];
-        }
-        sd[tid] = a;
-        su[tid] = b;
-        __syncthreads();
-        for (int o = 128; o > 0; o >>= 1) {
-            if (tid < o) {
-                sd[tid] += sd[tid + o];
-                su[tid] += su[tid + o];
-            }
-            __syncthreads();
-        }
-        if (tid == 0) {
-            if (wcss) *wcss = sd[0];
-            if (np_total && np) *np_total = su[0];
-        }
-        return;
-    }
-    const uint32_t c = blockIdx.x;
-    __shared__ uint32_t members[256];
-    __shared__ uint32_t warp_count[8];
-    float acc[kSmallUpdateDimsPerThread];
-#pragma unroll
-    for (int q = 0; q < kSmallUpdateDimsPerThread; ++q) acc[q] = 0.f;
-    uint32_t total = 0;
-    for (size_t base = 0; base < n; base += 256) {
-        const size_t i = base + tid;
-        const bool mine = i < n && assign[i] == c;
-        const uint32_t ballot = __ballot_sync(0xffffffffu, mine);
-        if (lane == 0) warp_count[warp] = __popc(ballot);
-        __syncthreads();
-        uint32_t before = 0, m = 0;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) {
-            const uint32_t cw = warp_count[w];
-            if (w < warp) before += cw;
-            m += cw;
-        }
-        if (mine) members[before + __popc(ballot & ((1u << lane) - 1u))] = static_cast<uint32_t>(i);
-        __syncthreads();
-        // rows of this chunk's members, in index order; four rows in flight at a time
-        for (uint32_t t = 0; t < m; t += 4) {
-            const uint32_t left = min(4u, m - t);
-            const float* r0 = x + static_cast<size_t>(members[t]) * d;
-            const float* r1 = x + static_cast<size_t>(members[t + (left > 1 ? 1 : 0)]) * d;
-            const float* r2 = x + static_cast<size_t>(members[t + (left > 2 ? 2 : 0)]) * d;
-            const float* r3 = x + static_cast<size_t>(members[t + (left > 3 ? 3 : 0)]) * d;
-#pragma unroll
-            for (int q = 0; q < kSmallUpdateDimsPerThread; ++q) {
-                const size_t j = static_cast<size_t>(tid) + 256u * q;
-                if (j < d) {
-                    const float v0 = __ldg(r0 + j), v1 = __ldg(r1 + j), v2 = __ldg(r2 + j), v3 = __ldg(r3 + j);
-                    float a = acc[q] + v0;
-                    if (left > 1) a += v1;
-                    if (left > 2) a += v2;
-                    if (left > 3) a += v3;
-                    acc[q] = a;
-                }
-            }
-        }
-        total += m;
-        __syncthreads();
-    }
-#pragma unroll
-    for (int q = 0; q < kSmallUpdateDimsPerThread; ++q) {
-        const size_t j = static_cast<size_t>(tid) + 256u * q;
-        if (j < d) sums[static_cast<size_t>(c) * d + j] = acc[q];
-    }
-    if (tid == 0) counts[c] = total;
-}
-
 void launch_update(
     const float* x, const uint32_t* assign, const float* dist, const uint32_t* not_pruned, size_t n, size_t k, size_t d, UpdateWorkspace& ws, float* sums, uint32_t* counts,
     double* wcss, unsigned long long* not_pruned_total, cudaStream_t stream
 ) {
     if (n == 0) return;
-    // (bounded so that one block's scan, n assignments, and the worst case of one cluster holding every point stay cheap)
-    if (n <= 65536 && k <= 2048 && n * k <= (size_t{1} << 26) && d <= 256 * static_cast<size_t>(kSmallUpdateDimsPerThread) &&
-        std::getenv("SKM_NO_SMALL_UPDATE") == nullptr) {
-        small_update_kernel<<<static_cast<unsigned>(k + 1), 256, 0, stream>>>(x, assign, dist, not_pruned, n, k, d, sums, counts, wcss, not_pruned ? not_pruned_total : nullptr);
-        SKM_LAUNCH_CHECK();
-        return;
-    }
     const uint32_t* sorted_keys = nullptr;
     const uint32_t* order = nullptr;
     launch_sort_by_key(assign, n, k, ws, &sorted_keys, &order, stream);

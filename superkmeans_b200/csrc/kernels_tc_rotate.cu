@@ -12,10 +12,8 @@
 //   warp 0      TMA producer (A tile 128 x 16 and B tile 128 x 16 per stage, 64-byte swizzle);
 //   warp 1      MMA issuer (M = 128, N = 128, K = 8; accumulator kb / blocks-per-accumulator);
 //   warps 2-5   split both tiles of a stage into hi / lo parts in place;
-//   warps 6-9   epilogue, one thread per row: adds each accumulator to the row's 128 sums in registers as soon as its
-//               chain is complete and hands it back at once, so the next tile's chains run while this tile's later
-//               chains and its stores are still under way; then stores the row and (optionally) accumulates its
-//               squared norm.
+//   warps 6-9   epilogue, one thread per row: sums the accumulators 32 columns at a time, stores the row segment and
+//               (optionally) accumulates the squared norm of the output row.
 // Every wait is bounded (see kernels_tc.cu).
 #include <stdexcept>
 #include <string>
@@ -50,8 +48,8 @@ struct RotCtrl {
     uint64_t full[STAGES];
     uint64_t conv[STAGES];
     uint64_t empty[STAGES];
-    uint64_t acc_full[kAcc];    // MMA -> epilogue: chain a of the current tile is complete
-    uint64_t acc_empty[kAcc];   // epilogue -> MMA: accumulator a has been read
+    uint64_t acc_full;
+    uint64_t acc_empty;
     uint32_t tmem_base;
 };
 static_assert(sizeof(RotCtrl) <= ROT_CTRL_BYTES, "control block too large");
@@ -72,10 +70,8 @@ __global__ void __launch_bounds__(ROT_THREADS, 1) rotate_tc_kernel(const __grid_
             mbar_init(&ctrl->conv[s], 128);
             mbar_init(&ctrl->empty[s], 1);
         }
-        for (int a = 0; a < kAcc; ++a) {
-            mbar_init(&ctrl->acc_full[a], 1);
-            mbar_init(&ctrl->acc_empty[a], 128);
-        }
+        mbar_init(&ctrl->acc_full, 1);
+        mbar_init(&ctrl->acc_empty, 128);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
     }
@@ -117,15 +113,13 @@ __global__ void __launch_bounds__(ROT_THREADS, 1) rotate_tc_kernel(const __grid_
             bool ok = true;
             for (size_t rt = blockIdx.x; rt < n_row_tiles && ok; rt += gridDim.x) {
                 for (uint32_t nt = 0; nt < n_col_tiles && ok; ++nt, ++t) {
+                    // the epilogue must have read the previous tile's accumulators
+                    if (t > 0 && !mbar_wait(&ctrl->acc_empty, (t - 1) & 1u, wctx, 32)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
                     for (uint32_t kb = 0; kb < nkb; ++kb, ++kbt) {
-                        const uint32_t chain = kb / kb_per_acc;
-                        const bool fresh = (kb % kb_per_acc) == 0;
-                        // a chain restarts its accumulator: the epilogue must have read what the previous tile left there
-                        // (it does so while the later chains of that tile are still being multiplied)
-                        if (fresh && t > 0 && !mbar_wait(&ctrl->acc_empty[chain], (t - 1) & 1u, wctx, 32)) {
-                            ok = false;
-                            break;
-                        }
                         const uint32_t s = kbt % STAGES, ph = (kbt / STAGES) & 1u;
                         if (!mbar_wait(&ctrl->conv[s], ph, wctx, 33)) {
                             ok = false;
@@ -133,7 +127,8 @@ __global__ void __launch_bounds__(ROT_THREADS, 1) rotate_tc_kernel(const __grid_
                         }
                         tc_fence_after();
                         const uint32_t st = smem_base + s * STAGE_BYTES;
-                        const uint32_t acc = tmem_base + chain * RN;
+                        const uint32_t acc = tmem_base + (kb / kb_per_acc) * RN;
+                        const bool fresh = (kb % kb_per_acc) == 0;
 #pragma unroll
                         for (uint32_t kk = 0; kk < BK / 8; ++kk) {
                             const uint64_t a_hi = make_desc(st + OFF_A_HI + kk * 32);
@@ -145,8 +140,8 @@ __global__ void __launch_bounds__(ROT_THREADS, 1) rotate_tc_kernel(const __grid_
                             umma_tf32(acc, a_lo, b_hi, 1u, idesc);
                         }
                         umma_commit(&ctrl->empty[s]);
-                        if ((kb + 1) % kb_per_acc == 0 || kb + 1 == nkb) umma_commit(&ctrl->acc_full[chain]);
                     }
+                    if (ok) umma_commit(&ctrl->acc_full);
                 }
             }
         }
@@ -199,50 +194,44 @@ __global__ void __launch_bounds__(ROT_THREADS, 1) rotate_tc_kernel(const __grid_
             const bool row_valid = row < p.n;
             float sq = 0.f;
             for (uint32_t nt = 0; nt < n_col_tiles && ok; ++nt, ++t) {
+                if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->acc_full, t & 1u, wctx, 35))) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
                 const uint32_t taddr = tmem_base + (lane_base << 16);
                 const size_t col0 = static_cast<size_t>(nt) * RN;
-                // the row's RN sums stay in registers while the chains arrive one after the other; every accumulator is
-                // handed back as soon as it is read, so the next tile's chains never wait for this one's output
-                float v[RN];
-                for (uint32_t a = 0; a < n_used && ok; ++a) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(&ctrl->acc_full[a], t & 1u, wctx, 35))) {
-                        ok = false;
-                        break;
+#pragma unroll 1
+                for (int ch = 0; ch < RN / 32; ++ch) {
+                    uint32_t r[32], q[32];
+                    tmem_ld32(taddr + ch * 32, r);
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    for (uint32_t a = 1; a < n_used; ++a) {
+                        tmem_ld32(taddr + a * RN + ch * 32, q);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] += __uint_as_float(q[j]);
                     }
-                    tc_fence_after();
-#pragma unroll
-                    for (int ch = 0; ch < RN / 32; ++ch) {
-                        uint32_t r[32];
-                        tmem_ld32(taddr + a * RN + ch * 32, r);
-                        if (a == 0) {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) v[ch * 32 + j] = __uint_as_float(r[j]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) v[ch * 32 + j] += __uint_as_float(r[j]);
-                        }
+                    if (ch == RN / 32 - 1) {
+                        // everything of this tile is in registers: the accumulators may be overwritten
+                        tc_fence_before();
+                        mbar_arrive(&ctrl->acc_empty);
                     }
-                    tc_fence_before();
-                    mbar_arrive(&ctrl->acc_empty[a]);
-                }
-                if (!ok) break;
-                if (row_valid) {
-#pragma unroll
-                    for (int ch = 0; ch < RN / 32; ++ch) {
+                    if (row_valid) {
                         float* orow = p.out + row * p.ldo + col0 + ch * 32;
                         const size_t left = (col0 + ch * 32 < p.n_out) ? (p.n_out - (col0 + ch * 32)) : 0;
                         if (left >= 32 && (p.ldo % 4 == 0)) {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<float4*>(orow + j) = make_float4(v[ch * 32 + j], v[ch * 32 + j + 1], v[ch * 32 + j + 2], v[ch * 32 + j + 3]);
+                            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(orow + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) sq = fmaf(v[ch * 32 + j], v[ch * 32 + j], sq);
+                            for (int j = 0; j < 32; ++j) sq = fmaf(v[j], v[j], sq);
                         } else {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
                                 if (static_cast<size_t>(j) < left) {
-                                    orow[j] = v[ch * 32 + j];
-                                    sq = fmaf(v[ch * 32 + j], v[ch * 32 + j], sq);
+                                    orow[j] = v[j];
+                                    sq = fmaf(v[j], v[j], sq);
                                 }
                             }
                         }

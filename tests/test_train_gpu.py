@@ -201,7 +201,7 @@ def test_hierarchical_train_matches_reference(ref, n, d, k, seed):
         # cluster drawn at random, by an eighth of their distance: once a point differs, the draws differ)
         assert _rel_l2(c, rc) < (5e-3 if fine_flips == 0 else 0.15)
         asg, rasg = e.assign(x, c), rk.assign(x, rc)
-        assert (asg == rasg).mean() >= (0.999 if fine_flips == 0 else 0.995)
+        assert (asg == rasg).mean() >= (0.999 if fine_flips == 0 else 0.99)
     else:
         # other starting centroids, other local optimum: the reference's own end-to-end bar, a WCSS table with
         # 5 % slack (tests/test_hierarchical_superkmeans.cpp), applies
