@@ -53,7 +53,9 @@ def parse_args():
     p.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     p.add_argument("--n", type=int, default=0, help="override the number of rows (0 = the workload's)")
     p.add_argument("--iters", type=int, default=0, help="override the iterations of a flat workload (0 = the workload's), for short profiling runs")
-    p.add_argument("--cpu-sample", type=int, default=1_000_000, help="rows of the workload given to the CPU reference by the cpu_baseline leg")
+    p.add_argument("--cpu-sample", type=int, default=0,
+                   help="rows of the workload given to the CPU reference by the cpu_baseline leg (0 = 1 000 000, or 400 000 when warm-up + steps exceed 8, "
+                        "so that a long run still ends within its time limit: the reference needs ~270 s per million rows of the headline workload)")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-pageable", action="store_true", help="skip the end-to-end figure from pageable host memory")
     p.add_argument("--no-cpu-baseline", action="store_true")
@@ -606,7 +608,8 @@ def main():
         from oracle import ref
 
         if ref.available():
-            rows = max(k, min(args.cpu_sample, n))
+            cpu_rows = args.cpu_sample or (1_000_000 if args.warmup + args.steps <= 8 else 400_000)
+            rows = max(k, min(cpu_rows, n))
             sample = np.ascontiguousarray(x[:rows].cpu().numpy())
             dt, r_it = reference_run(spec, sample, cent_host)
             cpu_baseline = {"value": rows * r_it / dt, "unit": unit, "cores": host_cores(), "kind": "reference", "seconds": dt,
