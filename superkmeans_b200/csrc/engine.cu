@@ -832,12 +832,14 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
         const double survival = static_cast<double>(host[0]) / (static_cast<double>(p.n) * n_sample);
         b.last_survival = survival;
         // Which family of routes: candidate lists cost one gathered 64-dimension block per surviving pair and step, so
-        // they win while few pairs survive the first test; past ~2.5 % of surviving pairs, and with at least a tile's
-        // worth of points per cluster, the points go, in the order of their previous centroid, through the chain over
-        // each tile's reachable centroids (whose cost follows the union of the tile's survivors, not their number).
+        // they win while few pairs survive the first test; past ~2.5 % of surviving pairs, and with at least 32 points
+        // per cluster (so that a tile of 128 ordered points spans few clusters), the points go, in the order of their
+        // previous centroid, through the chain over each tile's reachable centroids (whose cost follows the union of
+        // the tile's survivors, not their number).
         // Measured on one B200, 10 iterations: 10M x 1024, k = 10 000 (survival 3.3 - 4.2 %): 5.0 s against 7.3 s;
-        // 1M x 1536, k = 4096 (2.2 %, then below 0.1 %): lists 0.22 s against 0.39 s.
-        if (auto_mode && tc_ok && p.k <= 65536 && survival >= auto_chain_survival() && p.n >= 128 * p.k) {
+        // 1M x 1536, k = 4096 (2.2 %, then below 0.1 %): lists 0.22 s against 0.39 s; a shard of 1.25M x 1024 of the
+        // first workload (125 points per cluster): 0.58 s against 0.99 s.
+        if (auto_mode && tc_ok && p.k <= 65536 && survival >= auto_chain_survival() && p.n >= 32 * p.k) {
             run_pruned_pass_sorted(p, b, ratio_first, device, stream, timers, 10);
             return;
         }

@@ -60,7 +60,7 @@ def _equal_up_to_ties(xr, centroids, knn, rknn):
     return 1.0 - float((~tied).sum()) / len(knn), 1.0 - len(differ) / len(knn), differ, tied
 
 
-def _flat_against_reference(ref, x, k, seed, iters, replay, end_to_end_agree, classify_cap=150, other_routes=(10,)):
+def _flat_against_reference(ref, x, k, seed, iters, replay, end_to_end_agree, classify_cap=150, other_routes=(9, 10)):
     import superkmeans_b200 as skm
     from superkmeans_b200 import engine as eng
 
@@ -92,8 +92,8 @@ def _flat_against_reference(ref, x, k, seed, iters, replay, end_to_end_agree, cl
         print(f"iteration {t + 1}: assignments equal {raw:.5f}; {int(tied.sum())} of {len(differ)} differences are ties at the reference's own rounding "
               f"({int((rep[knn[differ]] == rep[rknn[differ]]).sum())} between coincident centroids, {int((rep != np.arange(k)).sum())} such centroids); equal up to ties {agree:.5f}")
         assert agree >= 0.999, (t, agree, raw)
-        # the same step through the kernels the automatic choice did not take here (the ordered chain with its candidate
-        # replay is what the headline workload runs)
+        # the same step through both families of kernels, whichever the automatic choice took: 9 = unordered lists with the
+        # dense chain for expensive points, 10 = ordered chain with its candidate replay (what the headline workload runs)
         for route in other_routes:
             eng.set_prune_split(route)
             try:
