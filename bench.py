@@ -304,26 +304,33 @@ def run_reference_arm(args, spec, n):
         print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref was not built (reference sources absent at build time)"}))
         return
     cores = host_cores()
-    # Sample sized for the whole run: about seven minutes of CPU work shared by warmup + steps passes.  Measured: one
-    # Train of the headline shape on 100 000 rows takes ~30 s on 16 cores (most of it work that grows with k, not n).
-    per_pass_s = 420.0 / max(1, args.warmup + args.steps)
+    # The whole arm is given about seven minutes of CPU work.  The reference needs ~3 s + 0.27 s per 1000 rows for one
+    # Train of the headline shape on 16 cores (measured: 30 s at 100 000 rows, 274 s at 1 000 000), and a sample with
+    # only a handful of points per cluster is not the workload any more (thousands of empty clusters per iteration,
+    # whose re-seeding walk then dominates).  So the passes are capped at one warm-up + three timed ones, each on as
+    # many rows as the budget allows; the line reports the passes actually run.
+    n_warm = min(args.warmup, 1)
+    n_timed = max(1, min(args.steps, 3))
+    per_pass_s = 420.0 / (n_warm + n_timed)
     if spec["kind"] == "assign":
         rows = int(min(n, max(10_000, 2.0e6 * per_pass_s / 60.0 * cores / 16.0)))
     else:
-        rows = int(min(n, 1_000_000, max(3 * spec["k"], 100_000 * per_pass_s / 30.0 * cores / 16.0 * (1024 * 10_000) / (spec["d"] * spec["k"]))))
+        rows = int(min(n, 1_000_000, max(3 * spec["k"], (per_pass_s - 3.0) / 0.271e-3 * cores / 16.0 * (1024 * 10_000) / (spec["d"] * spec["k"]))))
     rows = max(rows, spec["k"])
     sample, cent = host_rows_numpy(spec, rows)
     times, n_it = [], 1
-    for i in range(args.warmup + args.steps):
+    for i in range(n_warm + n_timed):
         dt, n_it = reference_run(spec, sample, cent)
-        if i >= args.warmup:
+        if i >= n_warm:
             times.append(dt)
     t = float(np.mean(times))
     value = rows * n_it / t
-    sample_text = (f"{rows} rows drawn on the host with the workload's law (a separate numpy draw, not the GPU arm's rows), same d, k and iterations; sized so that "
-                   f"{args.warmup + args.steps} passes take about seven minutes; SuperKMeans reference headers + SciPy OpenBLAS")
+    sample_text = (f"{rows} rows drawn on the host with the workload's law (a separate numpy draw, not the GPU arm's rows), same d, k and iterations; "
+                   f"{n_warm} warm-up + {n_timed} timed passes (asked for: {args.warmup} + {args.steps}), sized so that they take about seven minutes; "
+                   f"SuperKMeans reference headers + SciPy OpenBLAS")
     line = {
-        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": n_timed, "warmup": n_warm,
+        "steps_requested": args.steps, "warmup_requested": args.warmup,
         "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": spec["text"], "sample_rows": rows},
         "cpu_baseline": {"value": value, "unit": unit, "cores": int(cores), "kind": "reference", "sample": sample_text},
