@@ -184,7 +184,7 @@ skm_status skm_reset_phase_times(skm_handle* h);
 void skm_set_tensor_cores(int enabled);
 int skm_get_tensor_cores(void);
 /* Which kernels a pruned assignment pass uses.  0 (default): with rows that TMA can address (d % 4 == 0) the share of
- * pairs that survive the first test is estimated on 128 sampled centroids; below 2.5 % (or with fewer than 32 points per cluster) every point takes the
+ * pairs that survive the first test is estimated on 128 sampled centroids; below 2.5 % (or with fewer than 32 points per cluster, or fewer than 262 144 points) every point takes the
  * tensor-core first test + list walk in the original order (points that keep many centroids alive go through the dense
  * chain instead: the choice of 9), otherwise (and k <= 65536) the points are taken in the order of their previous
  * centroid and every tile of 128 goes through the chain over the centroids its rows can still reach (the choice of

@@ -838,8 +838,9 @@ void run_pruned_pass_on(PrunedParams p, PrunePassBuffers& b, float ratio_first, 
         // the tile's survivors, not their number).
         // Measured on one B200, 10 iterations: 10M x 1024, k = 10 000 (survival 3.3 - 4.2 %): 5.0 s against 7.3 s;
         // 1M x 1536, k = 4096 (2.2 %, then below 0.1 %): lists 0.22 s against 0.39 s; a shard of 1.25M x 1024 of the
-        // first workload (125 points per cluster): 0.58 s against 0.99 s.
-        if (auto_mode && tc_ok && p.k <= 65536 && survival >= auto_chain_survival() && p.n >= 32 * p.k) {
+        // first workload (125 points per cluster): 0.58 s against 0.99 s.  Below 2^18 points the fixed costs of the
+        // ordered route (sort, batches, host round trips) outweigh it: 100k x 768, k = 1000: 23.5 ms against 16.9 ms.
+        if (auto_mode && tc_ok && p.k <= 65536 && survival >= auto_chain_survival() && p.n >= 32 * p.k && p.n >= (size_t{1} << 18)) {
             run_pruned_pass_sorted(p, b, ratio_first, device, stream, timers, 10);
             return;
         }

@@ -275,7 +275,7 @@ def tensor_cores_enabled() -> bool:
 
 
 def set_prune_split(mode: int) -> None:
-    """0 = automatic (by the sampled survival of the first test: 9 below 2.5 % or under 32 points per cluster, else 10), 1 = SIMT candidate lists, 2 = dense SIMT chain, 3 = dense
+    """0 = automatic (by the sampled survival of the first test: 9 below 2.5 %, under 32 points per cluster or under 262 144 points, else 10), 1 = SIMT candidate lists, 2 = dense SIMT chain, 3 = dense
     tensor-core chain, 4 = tensor-core first test + list walk, 5 = as 4 with small lists, 6 = ordered points + exact gathered chain, 7 = ordered points +
     lists, 8 = as 7 with small lists, 9 = unordered lists with the dense chain for expensive points, 10 = ordered points + optimistic chain pass with
     exact redo, 11 = ordered points, route chosen per tile (see skm_set_prune_split)."""
