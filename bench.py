@@ -556,6 +556,9 @@ def main():
         rows_per_launch = work_rows(dom, n_local, stats, e if kind == "flat" else None) * args.steps / dom_calls
         roofline["traffic"] = traffic * rows_per_launch
         roofline["traffic_note"] = "DRAM bytes of an ncu capture of this kernel on a slice of the workload (same d and k), per row, times the rows one launch covers"
+        if dom == "sparse_chain_kernel":
+            roofline["traffic_note"] += ("; captured in the first pruned iteration of a 1 000 000-row slice, where a tile reaches about twice as many centroids as in "
+                                         "the later iterations of the full workload: an upper figure")
 
     # ---- the configurations that say "Train + Assign": Assign and AssignTrainingPoints of the training rows, device-resident
     extra_calls = None
